@@ -1,0 +1,166 @@
+"""numpy/ctypes front-end of the CPU oracle (TEST INFRASTRUCTURE, not product code).
+
+Only the tests, the smoke check and the benchmark's CPU-baseline leg import this module.
+The shared library is compiled on first use with the host's own instruction set (the file
+name carries a hash of the CPU flags, so a library built on one machine is never loaded on
+another).
+
+The arithmetic restates candle-core 0.10.2's CPU path behind tur's
+`QTensor::dequantize` (src/weights/mod.rs:150,161) and `QMatMul::forward`
+(src/models/layers/linear.rs:24); see turq_oracle.c for the pinning status.
+"""
+from __future__ import annotations
+
+import ctypes
+import hashlib
+import os
+import subprocess
+
+import numpy as np
+
+F32, F16, Q8_0, Q4_K, Q5_K, Q6_K, Q8_K, BF16 = 0, 1, 8, 12, 13, 14, 15, 30
+NAMES = {F32: "F32", F16: "F16", Q8_0: "Q8_0", Q4_K: "Q4_K", Q5_K: "Q5_K", Q6_K: "Q6_K",
+         Q8_K: "Q8_K", BF16: "BF16"}
+WEIGHT_TYPES = (Q8_0, Q4_K, Q5_K, Q6_K)
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_lib = None
+
+
+def _cpu_tag() -> str:
+    flags = ""
+    try:
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                if line.startswith("flags"):
+                    flags = line
+                    break
+    except OSError:
+        pass
+    return hashlib.sha1(flags.encode()).hexdigest()[:10]
+
+
+def lib_path() -> str:
+    return os.path.join(_HERE, f"libturq_oracle.{_cpu_tag()}.so")
+
+
+def build(force: bool = False) -> str:
+    """Compile turq_oracle.c for this host; returns the path of the shared library."""
+    out = lib_path()
+    src = os.path.join(_HERE, "turq_oracle.c")
+    hdr = os.path.join(_HERE, "turq_oracle.h")
+    stale = (not os.path.exists(out)
+             or os.path.getmtime(out) < max(os.path.getmtime(src), os.path.getmtime(hdr)))
+    if force or stale:
+        cmd = ["gcc", "-O3", "-march=native", "-fopenmp", "-fPIC", "-ffp-contract=off",
+               "-fno-fast-math", "-std=c11", "-shared", "-o", out + ".tmp", src, "-lm"]
+        subprocess.run(cmd, check=True, cwd=_HERE)
+        os.replace(out + ".tmp", out)
+    return out
+
+
+def _load():
+    global _lib
+    if _lib is not None:
+        return _lib
+    lib = ctypes.CDLL(build())
+    i64, vp, ci = ctypes.c_int64, ctypes.c_void_p, ctypes.c_int
+    lib.tqo_block_elems.argtypes = [ci]
+    lib.tqo_block_bytes.argtypes = [ci]
+    lib.tqo_row_bytes.argtypes = [ci, i64]
+    lib.tqo_row_bytes.restype = ctypes.c_size_t
+    lib.tqo_dequantize.argtypes = [ci, vp, vp, i64, i64]
+    lib.tqo_quantize.argtypes = [ci, vp, vp, i64, i64]
+    lib.tqo_qmatmul.argtypes = [ci, vp, i64, i64, vp, i64, vp, ci]
+    lib.tqo_matmul_f64.argtypes = [ci, vp, i64, i64, vp, i64, vp, ci]
+    lib.tqo_vec_dot.argtypes = [ci, vp, vp, i64]
+    lib.tqo_vec_dot.restype = ctypes.c_float
+    lib.tqo_f32_to_f16.argtypes = [ctypes.c_float]
+    lib.tqo_f32_to_f16.restype = ctypes.c_uint16
+    lib.tqo_f16_to_f32.argtypes = [ctypes.c_uint16]
+    lib.tqo_f16_to_f32.restype = ctypes.c_float
+    lib.tqo_num_threads.restype = ci
+    _lib = lib
+    return lib
+
+
+def _ptr(a: np.ndarray):
+    return a.ctypes.data_as(ctypes.c_void_p)
+
+
+def block_elems(dtype: int) -> int:
+    return _load().tqo_block_elems(dtype)
+
+
+def block_bytes(dtype: int) -> int:
+    return _load().tqo_block_bytes(dtype)
+
+
+def row_bytes(dtype: int, k: int) -> int:
+    rb = _load().tqo_row_bytes(dtype, k)
+    if rb == 0 and k != 0:
+        raise ValueError(f"k={k} is not a multiple of the {NAMES.get(dtype, dtype)} block size")
+    return rb
+
+
+def num_threads() -> int:
+    return _load().tqo_num_threads()
+
+
+def quantize(dtype: int, x: np.ndarray) -> np.ndarray:
+    """f32 [nrows, k] -> uint8 [nrows, row_bytes]."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    if x.ndim == 1:
+        x = x[None, :]
+    nrows, k = x.shape
+    out = np.empty((nrows, row_bytes(dtype, k)), dtype=np.uint8)
+    if _load().tqo_quantize(dtype, _ptr(x), _ptr(out), nrows, k) != 0:
+        raise ValueError("tqo_quantize failed")
+    return out
+
+
+def dequantize(dtype: int, blocks: np.ndarray, k: int) -> np.ndarray:
+    """uint8 [nrows, row_bytes] -> f32 [nrows, k]."""
+    blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+    rb = row_bytes(dtype, k)
+    nrows = blocks.size // rb if rb else 0
+    assert blocks.size == nrows * rb, "byte count is not a whole number of rows"
+    out = np.empty((nrows, k), dtype=np.float32)
+    if _load().tqo_dequantize(dtype, _ptr(blocks), _ptr(out), nrows, k) != 0:
+        raise ValueError("tqo_dequantize failed")
+    return out
+
+
+def act_type(dtype: int) -> int:
+    """Activation block format the CPU scheme pairs with a weight type."""
+    return Q8_0 if dtype == Q8_0 else Q8_K
+
+
+def qmatmul(dtype: int, w: np.ndarray, n: int, k: int, x: np.ndarray, nthreads: int = 0) -> np.ndarray:
+    """CPU quantized scheme: y[m, n] = quantize_act(x)[m] . W[n]."""
+    w = np.ascontiguousarray(w, dtype=np.uint8)
+    x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, k)
+    assert w.size == n * row_bytes(dtype, k)
+    y = np.empty((x.shape[0], n), dtype=np.float32)
+    if _load().tqo_qmatmul(dtype, _ptr(w), n, k, _ptr(x), x.shape[0], _ptr(y), nthreads) != 0:
+        raise ValueError("tqo_qmatmul failed")
+    return y
+
+
+def matmul_f64(dtype: int, w: np.ndarray, n: int, k: int, x: np.ndarray, nthreads: int = 0) -> np.ndarray:
+    """Dequantize-then-matmul with f64 accumulation, returned as f32."""
+    w = np.ascontiguousarray(w, dtype=np.uint8)
+    x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, k)
+    assert w.size == n * row_bytes(dtype, k)
+    y = np.empty((x.shape[0], n), dtype=np.float32)
+    if _load().tqo_matmul_f64(dtype, _ptr(w), n, k, _ptr(x), x.shape[0], _ptr(y), nthreads) != 0:
+        raise ValueError("tqo_matmul_f64 failed")
+    return y
+
+
+def rel_fro(a: np.ndarray, b: np.ndarray) -> float:
+    """Relative Frobenius error ||a - b|| / ||b|| in f64."""
+    a = np.asarray(a, dtype=np.float64)
+    b = np.asarray(b, dtype=np.float64)
+    den = np.linalg.norm(b)
+    return float(np.linalg.norm(a - b) / den) if den > 0 else float(np.linalg.norm(a - b))
