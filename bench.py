@@ -1,0 +1,362 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-linear path: one step = one decode pass (M activation rows)
+through every quantized linear of the named model's stack, weights resident in HBM.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2] [--m 1]
+  python bench.py --impl reference ...      # the CPU scheme on the host cores
+
+Prints ONE JSON line. `value` is weight bytes streamed per second over all GPUs (the
+"QMatMul weight GB/s" metric); `e2e` is the same pass driven through the host-buffer entry
+(activations copied in, results copied out, every linear); `roofline` describes the dominant
+GEMV kernel; `cpu_baseline` is the CPU restatement of the reference scheme on this host.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from tur_b200.workloads import BLOCK, SEED, TYPE_NAMES, WORKLOADS, Weight  # noqa: E402
+
+METRIC = "qmatmul_decode_weight_bandwidth"
+UNIT = "GB/s"
+# per-launch DRAM traffic of the dominant kernel from the ncu capture summarised under
+# profiles/ (bytes; None until a capture exists for that kernel/shape)
+NCU_TRAFFIC_BYTES = {}
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+# ------------------------------------------------------------------ synthetic inputs
+
+def gen_weight_blocks(w: Weight, seed: int, max_rows: int = 16384) -> np.ndarray:
+    """Seeded N(0, 0.02) f32 weights quantized by the CPU quantizer; beyond max_rows the
+    distinct rows repeat (the bytes streamed are what matters for timing)."""
+    import oracle
+    rng = np.random.default_rng(seed)
+    rows = min(w.n, max_rows)
+    f = (rng.standard_normal((rows, w.k), dtype=np.float32) * np.float32(0.02))
+    blocks = oracle.quantize(w.dtype, f)
+    if rows < w.n:
+        reps = -(-w.n // rows)
+        blocks = np.tile(blocks, (reps, 1))[: w.n]
+    return np.ascontiguousarray(blocks)
+
+
+def gen_activations(m: int, k: int, seed: int) -> np.ndarray:
+    return np.random.default_rng(seed).standard_normal((m, k), dtype=np.float32)
+
+
+# ------------------------------------------------------------------ clocks
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while a region runs (read-only)."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h) if hasattr(nv, "nvmlDeviceGetCurrentClocksEventReasons") \
+                    else nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for bit, name in self.REASONS.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.02)
+
+    def __enter__(self):
+        if self._nv:
+            self._stop.clear()
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        if self._thread:
+            self._stop.set()
+            self._thread.join()
+            self._thread = None
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ------------------------------------------------------------------ CPU arm
+
+def cpu_scheme_timing(wl, m: int, budget_s: float, steps: int | None = None, warmup: int = 1):
+    """Times the CPU restatement of the reference's QMatMul::forward scheme (oracle/) on one
+    layer's seven linears with all host threads. Returns (GB/s of weight bytes, cores, sample)."""
+    import oracle
+    ws = [(w, gen_weight_blocks(w, SEED + i)) for i, w in enumerate(wl.per_layer)]
+    xs = {src: gen_activations(m, k, SEED + 10**6 + m + j) for j, (src, k) in
+          enumerate(sorted({(w.source, w.k) for w in wl.per_layer}))}
+    layer_bytes = wl.layer_bytes()
+
+    def one_pass():
+        for w, b in ws:
+            oracle.qmatmul(w.dtype, b, w.n, w.k, xs[w.source])
+
+    for _ in range(max(1, warmup)):
+        one_pass()
+    times = []
+    t_end = time.perf_counter() + budget_s
+    while (steps is None and time.perf_counter() < t_end and len(times) < 200) or (steps is not None and len(times) < steps):
+        t0 = time.perf_counter()
+        one_pass()
+        times.append(time.perf_counter() - t0)
+    med = statistics.median(times)
+    sample = f"one layer of {wl.name} (7 linears, {layer_bytes / 1e6:.1f} MB of blocks), M={m}, {len(times)} passes, median"
+    return layer_bytes / med / 1e9, oracle.num_threads(), sample, med * 1e3, len(times)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    wl = WORKLOADS[args.workload]
+    gbs, cores, sample, ms, n = cpu_scheme_timing(wl, args.m, budget_s=1e9, steps=args.steps, warmup=args.warmup)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": n,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8", "data": "synthetic",
+        "config": {"workload": f"{wl.name}: {wl.description}, decode M={args.m}", "sample": sample},
+        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "note": "CPU restatement of the reference's quantized matmul scheme (candle-core is not vendored and no "
+                "Rust toolchain exists here); each step is one layer's seven linears on all host threads",
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------ GPU arm
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    from tur_b200 import GgmlDType, Mode, QMatMul, QTensor, context
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    wl = WORKLOADS[args.workload]
+    m = args.m
+    mode = Mode[args.mode]
+    ctx = context(local)
+
+    # ---- weights: every layer gets its own device buffers so a pass streams from HBM
+    protos = []
+    for i, w in enumerate(wl.per_layer):
+        protos.append((w, torch.from_numpy(gen_weight_blocks(w, SEED + i)).to(dev)))
+    layers = []
+    for _ in range(wl.layers):
+        layers.append([(w, QMatMul.from_arc(QTensor.new(b, GgmlDType(w.dtype), (w.n, w.k)))) for w, b in protos])
+    head = None
+    if wl.head is not None:
+        hb = torch.from_numpy(gen_weight_blocks(wl.head, SEED + 999)).to(dev)
+        head = (wl.head, QMatMul.from_arc(QTensor.new(hb, GgmlDType(wl.head.dtype), (wl.head.n, wl.head.k))))
+        del hb
+    del protos
+    torch.cuda.synchronize()
+
+    srcs = sorted({(w.source, w.k) for w in wl.per_layer})
+    x_host = {s: torch.from_numpy(gen_activations(m, k, SEED + 10**6 + m + j)).pin_memory() for j, (s, k) in enumerate(srcs)}
+    x_dev = {s: t.to(dev) for s, t in x_host.items()}
+    all_w = list(wl.per_layer) + ([wl.head] if wl.head else [])
+    y_dev = {w.name: torch.empty((m, w.n), dtype=torch.float32, device=dev) for w in all_w}
+    y_host = {w.name: torch.empty((m, w.n), dtype=torch.float32).pin_memory() for w in all_w}
+
+    def one_pass_device():
+        for layer in layers:
+            for w, mm in layer:
+                mm.forward(x_dev[w.source], mode=mode, out=y_dev[w.name])
+        if head:
+            head[1].forward(x_dev["hidden"], mode=mode, out=y_dev["output"])
+
+    def one_pass_host():
+        for layer in layers:
+            for w, mm in layer:
+                mm.forward(x_host[w.source], mode=mode, out=y_host[w.name])
+        if head:
+            head[1].forward(x_host["hidden"], mode=mode, out=y_host["output"])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- warm-up (also sizes the scratch buffers before graph capture)
+    for _ in range(max(3, args.warmup)):
+        one_pass_device()
+    torch.cuda.synchronize()
+    l0 = ctx.launch_count()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            one_pass_device()
+    launches_per_step = ctx.launch_count() - l0
+    for _ in range(max(3, args.warmup)):
+        graph.replay()
+
+    sampler = ClockSampler(local)
+    # ---- timed region: K graph replays, device timed
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with sampler:
+        e0.record()
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+    barrier()
+    ms = e0.elapsed_time(e1)
+
+    # ---- end to end through the host-buffer entry (H2D x, kernels, D2H y, per linear)
+    e2e_ms = None
+    e2e_steps = max(1, min(args.steps, args.e2e_steps))
+    if not args.no_e2e:
+        for _ in range(3):
+            one_pass_host()
+        barrier()
+        with sampler:
+            t0 = time.perf_counter()
+            e0.record()
+            for _ in range(e2e_steps):
+                one_pass_host()
+            e1.record()
+            torch.cuda.synchronize()
+            wall = (time.perf_counter() - t0) * 1e3
+        barrier()
+        e2e_ms = max(e0.elapsed_time(e1), wall)
+
+    # ---- dominant kernel, timed alone over the layers' distinct buffers
+    dom = max(wl.per_layer, key=lambda w: w.nbytes * (2 if w.name in ("ffn_gate", "ffn_up") else 1))
+    di = list(wl.per_layer).index(dom)
+    dg = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(dg, stream=side):
+            for layer in layers:
+                layer[di][1].forward(x_dev[dom.source], mode=mode, out=y_dev[dom.name])
+    for _ in range(3):
+        dg.replay()
+    torch.cuda.synchronize()
+    reps = 20
+    e0.record()
+    for _ in range(reps):
+        dg.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    # each forward = activation-quantization launch + GEMV launch; the pair is timed together
+    dom_us = e0.elapsed_time(e1) * 1e3 / (reps * len(layers))
+    alg_bytes = dom.nbytes + m * dom.k * 4 + m * dom.n * 4
+
+    # ---- reduce over ranks
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms or 0.0], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0]), (float(t[1]) if e2e_ms is not None else None)
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    total_bytes = wl.total_bytes() * world
+    value = total_bytes * args.steps / (ms * 1e-3) / 1e9
+    peak, peak_kind = measured_peaks()
+    achieved = alg_bytes / (dom_us * 1e-6) / 1e9
+    traffic = NCU_TRAFFIC_BYTES.get((dom.name, wl.name))
+    h2d = sum(m * w.k * 4 for w in wl.per_layer) * wl.layers + (m * wl.head.k * 4 if wl.head else 0)
+    d2h = sum(m * w.n * 4 for w in wl.per_layer) * wl.layers + (m * wl.head.n * 4 if wl.head else 0)
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8" if mode in (Mode.INT8_ACT, Mode.AUTO) else "f32", "data": "synthetic",
+        "config": {
+            "workload": f"{wl.name}: {wl.description}, decode M={m}, {wl.layers} layers x 7 linears"
+                        + (" + lm_head" if wl.head else ""),
+            "mode": mode.name, "weight_bytes_per_step_per_gpu": wl.total_bytes(), "parallelism": f"replicas x{world}",
+            "l2": "weights per pass exceed L2 (distinct buffers per layer); CUDA-graph replay per step",
+            "tokens_per_s": m * world * args.steps / (ms * 1e-3),
+        },
+        "e2e": None if e2e_ms is None else {
+            "value": total_bytes * e2e_steps / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "steps": e2e_steps,
+            "ms_per_step": e2e_ms / e2e_steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+            "api": "turq_qmatmul_host per linear (pinned host x and y)"},
+        "gpu_launches": launches_per_step * args.steps,
+        "clocks": sampler.summary(),
+        "roofline": {"bound": "hbm", "kernel": f"gemv_int8 {TYPE_NAMES[dom.dtype]} {dom.n}x{dom.k} ({dom.name}) + its activation quantization",
+                     "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                     "us_per_launch": dom_us, "algorithmic_bytes": alg_bytes, "traffic": traffic},
+    }
+    if not args.no_cpu and world == 1:
+        gbs, cores, sample, _, _ = cpu_scheme_timing(wl, m, budget_s=args.cpu_budget)
+        line["cpu_baseline"] = {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="turq", choices=["turq", "reference"])
+    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
+    ap.add_argument("--m", type=int, default=1, help="activation rows per linear (decode batch)")
+    ap.add_argument("--mode", default="INT8_ACT", choices=["AUTO", "INT8_ACT", "EXACT_F32", "TENSOR_CORE"])
+    ap.add_argument("--e2e-steps", type=int, default=20)
+    ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU-baseline timing")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

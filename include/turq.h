@@ -1,0 +1,137 @@
+/*
+ * turq - B200 (sm_100a) kernels for GGUF quantized linear layers behind a flat C ABI.
+ *
+ * This is the drop-in boundary for the one path tur runs through candle:
+ *   LinearX::Quantized -> QMatMul::forward          (src/models/layers/linear.rs:19-32)
+ *   QVarBuilder::get   -> Arc<QTensor> on a device  (src/weights/gguf_varbuilder.rs:52-94)
+ *   QTensor::dequantize                             (src/weights/mod.rs:150,161)
+ * A Rust `-sys` crate binds exactly these symbols; candle's names map as noted per entry.
+ *
+ * Conventions
+ *   - every entry returns a turq_status (0 = OK); nothing throws or aborts across the ABI;
+ *   - `turq_last_error(ctx)` returns the message of the last failing call on that context;
+ *   - pointers named dev_* are CUDA device pointers on the context's device, host_* are
+ *     host pointers; `stream` is a cudaStream_t passed as void* (NULL = default stream);
+ *   - calls are asynchronous on `stream` unless stated otherwise; the library never frees
+ *     caller memory and never falls back to a CPU implementation;
+ *   - dtype arguments use the GGUF wire-format type ids (enum turq_dtype).
+ */
+#ifndef TURQ_H
+#define TURQ_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TURQ_VERSION 100 /* major*10000 + minor*100 + patch */
+
+typedef enum {
+  TURQ_OK = 0,
+  TURQ_E_INVALID_ARG = 1, /* null pointer, bad handle, bad enum value */
+  TURQ_E_SHAPE = 2,       /* K not a multiple of the block size, M <= 0, size mismatch */
+  TURQ_E_DTYPE = 3,       /* type not supported by this entry */
+  TURQ_E_ALIGN = 4,       /* pointer alignment requirement not met */
+  TURQ_E_CUDA = 5,        /* a CUDA runtime call or kernel launch failed */
+  TURQ_E_NCCL = 6,
+  TURQ_E_TIMEOUT = 7,
+  TURQ_E_NO_DEVICE = 8, /* no CUDA device: there is no CPU fallback */
+  TURQ_E_LIMIT = 9      /* request exceeds a fixed capacity of the entry point */
+} turq_status;
+
+/* GGUF tensor type ids (candle: GgmlDType) */
+typedef enum {
+  TURQ_F32 = 0,
+  TURQ_F16 = 1,
+  TURQ_Q8_0 = 8,
+  TURQ_Q4_K = 12,
+  TURQ_Q5_K = 13,
+  TURQ_Q6_K = 14,
+  TURQ_Q8_K = 15,
+  TURQ_BF16 = 30
+} turq_dtype;
+
+/* How QMatMul::forward computes.
+ *   INT8_ACT    the reference CPU scheme: activation rows are quantized to Q8_0 (Q8_0 weights)
+ *               or Q8_K (K-quant weights) and block dots run in integers.
+ *   EXACT_F32   weights are dequantized on the fly to their exact f32 values, f32 FMA.
+ *   TENSOR_CORE tcgen05 f16 MMA with f32 accumulation (prefill-sized M).
+ *   AUTO        INT8_ACT for M <= 64, TENSOR_CORE above. */
+typedef enum {
+  TURQ_MODE_AUTO = 0,
+  TURQ_MODE_INT8_ACT = 1,
+  TURQ_MODE_EXACT_F32 = 2,
+  TURQ_MODE_TENSOR_CORE = 3
+} turq_mode;
+
+typedef struct turq_ctx turq_ctx;         /* one device + its scratch memory */
+typedef struct turq_qtensor turq_qtensor; /* immutable quantized weight on the device */
+
+int32_t turq_version(void);
+const char* turq_status_string(int32_t status);
+
+/* Block geometry of the wire format (candle: GgmlDType::block_size / type_size). */
+int32_t turq_block_elems(int32_t dtype);
+int32_t turq_block_bytes(int32_t dtype);
+/* bytes of one row of k elements, 0 if k is not a whole number of blocks */
+size_t turq_row_bytes(int32_t dtype, int64_t k);
+
+/* Context: binds to CUDA device `device`. Fails with TURQ_E_NO_DEVICE when none exists. */
+int32_t turq_ctx_create(int32_t device, turq_ctx** out);
+int32_t turq_ctx_destroy(turq_ctx* ctx);
+const char* turq_last_error(const turq_ctx* ctx);
+/* Number of kernels this context has launched so far (bookkeeping for benchmarks). */
+int64_t turq_ctx_launch_count(const turq_ctx* ctx);
+
+/* QTensor from GGUF wire-format blocks in host memory: uploads and converts to the device
+ * layout. Replaces gguf_file::Content::tensor(reader, name, device)
+ * (src/weights/gguf_varbuilder.rs:73) / QTensor::new. Synchronous. */
+int32_t turq_qtensor_from_host(turq_ctx* ctx, int32_t dtype, int64_t n_rows, int64_t n_cols,
+                               const void* host_blocks, size_t nbytes, turq_qtensor** out);
+/* Same, blocks already in device memory (copied; the caller keeps ownership of dev_blocks). */
+int32_t turq_qtensor_from_device(turq_ctx* ctx, int32_t dtype, int64_t n_rows, int64_t n_cols,
+                                 const void* dev_blocks, size_t nbytes, void* stream,
+                                 turq_qtensor** out);
+/* Tensor-parallel shards (no counterpart in the reference, which is single-device):
+ * rows [row0, row0+n) for column-parallel linears, columns [col0, col0+n) for row-parallel
+ * ones. row0 must be a multiple of 16, col0 and n (columns) multiples of the block size.
+ * The result owns its own memory. */
+int32_t turq_qtensor_slice_rows(turq_ctx* ctx, const turq_qtensor* src, int64_t row0, int64_t n,
+                                turq_qtensor** out);
+int32_t turq_qtensor_slice_cols(turq_ctx* ctx, const turq_qtensor* src, int64_t col0, int64_t n,
+                                turq_qtensor** out);
+int32_t turq_qtensor_free(turq_qtensor* qt);
+/* candle: QTensor::{dtype, shape, storage_size_in_bytes}; any out pointer may be NULL */
+int32_t turq_qtensor_info(const turq_qtensor* qt, int32_t* dtype, int64_t* n_rows,
+                          int64_t* n_cols, size_t* wire_bytes);
+
+/* QTensor::dequantize (src/weights/mod.rs:150): dev_out is [n_rows, n_cols] row-major of
+ * out_dtype (F32, F16 or BF16). F32 output is bit-exact with the GGUF definition. */
+int32_t turq_dequantize(turq_ctx* ctx, const turq_qtensor* qt, int32_t out_dtype, void* dev_out,
+                        void* stream);
+
+/* Activation quantization used inside QMatMul::forward (entered at
+ * src/models/layers/linear.rs:24): x [m, k] (F32 or BF16) -> wire-format Q8_0 or Q8_K blocks,
+ * m rows of turq_row_bytes(fmt, k) bytes. */
+int32_t turq_quantize_act(turq_ctx* ctx, int32_t fmt, const void* dev_x, int32_t x_dtype,
+                          int64_t m, int64_t k, void* dev_blocks, void* stream);
+
+/* QMatMul::forward (src/models/layers/linear.rs:24) with the optional bias add of
+ * LinearX::forward (linear.rs:25-28): y[m, n] = sum_k x[m, k] * W[n, k] (+ bias[n]).
+ * x is [m, n_cols] row-major F32 or BF16, y is [m, n_rows] row-major F32,
+ * dev_bias is NULL or n_rows f32 values. */
+int32_t turq_qmatmul(turq_ctx* ctx, const turq_qtensor* qt, const void* dev_x, int32_t x_dtype,
+                     int64_t m, float* dev_y, int32_t mode, const float* dev_bias, void* stream);
+
+/* The same call for a caller that keeps activations in host memory, as tur does today
+ * (Device::Cpu everywhere: tests/common.rs:5): copies x to the device, runs, copies y back
+ * and synchronizes. x and y are f32. */
+int32_t turq_qmatmul_host(turq_ctx* ctx, const turq_qtensor* qt, const float* host_x, int64_t m,
+                          float* host_y, int32_t mode, const float* host_bias);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,227 @@
+"""CUDA path against the CPU oracle, through the C ABI (tur_b200.quantized is a thin ctypes
+layer). Bit-exact for dequantize and activation blocks; matmul within 2e-3 relative
+Frobenius error of the oracle of the same scheme (the north-star tolerance)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+TYPES = [oracle.Q8_0, oracle.Q4_K, oracle.Q5_K, oracle.Q6_K]
+ids = [oracle.NAMES[t] for t in TYPES]
+TOL = 2e-3
+SEED = 299792458
+
+
+@pytest.fixture(scope="module")
+def tq():
+    import tur_b200
+    from tur_b200 import quantized
+    assert torch.cuda.is_available()
+    return quantized
+
+
+def bits(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+
+def make_weight(dt, n, k, seed):
+    rng = np.random.default_rng(seed)
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    return oracle.quantize(dt, w)
+
+
+# ---------------------------------------------------------------- dequantize
+
+@pytest.mark.parametrize("dt", TYPES, ids=ids)
+def test_dequantize_golden_blocks_bit_exact(tq, dt, golden_dir):
+    g = np.load(os.path.join(golden_dir, "gguf_dequantize.npz"))
+    name = oracle.NAMES[dt]
+    blocks, want = g[f"{name}_blocks"], g[f"{name}_f32"]
+    nb, be = blocks.shape[0], oracle.block_elems(dt)
+    # lay the blocks out as a [rows, cols] tensor in several shapes (1 row, ragged rows)
+    for rows in (1, 3, nb):
+        if nb % rows:
+            continue
+        cols = nb // rows * be
+        qt = tq.QTensor.new(blocks, tq.GgmlDType(dt), (rows, cols))
+        got = qt.dequantize().cpu().numpy()
+        assert np.array_equal(bits(got), bits(want.reshape(rows, cols)))
+
+
+@pytest.mark.parametrize("dt", TYPES, ids=ids)
+@pytest.mark.parametrize("n,k", [(1, 256), (17, 2560), (33, 4096), (130, 512)])
+def test_dequantize_matches_oracle_bit_exact(tq, dt, n, k):
+    w = make_weight(dt, n, k, SEED + n + k)
+    qt = tq.QTensor.new(w, tq.GgmlDType(dt), (n, k))
+    assert qt.shape() == (n, k) and qt.dtype() == tq.GgmlDType(dt) and qt.storage_size_in_bytes() == w.size
+    want = oracle.dequantize(dt, w, k)
+    got = qt.dequantize().cpu().numpy()
+    assert np.array_equal(bits(got), bits(want))
+    # from device-resident wire blocks too
+    qt2 = tq.QTensor.new(torch.from_numpy(w).cuda(), tq.GgmlDType(dt), (n, k))
+    assert np.array_equal(bits(qt2.dequantize().cpu().numpy()), bits(want))
+    # half outputs are the exact f32 rounded once
+    h = qt.dequantize(torch.float16).cpu()
+    assert torch.equal(h, torch.from_numpy(want).to(torch.float16))
+    b = qt.dequantize(torch.bfloat16).cpu()
+    assert torch.equal(b, torch.from_numpy(want).to(torch.bfloat16))
+
+
+# ---------------------------------------------------------------- activation quantization
+
+def test_activation_blocks_golden_bit_exact(tq, golden_dir):
+    g = np.load(os.path.join(golden_dir, "oracle_matmul.npz"))
+    x = torch.from_numpy(g["act_x"]).cuda()
+    assert np.array_equal(tq.quantize_act(x, tq.GgmlDType.Q8K).cpu().numpy(), g["act_q8k"])
+    assert np.array_equal(tq.quantize_act(x, tq.GgmlDType.Q8_0).cpu().numpy(), g["act_q8_0"])
+    g2 = np.load(os.path.join(golden_dir, "gguf_quantize_q8_0.npz"))
+    got = tq.quantize_act(torch.from_numpy(g2["x"]).cuda(), tq.GgmlDType.Q8_0).cpu().numpy()
+    assert np.array_equal(got, g2["blocks"])
+
+
+@pytest.mark.parametrize("m,k", [(1, 256), (5, 4096), (16, 12288), (64, 2560)])
+def test_activation_blocks_match_oracle_bit_exact(tq, m, k):
+    rng = np.random.default_rng(SEED + 10**6 + m)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    x[0, :256] = 0.0
+    if m > 1:
+        x[1] *= 1e-3
+        x[1, 3], x[1, 77] = 2.5, -2.5      # equal magnitudes: first wins, mirror clamps
+    xd = torch.from_numpy(x).cuda()
+    for fmt, ofmt in ((tq.GgmlDType.Q8K, oracle.Q8_K), (tq.GgmlDType.Q8_0, oracle.Q8_0)):
+        assert np.array_equal(tq.quantize_act(xd, fmt).cpu().numpy(), oracle.quantize(ofmt, x))
+    xb = xd.to(torch.bfloat16)
+    want = oracle.quantize(oracle.Q8_K, xb.float().cpu().numpy())
+    assert np.array_equal(tq.quantize_act(xb, tq.GgmlDType.Q8K).cpu().numpy(), want)
+
+
+# ---------------------------------------------------------------- matmul
+
+@pytest.mark.parametrize("dt", TYPES, ids=ids)
+def test_matmul_golden(tq, dt, golden_dir):
+    g = np.load(os.path.join(golden_dir, "oracle_matmul.npz"))
+    name = oracle.NAMES[dt]
+    w, x = g[f"{name}_w"], g["act_x"]
+    n, k = w.shape[0], x.shape[1]
+    mm = tq.QMatMul.from_arc(tq.QTensor.new(w, tq.GgmlDType(dt), (n, k)))
+    xd = torch.from_numpy(x).cuda()
+    y_int = mm.forward(xd, mode=tq.Mode.INT8_ACT).cpu().numpy()
+    y_f32 = mm.forward(xd, mode=tq.Mode.EXACT_F32).cpu().numpy()
+    assert oracle.rel_fro(y_int, g[f"{name}_y_cpu_scheme"]) < 1e-5
+    assert oracle.rel_fro(y_f32, g[f"{name}_y_f64"]) < 1e-5
+
+
+@pytest.mark.parametrize("dt", TYPES, ids=ids)
+@pytest.mark.parametrize("n,k,m", [(16, 256, 1), (3, 512, 2), (1024, 4096, 1), (1024, 4096, 4), (100, 2560, 8),
+                                   (640, 2560, 16), (257, 1024, 5), (4096, 12288, 1), (2048, 1024, 33)])
+def test_matmul_matches_oracle_of_same_scheme(tq, dt, n, k, m):
+    w = make_weight(dt, n, k, SEED + 1000 + n)
+    rng = np.random.default_rng(SEED + 10**6 + m)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    mm = tq.QMatMul.from_arc(tq.QTensor.new(w, tq.GgmlDType(dt), (n, k)))
+    xd = torch.from_numpy(x).cuda()
+    y_int = mm.forward(xd, mode=tq.Mode.INT8_ACT).cpu().numpy()
+    want_int = oracle.qmatmul(dt, w, n, k, x)
+    assert y_int.shape == (m, n)
+    assert oracle.rel_fro(y_int, want_int) < TOL
+    assert oracle.rel_fro(y_int, want_int) < 1e-5      # only the f32 summation order differs
+    if n * k * m <= 4096 * 4096 * 4:
+        y_f32 = mm.forward(xd, mode=tq.Mode.EXACT_F32).cpu().numpy()
+        want_f64 = oracle.matmul_f64(dt, w, n, k, x)
+        assert oracle.rel_fro(y_f32, want_f64) < TOL
+        assert oracle.rel_fro(y_f32, want_f64) < 1e-5
+        # the two schemes differ by the activation rounding noise only
+        assert oracle.rel_fro(y_int, want_f64) < 2e-2
+
+
+@pytest.mark.parametrize("dt", TYPES, ids=ids)
+def test_rows_are_independent_of_batch_size_and_bias_is_added(tq, dt):
+    """tur's tests rely on a token's result not depending on its batch neighbours
+    (tests/pipeline_integration.rs:275-369, tests/engine_integration.rs:171-251)."""
+    n, k = 512, 2048
+    w = make_weight(dt, n, k, SEED + 5)
+    rng = np.random.default_rng(SEED + 6)
+    x = torch.from_numpy(rng.standard_normal((16, k)).astype(np.float32)).cuda()
+    bias = torch.from_numpy(rng.standard_normal(n).astype(np.float32)).cuda()
+    mm = tq.QMatMul.from_arc(tq.QTensor.new(w, tq.GgmlDType(dt), (n, k)))
+    for mode in (tq.Mode.INT8_ACT, tq.Mode.EXACT_F32):
+        y16 = mm.forward(x, mode=mode)
+        for rows in (slice(0, 1), slice(3, 5), slice(7, 16)):
+            assert torch.equal(mm.forward(x[rows], mode=mode), y16[rows])
+        yb = mm.forward(x, bias=bias, mode=mode)
+        assert torch.equal(yb, y16 + bias)
+    # rank-3 input keeps its leading dims (src/models/qwen3.rs:269-274 feeds [B, L, hidden])
+    y3 = mm.forward(x.reshape(2, 8, k), mode=tq.Mode.INT8_ACT)
+    assert y3.shape == (2, 8, n) and torch.equal(y3.reshape(16, n), mm.forward(x, mode=tq.Mode.INT8_ACT))
+
+
+@pytest.mark.parametrize("dt", TYPES, ids=ids)
+def test_bf16_activations(tq, dt):
+    n, k, m = 256, 1024, 4
+    w = make_weight(dt, n, k, SEED + 9)
+    rng = np.random.default_rng(SEED + 10)
+    xb = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).cuda().to(torch.bfloat16)
+    xr = xb.float().cpu().numpy()
+    mm = tq.QMatMul.from_arc(tq.QTensor.new(w, tq.GgmlDType(dt), (n, k)))
+    assert oracle.rel_fro(mm.forward(xb, mode=tq.Mode.INT8_ACT).cpu().numpy(), oracle.qmatmul(dt, w, n, k, xr)) < 1e-5
+    assert oracle.rel_fro(mm.forward(xb, mode=tq.Mode.EXACT_F32).cpu().numpy(), oracle.matmul_f64(dt, w, n, k, xr)) < 1e-5
+
+
+@pytest.mark.parametrize("dt", TYPES, ids=ids)
+def test_host_buffer_entry(tq, dt):
+    n, k, m = 300, 1024, 3
+    w = make_weight(dt, n, k, SEED + 11)
+    rng = np.random.default_rng(SEED + 12)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    mm = tq.QMatMul.from_arc(tq.QTensor.new(w, tq.GgmlDType(dt), (n, k)))
+    y = mm.forward(torch.from_numpy(x), bias=torch.from_numpy(bias)).numpy()
+    want = oracle.qmatmul(dt, w, n, k, x) + bias
+    assert oracle.rel_fro(y, want) < 1e-5
+
+
+@pytest.mark.parametrize("dt", TYPES, ids=ids)
+def test_shards_reassemble_the_unsharded_result(tq, dt):
+    """Column-parallel shards (row slices) are bit-exact pieces; row-parallel shards (column
+    slices) sum to the full result up to f32 reassociation."""
+    n, k, m = 96, 2048, 4
+    w = make_weight(dt, n, k, SEED + 13)
+    rng = np.random.default_rng(SEED + 14)
+    x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).cuda()
+    qt = tq.QTensor.new(w, tq.GgmlDType(dt), (n, k))
+    full = tq.QMatMul(qt).forward(x, mode=tq.Mode.INT8_ACT)
+    parts = [tq.QMatMul(qt.slice_rows(r0, cnt)).forward(x, mode=tq.Mode.INT8_ACT) for r0, cnt in ((0, 32), (32, 48), (80, 16))]
+    assert torch.equal(torch.cat(parts, dim=1), full)
+    acc = torch.zeros_like(full)
+    for c0, cnt in ((0, 768), (768, 256), (1024, 1024)):
+        acc += tq.QMatMul(qt.slice_cols(c0, cnt)).forward(x[:, c0:c0 + cnt].contiguous(), mode=tq.Mode.INT8_ACT)
+    assert oracle.rel_fro(acc.cpu().numpy(), full.cpu().numpy()) < 1e-5
+    assert np.array_equal(bits(qt.slice_cols(768, 256).dequantize().cpu().numpy()),
+                          bits(oracle.dequantize(dt, w, k)[:, 768:1024]))
+
+
+def test_error_paths_return_status_not_crash(tq):
+    w = make_weight(oracle.Q4_K, 16, 256, 1)
+    with pytest.raises(tq.TurqError) as e:
+        tq.QTensor.new(w, tq.GgmlDType.Q4K, (16, 512))          # byte count mismatch
+    assert e.value.status == 2
+    with pytest.raises(tq.TurqError) as e:
+        tq.QTensor.new(w, tq.GgmlDType.Q4K, (16, 100))          # not whole blocks
+    assert e.value.status == 2
+    with pytest.raises(tq.TurqError) as e:
+        tq.QTensor.new(w, tq.GgmlDType.F32, (16, 256))          # not a quantized weight type
+    assert e.value.status == 3
+    qt = tq.QTensor.new(w, tq.GgmlDType.Q4K, (16, 256))
+    with pytest.raises(tq.TurqError):
+        tq.QMatMul(qt).forward(torch.zeros(2, 128, device="cuda"))
+    with pytest.raises(tq.TurqError) as e:
+        qt.slice_rows(8, 8)
+    assert e.value.status == 2
+    with pytest.raises(tq.TurqError) as e:
+        qt.slice_cols(0, 100)
+    assert e.value.status == 2

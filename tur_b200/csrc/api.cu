@@ -1,0 +1,390 @@
+// C-ABI layer: argument validation, handle lifetimes, scratch memory, dispatch to kernels.
+// No entry throws, aborts or falls back to a CPU path; failures come back as turq_status
+// with a message stored on the context.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+
+#include "../../include/turq.h"
+#include "turq_internal.h"
+
+struct turq_ctx {
+  int device = 0;
+  int sm_count = 0;
+  uint8_t* scratch = nullptr;  // activation planes / f16 operand for the current call
+  size_t scratch_bytes = 0;
+  uint8_t* io = nullptr;  // device staging for the host-buffer entry (x, y, bias)
+  size_t io_bytes = 0;
+  int* dev_status = nullptr;  // status word written by kernels with bounded waits
+  cudaStream_t own_stream = nullptr;
+  int64_t launches = 0;
+  std::string err;
+};
+
+struct turq_qtensor {
+  int device = 0;
+  int dtype = 0;
+  int64_t n_rows = 0, n_cols = 0;
+  size_t wire_bytes = 0;
+  uint8_t* tiles = nullptr;
+  size_t tile_bytes = 0;
+};
+
+namespace {
+
+int32_t fail(turq_ctx* ctx, int32_t st, const char* fmt, ...) {
+  if (ctx) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    try {
+      ctx->err = buf;
+    } catch (...) {
+    }
+  }
+  return st;
+}
+
+int32_t cuda_fail(turq_ctx* ctx, cudaError_t e, const char* what) {
+  return fail(ctx, TURQ_E_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+#define TQ_CUDA(ctx, call)                                   \
+  do {                                                       \
+    cudaError_t e__ = (call);                                \
+    if (e__ != cudaSuccess) return cuda_fail(ctx, e__, #call); \
+  } while (0)
+
+int32_t ensure(turq_ctx* ctx, uint8_t** buf, size_t* have, size_t need) {
+  if (need <= *have) return TURQ_OK;
+  size_t want = need + need / 4;
+  want = (want + 0xFFFFF) & ~(size_t)0xFFFFF;
+  if (*buf) {
+    TQ_CUDA(ctx, cudaDeviceSynchronize());
+    TQ_CUDA(ctx, cudaFree(*buf));
+    *buf = nullptr;
+    *have = 0;
+  }
+  TQ_CUDA(ctx, cudaMalloc(reinterpret_cast<void**>(buf), want));
+  *have = want;
+  return TURQ_OK;
+}
+
+size_t tiled_bytes(int dtype, int64_t n_rows, int64_t k) {
+  int64_t row_tiles = (n_rows + TQ_TILE_ROWS - 1) / TQ_TILE_ROWS;
+  return (size_t)row_tiles * (size_t)(k / tq_block_elems(dtype)) * (size_t)tq_tile_bytes(dtype);
+}
+
+int32_t check_weight_args(turq_ctx* ctx, int32_t dtype, int64_t n_rows, int64_t n_cols, size_t nbytes) {
+  if (!tq_is_weight_type(dtype))
+    return fail(ctx, TURQ_E_DTYPE, "dtype %d is not a supported quantized weight type (Q8_0, Q4_K, Q5_K, Q6_K)", dtype);
+  if (n_rows <= 0 || n_cols <= 0) return fail(ctx, TURQ_E_SHAPE, "shape [%lld, %lld] must be positive", (long long)n_rows, (long long)n_cols);
+  if (n_cols % tq_block_elems(dtype) != 0)
+    return fail(ctx, TURQ_E_SHAPE, "n_cols %lld is not a multiple of the block size %d", (long long)n_cols, tq_block_elems(dtype));
+  size_t expect = (size_t)n_rows * (size_t)(n_cols / tq_block_elems(dtype)) * (size_t)tq_block_bytes(dtype);
+  if (nbytes != expect)
+    return fail(ctx, TURQ_E_SHAPE, "got %zu bytes, shape [%lld, %lld] of this type needs %zu", nbytes, (long long)n_rows, (long long)n_cols, expect);
+  return TURQ_OK;
+}
+
+int32_t new_qtensor(turq_ctx* ctx, int dtype, int64_t n_rows, int64_t n_cols, turq_qtensor** out) {
+  turq_qtensor* qt = new (std::nothrow) turq_qtensor();
+  if (!qt) return fail(ctx, TURQ_E_INVALID_ARG, "out of host memory");
+  qt->device = ctx->device;
+  qt->dtype = dtype;
+  qt->n_rows = n_rows;
+  qt->n_cols = n_cols;
+  qt->wire_bytes = (size_t)n_rows * (size_t)(n_cols / tq_block_elems(dtype)) * (size_t)tq_block_bytes(dtype);
+  qt->tile_bytes = tiled_bytes(dtype, n_rows, n_cols);
+  cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&qt->tiles), qt->tile_bytes);
+  if (e != cudaSuccess) {
+    delete qt;
+    return cuda_fail(ctx, e, "cudaMalloc(weight tiles)");
+  }
+  *out = qt;
+  return TURQ_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t turq_version(void) { return TURQ_VERSION; }
+
+const char* turq_status_string(int32_t st) {
+  switch (st) {
+    case TURQ_OK: return "ok";
+    case TURQ_E_INVALID_ARG: return "invalid argument";
+    case TURQ_E_SHAPE: return "shape mismatch";
+    case TURQ_E_DTYPE: return "unsupported dtype";
+    case TURQ_E_ALIGN: return "misaligned pointer";
+    case TURQ_E_CUDA: return "CUDA error";
+    case TURQ_E_NCCL: return "NCCL error";
+    case TURQ_E_TIMEOUT: return "timeout";
+    case TURQ_E_NO_DEVICE: return "no CUDA device (no CPU fallback exists)";
+    case TURQ_E_LIMIT: return "capacity of the entry point exceeded";
+    default: return "unknown status";
+  }
+}
+
+int32_t turq_block_elems(int32_t dtype) { return tq_block_elems(dtype); }
+int32_t turq_block_bytes(int32_t dtype) { return tq_block_bytes(dtype); }
+size_t turq_row_bytes(int32_t dtype, int64_t k) {
+  int be = tq_block_elems(dtype);
+  if (be == 0 || k < 0 || k % be != 0) return 0;
+  return (size_t)(k / be) * (size_t)tq_block_bytes(dtype);
+}
+
+int32_t turq_ctx_create(int32_t device, turq_ctx** out) {
+  if (!out) return TURQ_E_INVALID_ARG;
+  *out = nullptr;
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || count <= 0) {
+    cudaGetLastError();
+    return TURQ_E_NO_DEVICE;
+  }
+  if (device < 0 || device >= count) return TURQ_E_INVALID_ARG;
+  turq_ctx* ctx = new (std::nothrow) turq_ctx();
+  if (!ctx) return TURQ_E_INVALID_ARG;
+  ctx->device = device;
+  cudaDeviceProp prop;
+  if (cudaSetDevice(device) != cudaSuccess || cudaGetDeviceProperties(&prop, device) != cudaSuccess ||
+      cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaMalloc(reinterpret_cast<void**>(&ctx->dev_status), sizeof(int)) != cudaSuccess ||
+      cudaMemset(ctx->dev_status, 0, sizeof(int)) != cudaSuccess) {
+    cudaGetLastError();
+    delete ctx;
+    return TURQ_E_CUDA;
+  }
+  ctx->sm_count = prop.multiProcessorCount;
+  int32_t st = ensure(ctx, &ctx->scratch, &ctx->scratch_bytes, (size_t)8 << 20);
+  if (st != TURQ_OK) {
+    delete ctx;
+    return st;
+  }
+  *out = ctx;
+  return TURQ_OK;
+}
+
+int32_t turq_ctx_destroy(turq_ctx* ctx) {
+  if (!ctx) return TURQ_E_INVALID_ARG;
+  cudaSetDevice(ctx->device);
+  cudaDeviceSynchronize();
+  if (ctx->scratch) cudaFree(ctx->scratch);
+  if (ctx->io) cudaFree(ctx->io);
+  if (ctx->dev_status) cudaFree(ctx->dev_status);
+  if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
+  delete ctx;
+  return TURQ_OK;
+}
+
+const char* turq_last_error(const turq_ctx* ctx) { return ctx ? ctx->err.c_str() : "null context"; }
+int64_t turq_ctx_launch_count(const turq_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+int32_t turq_qtensor_from_device(turq_ctx* ctx, int32_t dtype, int64_t n_rows, int64_t n_cols,
+                                 const void* dev_blocks, size_t nbytes, void* stream, turq_qtensor** out) {
+  if (!ctx || !out || !dev_blocks) return fail(ctx, TURQ_E_INVALID_ARG, "null argument");
+  *out = nullptr;
+  int32_t st = check_weight_args(ctx, dtype, n_rows, n_cols, nbytes);
+  if (st != TURQ_OK) return st;
+  TQ_CUDA(ctx, cudaSetDevice(ctx->device));
+  turq_qtensor* qt = nullptr;
+  st = new_qtensor(ctx, dtype, n_rows, n_cols, &qt);
+  if (st != TURQ_OK) return st;
+  cudaError_t e = turq::launch_repack(dtype, static_cast<const uint8_t*>(dev_blocks), qt->tiles, n_rows, n_cols,
+                                      static_cast<cudaStream_t>(stream));
+  ctx->launches++;
+  if (e != cudaSuccess) {
+    turq_qtensor_free(qt);
+    return cuda_fail(ctx, e, "repack launch");
+  }
+  *out = qt;
+  return TURQ_OK;
+}
+
+int32_t turq_qtensor_from_host(turq_ctx* ctx, int32_t dtype, int64_t n_rows, int64_t n_cols,
+                               const void* host_blocks, size_t nbytes, turq_qtensor** out) {
+  if (!ctx || !out || !host_blocks) return fail(ctx, TURQ_E_INVALID_ARG, "null argument");
+  *out = nullptr;
+  int32_t st = check_weight_args(ctx, dtype, n_rows, n_cols, nbytes);
+  if (st != TURQ_OK) return st;
+  TQ_CUDA(ctx, cudaSetDevice(ctx->device));
+  uint8_t* tmp = nullptr;
+  TQ_CUDA(ctx, cudaMalloc(reinterpret_cast<void**>(&tmp), nbytes));
+  cudaError_t e = cudaMemcpyAsync(tmp, host_blocks, nbytes, cudaMemcpyHostToDevice, ctx->own_stream);
+  if (e == cudaSuccess) {
+    st = turq_qtensor_from_device(ctx, dtype, n_rows, n_cols, tmp, nbytes, ctx->own_stream, out);
+    if (st == TURQ_OK) e = cudaStreamSynchronize(ctx->own_stream);
+  }
+  cudaFree(tmp);
+  if (st != TURQ_OK) return st;
+  if (e != cudaSuccess) {
+    if (*out) turq_qtensor_free(*out);
+    *out = nullptr;
+    return cuda_fail(ctx, e, "weight upload");
+  }
+  return TURQ_OK;
+}
+
+int32_t turq_qtensor_slice_rows(turq_ctx* ctx, const turq_qtensor* src, int64_t row0, int64_t n, turq_qtensor** out) {
+  if (!ctx || !src || !out) return fail(ctx, TURQ_E_INVALID_ARG, "null argument");
+  *out = nullptr;
+  if (row0 < 0 || n <= 0 || row0 + n > src->n_rows) return fail(ctx, TURQ_E_SHAPE, "row range [%lld, +%lld) outside [0, %lld)", (long long)row0, (long long)n, (long long)src->n_rows);
+  if (row0 % TQ_TILE_ROWS != 0) return fail(ctx, TURQ_E_SHAPE, "row0 %lld must be a multiple of %d", (long long)row0, TQ_TILE_ROWS);
+  TQ_CUDA(ctx, cudaSetDevice(ctx->device));
+  turq_qtensor* qt = nullptr;
+  int32_t st = new_qtensor(ctx, src->dtype, n, src->n_cols, &qt);
+  if (st != TURQ_OK) return st;
+  size_t per_row_tile = (size_t)(src->n_cols / tq_block_elems(src->dtype)) * tq_tile_bytes(src->dtype);
+  size_t off = (size_t)(row0 / TQ_TILE_ROWS) * per_row_tile;
+  // A trailing partial row-tile of the slice carries rows of the source beyond row0+n; they
+  // are never written to an output because every kernel bounds rows by n_rows.
+  size_t avail = src->tile_bytes - off;
+  size_t nbytes = qt->tile_bytes < avail ? qt->tile_bytes : avail;
+  cudaError_t e = cudaMemcpyAsync(qt->tiles, src->tiles + off, nbytes, cudaMemcpyDeviceToDevice, ctx->own_stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->own_stream);
+  if (e != cudaSuccess) {
+    turq_qtensor_free(qt);
+    return cuda_fail(ctx, e, "slice_rows copy");
+  }
+  *out = qt;
+  return TURQ_OK;
+}
+
+int32_t turq_qtensor_slice_cols(turq_ctx* ctx, const turq_qtensor* src, int64_t col0, int64_t n, turq_qtensor** out) {
+  if (!ctx || !src || !out) return fail(ctx, TURQ_E_INVALID_ARG, "null argument");
+  *out = nullptr;
+  const int be = tq_block_elems(src->dtype);
+  if (col0 < 0 || n <= 0 || col0 + n > src->n_cols) return fail(ctx, TURQ_E_SHAPE, "column range [%lld, +%lld) outside [0, %lld)", (long long)col0, (long long)n, (long long)src->n_cols);
+  if (col0 % be != 0 || n % be != 0) return fail(ctx, TURQ_E_SHAPE, "column range must be whole blocks of %d", be);
+  TQ_CUDA(ctx, cudaSetDevice(ctx->device));
+  turq_qtensor* qt = nullptr;
+  int32_t st = new_qtensor(ctx, src->dtype, src->n_rows, n, &qt);
+  if (st != TURQ_OK) return st;
+  int64_t row_tiles = (src->n_rows + TQ_TILE_ROWS - 1) / TQ_TILE_ROWS;
+  cudaError_t e = turq::launch_slice_cols(src->dtype, src->tiles, qt->tiles, row_tiles, src->n_cols / be, col0 / be,
+                                          n / be, ctx->own_stream);
+  ctx->launches++;
+  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->own_stream);
+  if (e != cudaSuccess) {
+    turq_qtensor_free(qt);
+    return cuda_fail(ctx, e, "slice_cols");
+  }
+  *out = qt;
+  return TURQ_OK;
+}
+
+int32_t turq_qtensor_free(turq_qtensor* qt) {
+  if (!qt) return TURQ_E_INVALID_ARG;
+  if (qt->tiles) {
+    cudaSetDevice(qt->device);
+    cudaFree(qt->tiles);
+  }
+  delete qt;
+  return TURQ_OK;
+}
+
+int32_t turq_qtensor_info(const turq_qtensor* qt, int32_t* dtype, int64_t* n_rows, int64_t* n_cols, size_t* wire_bytes) {
+  if (!qt) return TURQ_E_INVALID_ARG;
+  if (dtype) *dtype = qt->dtype;
+  if (n_rows) *n_rows = qt->n_rows;
+  if (n_cols) *n_cols = qt->n_cols;
+  if (wire_bytes) *wire_bytes = qt->wire_bytes;
+  return TURQ_OK;
+}
+
+int32_t turq_dequantize(turq_ctx* ctx, const turq_qtensor* qt, int32_t out_dtype, void* dev_out, void* stream) {
+  if (!ctx || !qt || !dev_out) return fail(ctx, TURQ_E_INVALID_ARG, "null argument");
+  if (out_dtype != TURQ_F32 && out_dtype != TURQ_F16 && out_dtype != TURQ_BF16)
+    return fail(ctx, TURQ_E_DTYPE, "dequantize output must be F32, F16 or BF16 (got %d)", out_dtype);
+  if (qt->device != ctx->device) return fail(ctx, TURQ_E_INVALID_ARG, "tensor lives on device %d, context on %d", qt->device, ctx->device);
+  if ((uintptr_t)dev_out % 16 != 0) return fail(ctx, TURQ_E_ALIGN, "dev_out must be 16-byte aligned");
+  TQ_CUDA(ctx, cudaSetDevice(ctx->device));
+  cudaError_t e = turq::launch_dequant(qt->dtype, qt->tiles, dev_out, out_dtype, qt->n_rows, qt->n_cols,
+                                       static_cast<cudaStream_t>(stream));
+  ctx->launches++;
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "dequantize launch");
+  return TURQ_OK;
+}
+
+int32_t turq_quantize_act(turq_ctx* ctx, int32_t fmt, const void* dev_x, int32_t x_dtype, int64_t m, int64_t k,
+                          void* dev_blocks, void* stream) {
+  if (!ctx || !dev_x || !dev_blocks) return fail(ctx, TURQ_E_INVALID_ARG, "null argument");
+  if (fmt != TURQ_Q8_0 && fmt != TURQ_Q8_K) return fail(ctx, TURQ_E_DTYPE, "activation format must be Q8_0 or Q8_K (got %d)", fmt);
+  if (x_dtype != TURQ_F32 && x_dtype != TURQ_BF16) return fail(ctx, TURQ_E_DTYPE, "activations must be F32 or BF16 (got %d)", x_dtype);
+  if (m <= 0 || k <= 0 || k % tq_block_elems(fmt) != 0)
+    return fail(ctx, TURQ_E_SHAPE, "m=%lld k=%lld: k must be a positive multiple of %d", (long long)m, (long long)k, tq_block_elems(fmt));
+  if ((uintptr_t)dev_x % 16 != 0 || (uintptr_t)dev_blocks % 4 != 0)
+    return fail(ctx, TURQ_E_ALIGN, "dev_x must be 16-byte and dev_blocks 4-byte aligned");
+  TQ_CUDA(ctx, cudaSetDevice(ctx->device));
+  cudaError_t e = turq::launch_quantize_act_wire(fmt, dev_x, x_dtype, m, k, dev_blocks, static_cast<cudaStream_t>(stream));
+  ctx->launches++;
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "quantize_act launch");
+  return TURQ_OK;
+}
+
+int32_t turq_qmatmul(turq_ctx* ctx, const turq_qtensor* qt, const void* dev_x, int32_t x_dtype, int64_t m,
+                     float* dev_y, int32_t mode, const float* dev_bias, void* stream) {
+  if (!ctx || !qt || !dev_x || !dev_y) return fail(ctx, TURQ_E_INVALID_ARG, "null argument");
+  if (x_dtype != TURQ_F32 && x_dtype != TURQ_BF16) return fail(ctx, TURQ_E_DTYPE, "activations must be F32 or BF16 (got %d)", x_dtype);
+  if (m <= 0) return fail(ctx, TURQ_E_SHAPE, "m=%lld must be positive", (long long)m);
+  if (m > INT32_MAX / 2) return fail(ctx, TURQ_E_SHAPE, "m=%lld too large", (long long)m);
+  if (qt->device != ctx->device) return fail(ctx, TURQ_E_INVALID_ARG, "tensor lives on device %d, context on %d", qt->device, ctx->device);
+  if ((uintptr_t)dev_x % 16 != 0 || (uintptr_t)dev_y % 4 != 0) return fail(ctx, TURQ_E_ALIGN, "dev_x must be 16-byte aligned");
+  if (mode == TURQ_MODE_AUTO) mode = m <= 64 ? TURQ_MODE_INT8_ACT : TURQ_MODE_TENSOR_CORE;
+  TQ_CUDA(ctx, cudaSetDevice(ctx->device));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t k = qt->n_cols;
+  int launches = 0;
+  cudaError_t e = cudaSuccess;
+  if (mode == TURQ_MODE_INT8_ACT) {
+    const int fmt = qt->dtype == TURQ_Q8_0 ? TQ_Q8_0 : TQ_Q8_K;
+    turq::ActPackPlan plan = turq::plan_act_pack(fmt, m, k);
+    int32_t st = ensure(ctx, &ctx->scratch, &ctx->scratch_bytes, plan.total);
+    if (st != TURQ_OK) return st;
+    e = turq::launch_quantize_act_pack(fmt, dev_x, x_dtype, m, k, ctx->scratch, s);
+    launches++;
+    if (e == cudaSuccess)
+      e = turq::launch_gemv_int8(qt->dtype, qt->tiles, qt->n_rows, k, ctx->scratch, m, dev_y, dev_bias, ctx->sm_count, s, &launches);
+  } else if (mode == TURQ_MODE_EXACT_F32) {
+    e = turq::launch_gemv_f32(qt->dtype, qt->tiles, qt->n_rows, k, dev_x, x_dtype, m, dev_y, dev_bias, ctx->sm_count, s, &launches);
+  } else if (mode == TURQ_MODE_TENSOR_CORE) {
+    int32_t st = ensure(ctx, &ctx->scratch, &ctx->scratch_bytes, turq::gemm_tc_scratch_bytes(m, k));
+    if (st != TURQ_OK) return st;
+    e = turq::launch_gemm_tc(qt->dtype, qt->tiles, qt->n_rows, k, dev_x, x_dtype, m, dev_y, dev_bias, ctx->scratch,
+                             ctx->sm_count, s, &launches, ctx->dev_status);
+  } else {
+    return fail(ctx, TURQ_E_INVALID_ARG, "unknown mode %d", mode);
+  }
+  ctx->launches += launches;
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul launch");
+  return TURQ_OK;
+}
+
+int32_t turq_qmatmul_host(turq_ctx* ctx, const turq_qtensor* qt, const float* host_x, int64_t m, float* host_y,
+                          int32_t mode, const float* host_bias) {
+  if (!ctx || !qt || !host_x || !host_y) return fail(ctx, TURQ_E_INVALID_ARG, "null argument");
+  if (m <= 0) return fail(ctx, TURQ_E_SHAPE, "m=%lld must be positive", (long long)m);
+  TQ_CUDA(ctx, cudaSetDevice(ctx->device));
+  auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+  const size_t xb = up((size_t)m * qt->n_cols * 4), yb = up((size_t)m * qt->n_rows * 4), bb = up((size_t)qt->n_rows * 4);
+  int32_t st = ensure(ctx, &ctx->io, &ctx->io_bytes, xb + yb + bb);
+  if (st != TURQ_OK) return st;
+  float* dx = reinterpret_cast<float*>(ctx->io);
+  float* dy = reinterpret_cast<float*>(ctx->io + xb);
+  float* db = host_bias ? reinterpret_cast<float*>(ctx->io + xb + yb) : nullptr;
+  cudaStream_t s = ctx->own_stream;
+  TQ_CUDA(ctx, cudaMemcpyAsync(dx, host_x, (size_t)m * qt->n_cols * 4, cudaMemcpyHostToDevice, s));
+  if (db) TQ_CUDA(ctx, cudaMemcpyAsync(db, host_bias, (size_t)qt->n_rows * 4, cudaMemcpyHostToDevice, s));
+  st = turq_qmatmul(ctx, qt, dx, TURQ_F32, m, dy, mode, db, s);
+  if (st != TURQ_OK) return st;
+  TQ_CUDA(ctx, cudaMemcpyAsync(host_y, dy, (size_t)m * qt->n_rows * 4, cudaMemcpyDeviceToHost, s));
+  TQ_CUDA(ctx, cudaStreamSynchronize(s));
+  return TURQ_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,62 @@
+// Internal declarations shared by the kernel translation units and the C-ABI layer.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "layout.h"
+
+namespace turq {
+
+// Quantized activations as the GEMV kernels consume them (planes inside one scratch buffer).
+//   qs    int8  [m][k]          element order = input order
+//   dsc   f32   [m][k/bs]       bs = 256 (Q8_K) or 32 (Q8_0; value is the f16-rounded scale)
+//   bs16  int16 [m][k/16]       Q8_K only: sums of 16 consecutive qs
+//   bs32  int16 [m][k/32]       Q8_K only: sums of 32 consecutive qs
+struct ActPack {
+  const int8_t* qs;
+  const float* dsc;
+  const int16_t* bs16;
+  const int16_t* bs32;
+};
+
+struct ActPackPlan {
+  size_t off_qs, off_dsc, off_bs16, off_bs32, total;
+};
+ActPackPlan plan_act_pack(int fmt, int64_t m, int64_t k);
+
+// wire -> device tiles. n_rows may be any positive value; rows are padded to 16.
+cudaError_t launch_repack(int dtype, const uint8_t* dev_wire, uint8_t* dev_tiles, int64_t n_rows,
+                          int64_t k, cudaStream_t s);
+// device tiles -> row-major [n_rows, k]
+cudaError_t launch_dequant(int dtype, const uint8_t* dev_tiles, void* dev_out, int out_dtype,
+                           int64_t n_rows, int64_t k, cudaStream_t s);
+// copy K-tile range [kt0, kt0+nkt) of every row-tile into a new tiled tensor
+cudaError_t launch_slice_cols(int dtype, const uint8_t* src_tiles, uint8_t* dst_tiles,
+                              int64_t row_tiles, int64_t src_ktiles, int64_t kt0, int64_t nkt,
+                              cudaStream_t s);
+
+// activations -> wire-format Q8_0 / Q8_K blocks
+cudaError_t launch_quantize_act_wire(int fmt, const void* x, int x_dtype, int64_t m, int64_t k,
+                                     void* blocks, cudaStream_t s);
+// activations -> ActPack planes at `scratch` (laid out by plan_act_pack)
+cudaError_t launch_quantize_act_pack(int fmt, const void* x, int x_dtype, int64_t m, int64_t k,
+                                     uint8_t* scratch, cudaStream_t s);
+
+// y[m, n] = act . W^T in the integer scheme; m is processed in groups of up to 16 rows.
+cudaError_t launch_gemv_int8(int dtype, const uint8_t* tiles, int64_t n_rows, int64_t k,
+                             const uint8_t* act_scratch, int64_t m, float* y, const float* bias,
+                             int sm_count, cudaStream_t s, int* launches);
+// y[m, n] = x . dequant(W)^T with f32 FMAs on exact f32 weights.
+cudaError_t launch_gemv_f32(int dtype, const uint8_t* tiles, int64_t n_rows, int64_t k,
+                            const void* x, int x_dtype, int64_t m, float* y, const float* bias,
+                            int sm_count, cudaStream_t s, int* launches);
+
+// Tensor-core GEMM (tcgen05): x [m, k] -> f16 operand in scratch, then the fused
+// dequantize + MMA kernel. scratch must hold gemm_tc_scratch_bytes(m, k).
+size_t gemm_tc_scratch_bytes(int64_t m, int64_t k);
+cudaError_t launch_gemm_tc(int dtype, const uint8_t* tiles, int64_t n_rows, int64_t k,
+                           const void* x, int x_dtype, int64_t m, float* y, const float* bias,
+                           uint8_t* scratch, int sm_count, cudaStream_t s, int* launches,
+                           int* dev_status_word);
+
+}  // namespace turq

@@ -1,0 +1,227 @@
+"""Host-side mirror of the candle operator surface tur uses for quantized linears.
+
+Names and argument meaning follow `candle_core::quantized` as called by the reference:
+  GgmlDType                          block_size / type_size
+  QTensor::new / dequantize / shape  src/weights/gguf_varbuilder.rs:62,73,79; src/weights/mod.rs:150
+  QMatMul::from_arc / forward        src/models/layers/linear.rs:24,69
+Every method is a thin call into the C ABI (include/turq.h); torch is used only to own
+device memory and to name the current CUDA stream. Nothing here computes on the CPU.
+"""
+from __future__ import annotations
+
+import ctypes
+import enum
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from . import _lib
+
+
+class TurqError(RuntimeError):
+    """A C-ABI call returned a non-zero turq_status."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(f"turq status {status} ({_lib.load().turq_status_string(status).decode()}): {message}")
+        self.status = status
+
+
+class GgmlDType(enum.IntEnum):
+    F32 = 0
+    F16 = 1
+    Q8_0 = 8
+    Q4K = 12
+    Q5K = 13
+    Q6K = 14
+    Q8K = 15
+    BF16 = 30
+
+    def block_size(self) -> int:
+        return _lib.load().turq_block_elems(int(self))
+
+    def type_size(self) -> int:
+        return _lib.load().turq_block_bytes(int(self))
+
+
+class Mode(enum.IntEnum):
+    AUTO = 0
+    INT8_ACT = 1
+    EXACT_F32 = 2
+    TENSOR_CORE = 3
+
+
+_TORCH_TO_GGML = {torch.float32: GgmlDType.F32, torch.float16: GgmlDType.F16, torch.bfloat16: GgmlDType.BF16}
+_GGML_TO_TORCH = {v: k for k, v in _TORCH_TO_GGML.items()}
+
+
+class _Context:
+    """One turq_ctx per CUDA device, created on first use."""
+
+    def __init__(self, device: int):
+        lib = _lib.load()
+        handle = ctypes.c_void_p()
+        st = lib.turq_ctx_create(device, ctypes.byref(handle))
+        if st != 0:
+            raise TurqError(st, f"turq_ctx_create(device={device}) failed")
+        self.handle = handle
+        self.device = device
+
+    def check(self, st: int) -> None:
+        if st != 0:
+            raise TurqError(st, _lib.load().turq_last_error(self.handle).decode())
+
+    def launch_count(self) -> int:
+        return int(_lib.load().turq_ctx_launch_count(self.handle))
+
+
+_contexts: dict[int, _Context] = {}
+
+
+def context(device: int | torch.device | None = None) -> _Context:
+    if device is None:
+        device = torch.cuda.current_device() if torch.cuda.is_available() else 0
+    if isinstance(device, torch.device):
+        device = device.index if device.index is not None else torch.cuda.current_device()
+    ctx = _contexts.get(device)
+    if ctx is None:
+        ctx = _contexts[device] = _Context(device)
+    return ctx
+
+
+def _stream_ptr(device: int) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+class QTensor:
+    """Immutable quantized weight [rows, cols] resident on one GPU."""
+
+    def __init__(self, handle: ctypes.c_void_p, ctx: _Context):
+        self._h = handle
+        self._ctx = ctx
+        lib = _lib.load()
+        dt, r, c, nb = ctypes.c_int32(), ctypes.c_int64(), ctypes.c_int64(), ctypes.c_size_t()
+        ctx.check(lib.turq_qtensor_info(handle, ctypes.byref(dt), ctypes.byref(r), ctypes.byref(c), ctypes.byref(nb)))
+        self._dtype, self._shape, self._nbytes = GgmlDType(dt.value), (r.value, c.value), nb.value
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            try:
+                _lib.load().turq_qtensor_free(h)
+            except Exception:
+                pass
+
+    @classmethod
+    def new(cls, blocks: np.ndarray | bytes | torch.Tensor, dtype: GgmlDType, shape: Sequence[int],
+            device: int | torch.device | None = None) -> "QTensor":
+        """From GGUF wire-format blocks (host bytes, or a uint8 CUDA tensor)."""
+        if len(shape) != 2:
+            raise TurqError(2, f"QTensor needs a 2-D shape, got {tuple(shape)}")
+        rows, cols = int(shape[0]), int(shape[1])
+        lib = _lib.load()
+        out = ctypes.c_void_p()
+        if isinstance(blocks, torch.Tensor) and blocks.is_cuda:
+            ctx = context(blocks.device)
+            blocks = blocks.contiguous().view(torch.uint8)
+            ctx.check(lib.turq_qtensor_from_device(ctx.handle, int(dtype), rows, cols, ctypes.c_void_p(blocks.data_ptr()),
+                                                   blocks.numel(), _stream_ptr(ctx.device), ctypes.byref(out)))
+            torch.cuda.current_stream(ctx.device).synchronize()
+            return cls(out, ctx)
+        ctx = context(device)
+        if isinstance(blocks, torch.Tensor):
+            blocks = blocks.contiguous().view(torch.uint8).numpy()
+        buf = np.frombuffer(blocks, dtype=np.uint8) if isinstance(blocks, (bytes, bytearray)) else np.ascontiguousarray(blocks).view(np.uint8).reshape(-1)
+        ctx.check(lib.turq_qtensor_from_host(ctx.handle, int(dtype), rows, cols, buf.ctypes.data_as(ctypes.c_void_p),
+                                             buf.size, ctypes.byref(out)))
+        return cls(out, ctx)
+
+    def dtype(self) -> GgmlDType:
+        return self._dtype
+
+    def shape(self) -> tuple[int, int]:
+        return self._shape
+
+    def storage_size_in_bytes(self) -> int:
+        return self._nbytes
+
+    def device(self) -> torch.device:
+        return torch.device("cuda", self._ctx.device)
+
+    def dequantize(self, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        out = torch.empty(self._shape, dtype=out_dtype, device=self.device())
+        self._ctx.check(_lib.load().turq_dequantize(self._ctx.handle, self._h, int(_TORCH_TO_GGML[out_dtype]),
+                                                    ctypes.c_void_p(out.data_ptr()), _stream_ptr(self._ctx.device)))
+        return out
+
+    def slice_rows(self, row0: int, n: int) -> "QTensor":
+        out = ctypes.c_void_p()
+        self._ctx.check(_lib.load().turq_qtensor_slice_rows(self._ctx.handle, self._h, row0, n, ctypes.byref(out)))
+        return QTensor(out, self._ctx)
+
+    def slice_cols(self, col0: int, n: int) -> "QTensor":
+        out = ctypes.c_void_p()
+        self._ctx.check(_lib.load().turq_qtensor_slice_cols(self._ctx.handle, self._h, col0, n, ctypes.byref(out)))
+        return QTensor(out, self._ctx)
+
+
+def quantize_act(x: torch.Tensor, fmt: GgmlDType) -> torch.Tensor:
+    """x [m, k] (f32/bf16, CUDA) -> uint8 [m, row_bytes] of wire-format Q8_0 / Q8_K blocks."""
+    if not x.is_cuda:
+        raise TurqError(8, "quantize_act needs a CUDA tensor (no CPU fallback)")
+    ctx = context(x.device)
+    x2 = x.reshape(-1, x.shape[-1]).contiguous()
+    m, k = x2.shape
+    lib = _lib.load()
+    rb = lib.turq_row_bytes(int(fmt), k)
+    out = torch.empty((m, max(rb, 1)), dtype=torch.uint8, device=x.device)
+    ctx.check(lib.turq_quantize_act(ctx.handle, int(fmt), ctypes.c_void_p(x2.data_ptr()), int(_TORCH_TO_GGML[x2.dtype]),
+                                    m, k, ctypes.c_void_p(out.data_ptr()), _stream_ptr(ctx.device)))
+    return out
+
+
+class QMatMul:
+    """y = x . W^T for a quantized W (candle: QMatMul::from_arc + Module::forward)."""
+
+    def __init__(self, qtensor: QTensor, mode: Mode = Mode.AUTO):
+        self.qtensor = qtensor
+        self.mode = mode
+
+    @classmethod
+    def from_arc(cls, qtensor: QTensor) -> "QMatMul":
+        return cls(qtensor)
+
+    from_qtensor = from_arc
+
+    def forward(self, x: torch.Tensor, bias: Optional[torch.Tensor] = None, mode: Optional[Mode] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """x [..., k] -> [..., n] f32. CUDA tensors run stream-ordered on the current stream;
+        CPU tensors go through the host-buffer entry (copies inside the call)."""
+        qt = self.qtensor
+        n, k = qt.shape()
+        if x.dim() < 1 or x.shape[-1] != k:
+            raise TurqError(2, f"last dim of x {tuple(x.shape)} must equal in-features {k}")
+        mode = self.mode if mode is None else mode
+        lead = tuple(x.shape[:-1])
+        lib = _lib.load()
+        ctx = qt._ctx
+        if not x.is_cuda:
+            x2 = x.reshape(-1, k).to(torch.float32).contiguous()
+            y = out if out is not None else torch.empty((x2.shape[0], n), dtype=torch.float32, pin_memory=x2.is_pinned())
+            b = bias.to(torch.float32).contiguous() if bias is not None else None
+            ctx.check(lib.turq_qmatmul_host(ctx.handle, qt._h, ctypes.c_void_p(x2.data_ptr()), x2.shape[0],
+                                            ctypes.c_void_p(y.data_ptr()), int(mode),
+                                            ctypes.c_void_p(b.data_ptr()) if b is not None else None))
+            return y.reshape(*lead, n)
+        if x.dtype not in (torch.float32, torch.bfloat16):
+            x = x.to(torch.float32)
+        x2 = x.reshape(-1, k).contiguous()
+        m = x2.shape[0]
+        y = out if out is not None else torch.empty((m, n), dtype=torch.float32, device=x.device)
+        ctx.check(lib.turq_qmatmul(ctx.handle, qt._h, ctypes.c_void_p(x2.data_ptr()), int(_TORCH_TO_GGML[x2.dtype]), m,
+                                   ctypes.c_void_p(y.data_ptr()), int(mode),
+                                   ctypes.c_void_p(bias.data_ptr()) if bias is not None else None,
+                                   _stream_ptr(ctx.device)))
+        return y.reshape(*lead, n)
+
+    __call__ = forward

@@ -1,0 +1,77 @@
+"""Shapes of the quantized-linear stacks the benchmark configs name (out x in per weight).
+
+Each workload is a decoder's per-layer linear set as tur builds it
+(src/models/qwen3.rs:153-155 MLP, :212-215 attention; src/models/granite_41.rs:142-144,
+:192-195) with the per-weight GGUF types of the named quantization mix: in the *_K_M mixes
+`attn_v` and `ffn_down` (and the output head) are Q6_K, the rest Q4_K or Q5_K.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+Q8_0, Q4_K, Q5_K, Q6_K = 8, 12, 13, 14
+BLOCK = {Q8_0: (32, 34), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210)}
+TYPE_NAMES = {Q8_0: "Q8_0", Q4_K: "Q4_K", Q5_K: "Q5_K", Q6_K: "Q6_K"}
+SEED = 299792458  # tur's default seed (src/backend/engine.rs:60)
+
+
+@dataclass(frozen=True)
+class Weight:
+    name: str       # GGUF tensor stem: attn_q, attn_k, attn_v, attn_output, ffn_gate, ffn_up, ffn_down, output
+    n: int          # out features (rows)
+    k: int          # in features (cols)
+    dtype: int
+    source: str     # which activation feeds it: "hidden", "attn", "inter"
+    parallel: str   # tensor-parallel split: "column" (split n) or "row" (split k)
+
+    @property
+    def nbytes(self) -> int:
+        be, bb = BLOCK[self.dtype]
+        return self.n * (self.k // be) * bb
+
+
+@dataclass(frozen=True)
+class Workload:
+    name: str
+    description: str
+    hidden: int
+    layers: int
+    per_layer: tuple
+    head: Weight | None
+
+    def layer_bytes(self) -> int:
+        return sum(w.nbytes for w in self.per_layer)
+
+    def total_bytes(self) -> int:
+        return self.layers * self.layer_bytes() + (self.head.nbytes if self.head else 0)
+
+    def flops_per_row(self) -> int:
+        per = sum(2 * w.n * w.k for w in self.per_layer) * self.layers
+        return per + (2 * self.head.n * self.head.k if self.head else 0)
+
+
+def _decoder(hidden, q_out, kv_out, inter, main, alt):
+    return (
+        Weight("attn_q", q_out, hidden, main, "hidden", "column"),
+        Weight("attn_k", kv_out, hidden, main, "hidden", "column"),
+        Weight("attn_v", kv_out, hidden, alt, "hidden", "column"),
+        Weight("attn_output", hidden, q_out, main, "attn", "row"),
+        Weight("ffn_gate", inter, hidden, main, "hidden", "column"),
+        Weight("ffn_up", inter, hidden, main, "hidden", "column"),
+        Weight("ffn_down", hidden, inter, alt, "inter", "row"),
+    )
+
+
+def _mk(name, desc, hidden, q_out, kv_out, inter, layers, main, alt, vocab=None):
+    head = Weight("output", vocab, hidden, Q6_K if main != Q8_0 else Q8_0, "hidden", "column") if vocab else None
+    return Workload(name, desc, hidden, layers, _decoder(hidden, q_out, kv_out, inter, main, alt), head)
+
+
+WORKLOADS = {
+    "cfg1": _mk("cfg1", "Qwen3-0.6B linear stack, Q8_0", 1024, 2048, 1024, 3072, 28, Q8_0, Q8_0),
+    "cfg2": _mk("cfg2", "Qwen3-8B linear stack, Q4_K_M (+ Q6_K lm_head)", 4096, 4096, 1024, 12288, 36, Q4_K, Q6_K, 151936),
+    "cfg3-q5": _mk("cfg3-q5", "Qwen3-8B linear stack, Q5_K_M", 4096, 4096, 1024, 12288, 36, Q5_K, Q6_K, 151936),
+    "cfg4-q5": _mk("cfg4-q5", "3B dense decoder linear stack, Q5_K_M", 2560, 2560, 640, 8192, 40, Q5_K, Q6_K),
+    "cfg4-q8": _mk("cfg4-q8", "3B dense decoder linear stack, Q8_0", 2560, 2560, 640, 8192, 40, Q8_0, Q8_0),
+    "cfg5": _mk("cfg5", "Qwen3-32B linear stack, Q4_K_M (+ Q6_K lm_head)", 5120, 8192, 1024, 25600, 64, Q4_K, Q6_K, 151936),
+}
