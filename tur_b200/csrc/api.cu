@@ -8,29 +8,8 @@
 #include <string>
 
 #include "../../include/turq.h"
+#include "handles.h"
 #include "turq_internal.h"
-
-struct turq_ctx {
-  int device = 0;
-  int sm_count = 0;
-  uint8_t* scratch = nullptr;  // activation planes / f16 operand for the current call
-  size_t scratch_bytes = 0;
-  uint8_t* io = nullptr;  // device staging for the host-buffer entry (x, y, bias)
-  size_t io_bytes = 0;
-  int* dev_status = nullptr;  // status word written by kernels with bounded waits
-  cudaStream_t own_stream = nullptr;
-  int64_t launches = 0;
-  std::string err;
-};
-
-struct turq_qtensor {
-  int device = 0;
-  int dtype = 0;
-  int64_t n_rows = 0, n_cols = 0;
-  size_t wire_bytes = 0;
-  uint8_t* tiles = nullptr;
-  size_t tile_bytes = 0;
-};
 
 namespace {
 
