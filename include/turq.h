@@ -131,6 +131,21 @@ int32_t turq_qmatmul(turq_ctx* ctx, const turq_qtensor* qt, const void* dev_x, i
 int32_t turq_qmatmul_host(turq_ctx* ctx, const turq_qtensor* qt, const float* host_x, int64_t m,
                           float* host_y, int32_t mode, const float* host_bias);
 
+/* Integer-scheme QMatMul for hosts that must not allocate device memory during a call
+ * (a process whose memory pool already owns the GPU, a plugin inside a foreign runtime).
+ * No counterpart in the reference. Same arguments and results as turq_qmatmul with
+ * TURQ_MODE_INT8_ACT, but the quantized activation planes live in a fixed buffer inside the
+ * library image (TURQ_STATIC_SCRATCH_BYTES on every GPU that loads the library) instead of
+ * the context's growable scratch: the call performs no cudaMalloc/cudaFree. Requests whose
+ * planes do not fit (about m * k * 1.2 bytes) fail with TURQ_E_LIMIT. All calls on a GPU
+ * share that buffer, so calls that can overlap on the GPU (different streams) race and must
+ * be ordered by the caller. The first call on each device looks up the buffer's device
+ * address; make that call before starting any stream capture. */
+#define TURQ_STATIC_SCRATCH_BYTES (4 << 20)
+int32_t turq_qmatmul_static(turq_ctx* ctx, const turq_qtensor* qt, const void* dev_x,
+                            int32_t x_dtype, int64_t m, float* dev_y, const float* dev_bias,
+                            void* stream);
+
 #ifdef __cplusplus
 }
 #endif
