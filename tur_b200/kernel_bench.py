@@ -1,0 +1,124 @@
+"""Per-kernel timing of the quantized-linear kernels on one GPU.
+
+  python -m tur_b200.kernel_bench --op qmatmul --dtype Q4_K --n 12288 --k 4096 --m 1
+
+Rotates through `--copies` distinct weight buffers (default: enough to exceed L2 several
+times) so every launch streams from HBM, times `--iters` rounds with CUDA events on the
+launching stream and prints one JSON line with the average time per call, the algorithmic
+bytes (GGUF weight bytes + activations + outputs) and the implied bandwidth / flop rate.
+Small `--copies/--iters` values make it a suitable target for an `ncu` capture.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import numpy as np
+import torch
+
+from . import GgmlDType, Mode, QMatMul, QTensor, context
+from .workloads import BLOCK, SEED
+
+NAMES = {"Q8_0": 8, "Q4_K": 12, "Q5_K": 13, "Q6_K": 14}
+
+
+def random_blocks(dtype: int, n: int, k: int, seed: int, device) -> torch.Tensor:
+    """Valid wire blocks with plausible scales, generated on the GPU (timing input only)."""
+    be, bb = BLOCK[dtype]
+    g = torch.Generator(device=device).manual_seed(seed)
+    nb = n * (k // be)
+    raw = torch.randint(0, 256, (nb, bb), dtype=torch.uint8, device=device, generator=g)
+    scale = (torch.rand((nb,), device=device, generator=g) * 0.004 + 0.0005).to(torch.float16).view(torch.uint8).reshape(nb, 2)
+    if dtype == 14:
+        raw[:, 208:210] = scale
+    else:
+        raw[:, 0:2] = scale
+        if dtype in (12, 13):
+            raw[:, 2:4] = scale
+    return raw.reshape(-1)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", default="qmatmul", choices=["qmatmul", "dequantize"])
+    ap.add_argument("--dtype", default="Q4_K", choices=sorted(NAMES))
+    ap.add_argument("--n", type=int, default=12288)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--m", type=int, default=1)
+    ap.add_argument("--mode", default="INT8_ACT", choices=["AUTO", "INT8_ACT", "EXACT_F32", "TENSOR_CORE"])
+    ap.add_argument("--xdtype", default="f32", choices=["f32", "bf16"])
+    ap.add_argument("--copies", type=int, default=0)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no-graph", action="store_true")
+    args = ap.parse_args()
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    dt = NAMES[args.dtype]
+    be, bb = BLOCK[dt]
+    wbytes = args.n * (args.k // be) * bb
+    copies = args.copies or max(2, min(64, int(4 * 126e6 / wbytes) + 1))
+    ws = []
+    for i in range(copies):
+        blocks = random_blocks(dt, args.n, args.k, SEED + i, dev)
+        ws.append(QMatMul.from_arc(QTensor.new(blocks, GgmlDType(dt), (args.n, args.k))))
+        del blocks
+    rng = np.random.default_rng(SEED + 10**6 + args.m)
+    x = torch.from_numpy(rng.standard_normal((args.m, args.k), dtype=np.float32)).to(dev)
+    if args.xdtype == "bf16":
+        x = x.to(torch.bfloat16)
+    mode = Mode[args.mode]
+    ctx = context(0)
+    if args.op == "qmatmul":
+        y = torch.empty((args.m, args.n), dtype=torch.float32, device=dev)
+
+        def call(w):
+            w.forward(x, mode=mode, out=y)
+        alg_bytes = wbytes + args.m * args.k * x.element_size() + args.m * args.n * 4
+        flops = 2.0 * args.m * args.n * args.k
+    else:
+        out = torch.empty((args.n, args.k), dtype=torch.float32, device=dev)
+
+        def call(w):
+            ctx.check(__import__("tur_b200")._lib.load().turq_dequantize(
+                ctx.handle, w.qtensor._h, 0, out.data_ptr(), torch.cuda.current_stream().cuda_stream))
+        alg_bytes = wbytes + args.n * args.k * 4
+        flops = 0.0
+
+    def one_round():
+        for w in ws:
+            call(w)
+
+    for _ in range(args.warmup):
+        one_round()
+    torch.cuda.synchronize()
+    l0 = ctx.launch_count()
+    runner = one_round
+    if not args.no_graph:
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side), torch.cuda.graph(graph, stream=side):
+            one_round()
+        runner = graph.replay
+        runner()
+    launches_per_call = (ctx.launch_count() - l0) / copies if not args.no_graph else None
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.iters):
+        runner()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (args.iters * copies)
+    print(json.dumps({
+        "op": args.op, "dtype": args.dtype, "n": args.n, "k": args.k, "m": args.m, "mode": args.mode,
+        "copies": copies, "iters": args.iters, "us_per_call": us, "launches_per_call": launches_per_call,
+        "algorithmic_bytes": alg_bytes, "GBps": alg_bytes / us / 1e3, "weight_GBps": wbytes / us / 1e3,
+        "TFLOPs": flops / us / 1e6,
+    }))
+
+
+if __name__ == "__main__":
+    main()
