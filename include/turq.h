@@ -82,6 +82,10 @@ size_t turq_row_bytes(int32_t dtype, int64_t k);
 int32_t turq_ctx_create(int32_t device, turq_ctx** out);
 int32_t turq_ctx_destroy(turq_ctx* ctx);
 const char* turq_last_error(const turq_ctx* ctx);
+/* Kernels never trap: a device-side wait that runs out (mbarrier, cross-CTA hand-over) stops
+ * the kernel and records a status word. This call synchronizes `stream`, returns TURQ_OK or
+ * the recorded status (TURQ_E_TIMEOUT) and clears it. */
+int32_t turq_ctx_poll_status(turq_ctx* ctx, void* stream);
 /* Number of kernels this context has launched so far (bookkeeping for benchmarks). */
 int64_t turq_ctx_launch_count(const turq_ctx* ctx);
 

@@ -205,6 +205,10 @@ def test_shards_reassemble_the_unsharded_result(tq, dt):
                           bits(oracle.dequantize(dt, w, k)[:, 768:1024]))
 
 
+def test_no_kernel_gave_up_a_wait(tq):
+    tq.context().poll_status()
+
+
 def test_error_paths_return_status_not_crash(tq):
     w = make_weight(oracle.Q4_K, 16, 256, 1)
     with pytest.raises(tq.TurqError) as e:

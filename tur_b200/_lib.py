@@ -24,6 +24,7 @@ SIGNATURES = {
     "turq_ctx_destroy": (c_i32, [c_vp]),
     "turq_last_error": (ctypes.c_char_p, [c_vp]),
     "turq_ctx_launch_count": (c_i64, [c_vp]),
+    "turq_ctx_poll_status": (c_i32, [c_vp, c_vp]),
     "turq_qtensor_from_host": (c_i32, [c_vp, c_i32, c_i64, c_i64, c_vp, c_sz, PP]),
     "turq_qtensor_from_device": (c_i32, [c_vp, c_i32, c_i64, c_i64, c_vp, c_sz, c_vp, PP]),
     "turq_qtensor_slice_rows": (c_i32, [c_vp, c_vp, c_i64, c_i64, PP]),

@@ -6,7 +6,7 @@
 // Q8_K (GGML reference semantics): the element of largest magnitude (first one on ties)
 // maps to -128 before the clamp at 127, rounding is to nearest-even, d = 1/iscale.
 // Q8_0: d = amax/127 in f32, stored as f16; q = round-half-away(x * (1/d)).
-#include "device_utils.cuh"
+#include "actquant.cuh"
 #include "turq_internal.h"
 
 namespace turq {
@@ -36,23 +36,6 @@ struct ActOut {
   int16_t* bs32;
 };
 
-__device__ __forceinline__ void load8(const void* x, int is_bf16, int64_t idx, float (&v)[8]) {
-  if (is_bf16) {
-    uint4 r = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(x) + idx);
-    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-    for (int e = 0; e < 4; e++) {
-      v[2 * e] = __uint_as_float(w[e] << 16);
-      v[2 * e + 1] = __uint_as_float(w[e] & 0xFFFF0000u);
-    }
-  } else {
-    const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + idx);
-    float4 a = p[0], b = p[1];
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-  }
-}
-
 // One warp per 256-element block: lane owns elements 8*lane .. 8*lane+7.
 __global__ void __launch_bounds__(128) quant_q8k_kernel(const void* __restrict__ x, int is_bf16, int64_t m,
                                                         int64_t k, ActOut out) {
@@ -65,38 +48,10 @@ __global__ void __launch_bounds__(128) quant_q8k_kernel(const void* __restrict__
     int64_t row = wb / nblk, blk = wb - row * nblk;
     float v[8];
     load8(x, is_bf16, row * k + blk * 256 + lane * 8, v);
-    float amax = 0.f, mx = 0.f;
-    int idx = lane * 8;
-#pragma unroll
-    for (int e = 0; e < 8; e++) {
-      float a = fabsf(v[e]);
-      if (a > amax) { amax = a; mx = v[e]; idx = lane * 8 + e; }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      float a2 = __shfl_xor_sync(0xFFFFFFFFu, amax, o);
-      float m2 = __shfl_xor_sync(0xFFFFFFFFu, mx, o);
-      int i2 = __shfl_xor_sync(0xFFFFFFFFu, idx, o);
-      if (a2 > amax || (a2 == amax && i2 < idx)) { amax = a2; mx = m2; idx = i2; }
-    }
-    int q[8];
-    float d = 0.f;
-    if (amax == 0.f) {
-#pragma unroll
-      for (int e = 0; e < 8; e++) q[e] = 0;
-    } else {
-      float iscale = __fdiv_rn(-128.f, mx);
-#pragma unroll
-      for (int e = 0; e < 8; e++) q[e] = min(127, __float2int_rn(__fmul_rn(iscale, v[e])));
-      d = __fdiv_rn(1.f, iscale);
-    }
-    int s8 = 0;
-#pragma unroll
-    for (int e = 0; e < 8; e++) s8 += q[e];
-    int s16 = s8 + __shfl_xor_sync(0xFFFFFFFFu, s8, 1);
-    int s32 = s16 + __shfl_xor_sync(0xFFFFFFFFu, s16, 2);
-    uint32_t w0 = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((uint32_t)(q[3] & 0xFF) << 24);
-    uint32_t w1 = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | ((uint32_t)(q[7] & 0xFF) << 24);
+    uint32_t w0, w1;
+    float d;
+    int s16, s32;
+    quant_block_q8k(v, lane, w0, w1, d, s16, s32);
     if (out.wire) {
       uint8_t* b = out.wire + wb * 292;  // 292 = 4 * 73: every field stays 4-byte aligned
       if (lane == 0) *reinterpret_cast<float*>(b) = d;
@@ -133,19 +88,9 @@ __global__ void __launch_bounds__(128) quant_q8_0_kernel(const void* __restrict_
 #pragma unroll
       for (int e = 0; e < 8; e++) v[e] = 0.f;
     }
-    float amax = 0.f;
-#pragma unroll
-    for (int e = 0; e < 8; e++) amax = fmaxf(amax, fabsf(v[e]));
-    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
-    float d = __fdiv_rn(amax, 127.f);
-    float id = d == 0.f ? 0.f : __fdiv_rn(1.f, d);
-    int q[8];
-#pragma unroll
-    for (int e = 0; e < 8; e++) q[e] = (int)roundf(__fmul_rn(v[e], id));
-    __half dh = __float2half_rn(d);
-    uint32_t w0 = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((uint32_t)(q[3] & 0xFF) << 24);
-    uint32_t w1 = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | ((uint32_t)(q[7] & 0xFF) << 24);
+    uint32_t w0, w1;
+    __half dh;
+    quant_block_q8_0(v, w0, w1, dh);
     if (!live) continue;
     if (out.wire) {
       uint8_t* b = out.wire + (row * nblk + blk) * 34;  // 2-byte aligned only

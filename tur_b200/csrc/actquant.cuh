@@ -1,0 +1,88 @@
+// Warp-level activation quantization shared by the stand-alone kernels and the GEMV that
+// quantizes its activations in shared memory. Same arithmetic in both places, so the wire
+// blocks of the public entry and the planes the GEMV consumes always agree.
+#pragma once
+#include "device_utils.cuh"
+
+namespace turq {
+
+__device__ __forceinline__ void load8(const void* x, int is_bf16, int64_t idx, float (&v)[8]) {
+  if (is_bf16) {
+    uint4 r = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(x) + idx);
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+      v[2 * e] = __uint_as_float(w[e] << 16);
+      v[2 * e + 1] = __uint_as_float(w[e] & 0xFFFF0000u);
+    }
+  } else {
+    const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + idx);
+    float4 a = p[0], b = p[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+}
+
+__device__ __forceinline__ uint32_t pack4(const int* q) {
+  return (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((uint32_t)(q[3] & 0xFF) << 24);
+}
+
+// Q8_K block of 256 values held 8 per lane (lane owns elements 8*lane .. 8*lane+7).
+// GGML reference semantics: the element of largest magnitude (first on ties) maps to -128
+// before the clamp at 127, round-to-nearest-even, d = 1/iscale. Returns the packed quants
+// (w0, w1), the block scale d and the sums of this lane's aligned group of 16 and of 32.
+__device__ __forceinline__ void quant_block_q8k(const float (&v)[8], int lane, uint32_t& w0, uint32_t& w1, float& d,
+                                                int& s16, int& s32) {
+  float amax = 0.f, mx = 0.f;
+  int idx = lane * 8;
+#pragma unroll
+  for (int e = 0; e < 8; e++) {
+    float a = fabsf(v[e]);
+    if (a > amax) { amax = a; mx = v[e]; idx = lane * 8 + e; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float a2 = __shfl_xor_sync(0xFFFFFFFFu, amax, o);
+    float m2 = __shfl_xor_sync(0xFFFFFFFFu, mx, o);
+    int i2 = __shfl_xor_sync(0xFFFFFFFFu, idx, o);
+    if (a2 > amax || (a2 == amax && i2 < idx)) { amax = a2; mx = m2; idx = i2; }
+  }
+  int q[8];
+  d = 0.f;
+  if (amax == 0.f) {
+#pragma unroll
+    for (int e = 0; e < 8; e++) q[e] = 0;
+  } else {
+    float iscale = __fdiv_rn(-128.f, mx);
+#pragma unroll
+    for (int e = 0; e < 8; e++) q[e] = min(127, __float2int_rn(__fmul_rn(iscale, v[e])));
+    d = __fdiv_rn(1.f, iscale);
+  }
+  int s8 = 0;
+#pragma unroll
+  for (int e = 0; e < 8; e++) s8 += q[e];
+  s16 = s8 + __shfl_xor_sync(0xFFFFFFFFu, s8, 1);
+  s32 = s16 + __shfl_xor_sync(0xFFFFFFFFu, s16, 2);
+  w0 = pack4(q);
+  w1 = pack4(q + 4);
+}
+
+// Q8_0 block of 32 values held 8 per lane by 4 consecutive lanes: d = amax/127 in f32,
+// stored as f16; q = round-half-away(x * (1/d)).
+__device__ __forceinline__ void quant_block_q8_0(const float (&v)[8], uint32_t& w0, uint32_t& w1, __half& dh) {
+  float amax = 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; e++) amax = fmaxf(amax, fabsf(v[e]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+  float d = __fdiv_rn(amax, 127.f);
+  float id = d == 0.f ? 0.f : __fdiv_rn(1.f, d);
+  int q[8];
+#pragma unroll
+  for (int e = 0; e < 8; e++) q[e] = (int)roundf(__fmul_rn(v[e], id));
+  dh = __float2half_rn(d);
+  w0 = pack4(q);
+  w1 = pack4(q + 4);
+}
+
+}  // namespace turq

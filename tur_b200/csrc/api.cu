@@ -140,6 +140,13 @@ int32_t turq_ctx_create(int32_t device, turq_ctx** out) {
     return TURQ_E_CUDA;
   }
   ctx->sm_count = prop.multiProcessorCount;
+  const size_t ws_bytes = turq::gemv_workspace_bytes(ctx->sm_count);
+  if (cudaMalloc(reinterpret_cast<void**>(&ctx->gemv_ws), ws_bytes) != cudaSuccess ||
+      cudaMemset(ctx->gemv_ws, 0, ws_bytes) != cudaSuccess) {
+    cudaGetLastError();
+    turq_ctx_destroy(ctx);
+    return TURQ_E_CUDA;
+  }
   int32_t st = ensure(ctx, &ctx->scratch, &ctx->scratch_bytes, (size_t)8 << 20);
   if (st != TURQ_OK) {
     delete ctx;
@@ -156,6 +163,7 @@ int32_t turq_ctx_destroy(turq_ctx* ctx) {
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->io) cudaFree(ctx->io);
   if (ctx->dev_status) cudaFree(ctx->dev_status);
+  if (ctx->gemv_ws) cudaFree(ctx->gemv_ws);
   if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
   delete ctx;
   return TURQ_OK;
@@ -163,6 +171,21 @@ int32_t turq_ctx_destroy(turq_ctx* ctx) {
 
 const char* turq_last_error(const turq_ctx* ctx) { return ctx ? ctx->err.c_str() : "null context"; }
 int64_t turq_ctx_launch_count(const turq_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+int32_t turq_ctx_poll_status(turq_ctx* ctx, void* stream) {
+  if (!ctx) return TURQ_E_INVALID_ARG;
+  TQ_CUDA(ctx, cudaSetDevice(ctx->device));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int st = 0;
+  TQ_CUDA(ctx, cudaMemcpyAsync(&st, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost, s));
+  TQ_CUDA(ctx, cudaStreamSynchronize(s));
+  if (st != 0) {
+    TQ_CUDA(ctx, cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), s));
+    TQ_CUDA(ctx, cudaStreamSynchronize(s));
+    return fail(ctx, st, "a kernel gave up a bounded device-side wait (status %d)", st);
+  }
+  return TURQ_OK;
+}
 
 int32_t turq_qtensor_from_device(turq_ctx* ctx, int32_t dtype, int64_t n_rows, int64_t n_cols,
                                  const void* dev_blocks, size_t nbytes, void* stream, turq_qtensor** out) {
@@ -325,10 +348,8 @@ int32_t turq_qmatmul(turq_ctx* ctx, const turq_qtensor* qt, const void* dev_x, i
     turq::ActPackPlan plan = turq::plan_act_pack(fmt, m, k);
     int32_t st = ensure(ctx, &ctx->scratch, &ctx->scratch_bytes, plan.total);
     if (st != TURQ_OK) return st;
-    e = turq::launch_quantize_act_pack(fmt, dev_x, x_dtype, m, k, ctx->scratch, s);
-    launches++;
-    if (e == cudaSuccess)
-      e = turq::launch_gemv_int8(qt->dtype, qt->tiles, qt->n_rows, k, ctx->scratch, m, dev_y, dev_bias, ctx->sm_count, s, &launches);
+    e = turq::launch_gemv_int8(qt->dtype, qt->tiles, qt->n_rows, k, dev_x, x_dtype, ctx->scratch, m, dev_y, dev_bias,
+                               ctx->gemv_ws, ctx->dev_status, ctx->sm_count, s, &launches);
   } else if (mode == TURQ_MODE_EXACT_F32) {
     e = turq::launch_gemv_f32(qt->dtype, qt->tiles, qt->n_rows, k, dev_x, x_dtype, m, dev_y, dev_bias, ctx->sm_count, s, &launches);
   } else if (mode == TURQ_MODE_TENSOR_CORE) {
@@ -362,8 +383,7 @@ int32_t turq_qmatmul_host(turq_ctx* ctx, const turq_qtensor* qt, const float* ho
   st = turq_qmatmul(ctx, qt, dx, TURQ_F32, m, dy, mode, db, s);
   if (st != TURQ_OK) return st;
   TQ_CUDA(ctx, cudaMemcpyAsync(host_y, dy, (size_t)m * qt->n_rows * 4, cudaMemcpyDeviceToHost, s));
-  TQ_CUDA(ctx, cudaStreamSynchronize(s));
-  return TURQ_OK;
+  return turq_ctx_poll_status(ctx, s);
 }
 
 }  // extern "C"

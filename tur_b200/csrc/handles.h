@@ -14,6 +14,7 @@ struct turq_ctx {
   uint8_t* io = nullptr;  // device staging for the host-buffer entry (x, y, bias)
   size_t io_bytes = 0;
   int* dev_status = nullptr;  // status word written by kernels with bounded waits
+  uint8_t* gemv_ws = nullptr;  // split row-tile workspace of the streaming GEMV (zeroed once)
   cudaStream_t own_stream = nullptr;
   int64_t launches = 0;
   std::string err;

@@ -21,9 +21,10 @@
 
 namespace {
 
-// Quantized activation planes of the call in flight. Nothing in it has to start at zero:
-// every plane element a GEMV launch reads is written first by the activation-quantization
-// launch of the same call, so the previous call's contents are never observed.
+// Quantized activation planes of the call in flight, followed by the GEMV's workspace for
+// row-tiles split between CTAs. The planes need no clearing (every element read is written
+// first by the same call); the workspace's ready flags must start at zero and are cleared by
+// each call before its kernels run.
 static __device__ __align__(256) uint8_t g_static_scratch[TURQ_STATIC_SCRATCH_BYTES];
 
 constexpr int kMaxDevices = 64;
@@ -69,7 +70,9 @@ extern "C" int32_t turq_qmatmul_static(turq_ctx* ctx, const turq_qtensor* qt, co
   const int64_t k = qt->n_cols;
   const int fmt = qt->dtype == TURQ_Q8_0 ? TQ_Q8_0 : TQ_Q8_K;
   const turq::ActPackPlan plan = turq::plan_act_pack(fmt, m, k);
-  if (plan.total > (size_t)TURQ_STATIC_SCRATCH_BYTES) {
+  // the tail of the array is the GEMV's split row-tile workspace (partial sums + ready flags)
+  const size_t ws_bytes = (turq::gemv_workspace_bytes(ctx->sm_count) + 255) & ~(size_t)255;
+  if (plan.total + ws_bytes > (size_t)TURQ_STATIC_SCRATCH_BYTES) {
     char buf[200];
     snprintf(buf, sizeof(buf), "m=%lld x k=%lld needs %zu bytes of activation planes, the static buffer holds %d",
              (long long)m, (long long)k, plan.total, (int)TURQ_STATIC_SCRATCH_BYTES);
@@ -80,12 +83,13 @@ extern "C" int32_t turq_qmatmul_static(turq_ctx* ctx, const turq_qtensor* qt, co
   if (e == cudaSuccess) e = cudaSetDevice(ctx->device);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   int launches = 0;
-  if (e == cudaSuccess) {
-    e = turq::launch_quantize_act_pack(fmt, dev_x, x_dtype, m, k, scratch, s);
-    launches++;
-  }
+  uint8_t* ws = scratch + TURQ_STATIC_SCRATCH_BYTES - ws_bytes;
+  // The ready flags must read zero at kernel start. A completed call leaves them zero, but the
+  // array is shared and outlives failed calls, so they are cleared every time (stream-ordered).
+  if (e == cudaSuccess) e = cudaMemsetAsync(ws, 0, ws_bytes, s);
   if (e == cudaSuccess)
-    e = turq::launch_gemv_int8(qt->dtype, qt->tiles, qt->n_rows, k, scratch, m, dev_y, dev_bias, ctx->sm_count, s, &launches);
+    e = turq::launch_gemv_int8(qt->dtype, qt->tiles, qt->n_rows, k, dev_x, x_dtype, scratch, m, dev_y, dev_bias, ws,
+                               ctx->dev_status, ctx->sm_count, s, &launches);
   ctx->launches += launches;
   if (e != cudaSuccess) return fail(ctx, TURQ_E_CUDA, cudaGetErrorString(e));
   return TURQ_OK;

@@ -7,18 +7,6 @@
 
 namespace turq {
 
-// Quantized activations as the GEMV kernels consume them (planes inside one scratch buffer).
-//   qs    int8  [m][k]          element order = input order
-//   dsc   f32   [m][k/bs]       bs = 256 (Q8_K) or 32 (Q8_0; value is the f16-rounded scale)
-//   bs16  int16 [m][k/16]       Q8_K only: sums of 16 consecutive qs
-//   bs32  int16 [m][k/32]       Q8_K only: sums of 32 consecutive qs
-struct ActPack {
-  const int8_t* qs;
-  const float* dsc;
-  const int16_t* bs16;
-  const int16_t* bs32;
-};
-
 struct ActPackPlan {
   size_t off_qs, off_dsc, off_bs16, off_bs32, total;
 };
@@ -42,10 +30,15 @@ cudaError_t launch_quantize_act_wire(int fmt, const void* x, int x_dtype, int64_
 cudaError_t launch_quantize_act_pack(int fmt, const void* x, int x_dtype, int64_t m, int64_t k,
                                      uint8_t* scratch, cudaStream_t s);
 
-// y[m, n] = act . W^T in the integer scheme; m is processed in groups of up to 16 rows.
-cudaError_t launch_gemv_int8(int dtype, const uint8_t* tiles, int64_t n_rows, int64_t k,
-                             const uint8_t* act_scratch, int64_t m, float* y, const float* bias,
-                             int sm_count, cudaStream_t s, int* launches);
+// y[m, n] = quantize(x) . W^T in the integer scheme (gemv_stream.cu). Quantizes the
+// activations inside the kernel when they are small, else into `act_scratch` (which must hold
+// plan_act_pack(fmt, m, k).total bytes) with a preceding launch. `workspace` holds
+// gemv_workspace_bytes(sm_count) bytes, zero-initialised once; `status` is a device int.
+size_t gemv_workspace_bytes(int ctas);
+bool gemv_int8_fuses_act(int dtype, int64_t m, int64_t k);
+cudaError_t launch_gemv_int8(int dtype, const uint8_t* tiles, int64_t n_rows, int64_t k, const void* x,
+                             int x_dtype, uint8_t* act_scratch, int64_t m, float* y, const float* bias,
+                             uint8_t* workspace, int* status, int sm_count, cudaStream_t s, int* launches);
 // y[m, n] = x . dequant(W)^T with f32 FMAs on exact f32 weights.
 cudaError_t launch_gemv_f32(int dtype, const uint8_t* tiles, int64_t n_rows, int64_t k,
                             const void* x, int x_dtype, int64_t m, float* y, const float* bias,

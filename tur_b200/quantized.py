@@ -71,6 +71,10 @@ class _Context:
         if st != 0:
             raise TurqError(st, _lib.load().turq_last_error(self.handle).decode())
 
+    def poll_status(self) -> None:
+        """Synchronizes the current stream and raises if a kernel gave up a bounded wait."""
+        self.check(_lib.load().turq_ctx_poll_status(self.handle, _stream_ptr(self.device)))
+
     def launch_count(self) -> int:
         return int(_lib.load().turq_ctx_launch_count(self.handle))
 
