@@ -33,20 +33,21 @@ __device__ __forceinline__ uint32_t pack4(const int* q) {
 // (w0, w1), the block scale d and the sums of this lane's aligned group of 16 and of 32.
 __device__ __forceinline__ void quant_block_q8k(const float (&v)[8], int lane, uint32_t& w0, uint32_t& w1, float& d,
                                                 int& s16, int& s32) {
-  float amax = 0.f, mx = 0.f;
-  int idx = lane * 8;
+  // arg-max of |v| over the block with "first index wins" on ties: per-lane scan, then one
+  // warp-wide integer max on the float bit patterns (monotonic for non-negative floats) and a
+  // ballot to find the lowest lane that holds it.
+  uint32_t umax = 0;
+  float mx = 0.f;
 #pragma unroll
   for (int e = 0; e < 8; e++) {
-    float a = fabsf(v[e]);
-    if (a > amax) { amax = a; mx = v[e]; idx = lane * 8 + e; }
+    const uint32_t ua = __float_as_uint(fabsf(v[e]));
+    if (ua > umax) { umax = ua; mx = v[e]; }
   }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    float a2 = __shfl_xor_sync(0xFFFFFFFFu, amax, o);
-    float m2 = __shfl_xor_sync(0xFFFFFFFFu, mx, o);
-    int i2 = __shfl_xor_sync(0xFFFFFFFFu, idx, o);
-    if (a2 > amax || (a2 == amax && i2 < idx)) { amax = a2; mx = m2; idx = i2; }
-  }
+  const uint32_t wmax = __reduce_max_sync(0xFFFFFFFFu, umax);
+  const uint32_t holders = __ballot_sync(0xFFFFFFFFu, umax == wmax);
+  mx = __shfl_sync(0xFFFFFFFFu, mx, __ffs(holders) - 1);
+  const float amax = __uint_as_float(wmax);
+  (void)lane;
   int q[8];
   d = 0.f;
   if (amax == 0.f) {

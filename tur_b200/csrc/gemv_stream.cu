@@ -1,10 +1,14 @@
 // Decode-sized QMatMul::forward in the integer scheme, built to stay HBM-bound on B200.
 //
-//   * One persistent CTA per SM: a producer warp streams device tiles (contiguous bytes)
-//     into a shared-memory ring with bulk async copies (cp.async.bulk, no multicast) that
-//     complete on mbarriers; 16 consumer warps each take one tile of a stage, read their
+//   * Persistent CTAs, two or three per SM: a producer warp streams device tiles (contiguous
+//     bytes) into a shared-memory ring with bulk async copies (cp.async.bulk, no multicast)
+//     that complete on mbarriers; 8 consumer warps each take one tile of a stage, read their
 //     fragment chunks from shared memory with 128-bit loads and run the integer MMAs of
-//     gemv_tile.cuh. The bytes in flight per SM are set by the ring, not by registers.
+//     gemv_tile.cuh; an epilogue warp adds the consumers' partial sums and writes outputs, so
+//     consumers never meet at a CTA-wide barrier. The bytes in flight per SM are set by the
+//     ring, not by registers.
+//   * Programmatic dependent launch: the weight stream of a launch starts while the preceding
+//     kernel of the stream is still draining; only activations and outputs wait for it.
 //   * Work is split evenly over the CTAs in units of tiles (not rows): a CTA owns a
 //     contiguous tile range that may start or end inside a row-tile. The partial sums of a
 //     split row-tile go through a small global workspace and are added in CTA order by the
@@ -24,7 +28,7 @@
 
 namespace turq {
 
-constexpr int NW = 16;                 // consumer warps
+constexpr int NW = 8;                  // consumer warps
 constexpr int THREADS = (NW + 2) * 32; // + producer warp + epilogue warp
 constexpr int RED_SLOTS = 2;           // partial-sum hand-over buffers between consumers and epilogue
 constexpr int MAX_STAGES = 6;
@@ -71,29 +75,47 @@ __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, u
 }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory"); }
 
+#ifdef TURQ_TRACE
+// Debug timeline: per CTA, global-timer stamps at a few points (built only with -DTURQ_TRACE).
+__device__ unsigned long long g_trace[1024 * 8];
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+#define TRACE(slot) do { if (lane == 0) g_trace[(blockIdx.x & 1023) * 8 + (slot)] = gtime(); } while (0)
+extern "C" int turq_debug_read_trace(unsigned long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_trace, sizeof(unsigned long long) * n);
+}
+#else
+#define TRACE(slot) do { } while (0)
+#endif
+
+struct SmemPlan {
+  int ring, act_qs, act_dsc, act_bs16, act_bs32, red, bars, total, qs_stride;
+};
+
 struct StreamArgs {
   const uint8_t* tiles;
   int64_t n_rows;
   int row_tiles, ktiles, k;
-  const void* x;        // activations of the pass (row m_base first), f32 or bf16   [FUSED]
+  int KU;               // units (tiles; groups of 4 tiles for Q8_0) per row-tile
+  int split_q, split_r; // CTA b owns units [b*q + min(b,r), (b+1)*q + min(b+1,r))
+  const void* x;        // activations of the pass (first row of the pass), f32 or bf16   [FUSED]
   int x_is_bf16;
-  ActPack gact;         // planes in global scratch, already offset to row m_base     [!FUSED]
+  ActPack gact;         // planes in global scratch, already offset to the pass's first row [!FUSED]
   int rows;             // valid activation rows in this pass (<= 8 * MG)
-  float* y;             // output, already offset to row m_base
+  float* y;             // output, already offset to the pass's first row
   const float* bias;
   float* partial;       // [grid][MG * 128]: partial sums of a CTA's leading split row-tile
   int* flags;           // [grid], all zero between launches
   int* status;
   int stages;
   int stage_bytes;
+  SmemPlan sp;
 };
 
-struct SmemPlan {
-  int ring, act_qs, act_dsc, act_bs16, act_bs32, red, bars, total, qs_stride;
-};
-
-__host__ __device__ inline SmemPlan plan_smem(int dtype, int mg, bool fused, int rows_cap, int k, int stages,
-                                               int stage_bytes) {
+inline SmemPlan plan_smem(int dtype, int mg, bool fused, int rows_cap, int k, int stages, int stage_bytes) {
   auto up = [](int v) { return (v + 127) & ~127; };
   SmemPlan p{};
   p.ring = 0;
@@ -112,34 +134,64 @@ __host__ __device__ inline SmemPlan plan_smem(int dtype, int mg, bool fused, int
   p.red = off;
   off = up(off + RED_SLOTS * NW * mg * 128 * 4);
   p.bars = off;
-  off += (2 * MAX_STAGES + 2 * RED_SLOTS) * 8 + 16;
+  off += (MAX_STAGES * NW + MAX_STAGES + 2 * RED_SLOTS) * 8 + 16;
   p.total = off;
   return p;
 }
 
+// Walks a CTA's unit range stage by stage (a stage never crosses a row-tile); identical in
+// the producer, the consumers and the epilogue warp. No divisions on the way.
+struct StageWalk {
+  int rt, ku, left, KU;
+  __device__ __forceinline__ void init(int u0, int u1, int ku_) {
+    KU = ku_;
+    rt = u0 / KU;
+    ku = u0 - rt * KU;
+    left = u1 - u0;
+  }
+  __device__ __forceinline__ bool done() const { return left <= 0; }
+  __device__ __forceinline__ int count() const {
+    int n = KU - ku;
+    if (n > NW) n = NW;
+    if (n > left) n = left;
+    return n;
+  }
+  // advances past n units; returns true when that closed a segment (row-tile or range end)
+  __device__ __forceinline__ bool advance(int n) {
+    ku += n;
+    left -= n;
+    const bool closed = ku == KU || left == 0;
+    return closed;
+  }
+  __device__ __forceinline__ void next_row_if_needed() {
+    if (ku == KU) { ku = 0; rt++; }
+  }
+};
+
 template <int DT, int MG, bool FUSED>
-__global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const StreamArgs a) {
+__global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(const __grid_constant__ StreamArgs a) {
   constexpr int TB = TileGeom<DT>::BYTES;
   constexpr int GROUP = TileGeom<DT>::GROUP;
   constexpr int UNIT_BYTES = TB * GROUP;
   extern __shared__ __align__(128) uint8_t smem[];
-  const SmemPlan sp = plan_smem(DT, MG, FUSED, a.rows, a.k, a.stages, a.stage_bytes);
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + sp.bars);
-  uint64_t* empty = full + MAX_STAGES;
+  const SmemPlan& sp = a.sp;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + sp.bars);  // [stage][consumer warp]: one tile each
+  uint64_t* empty = full + MAX_STAGES * NW;
   uint64_t* red_full = empty + MAX_STAGES;
   uint64_t* red_empty = red_full + RED_SLOTS;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(red_empty + RED_SLOTS);
   float* red = reinterpret_cast<float*>(smem + sp.red);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int KU = (a.ktiles + GROUP - 1) / GROUP;  // units per row-tile
-  const int64_t T = (int64_t)a.row_tiles * KU;
-  const int64_t G = gridDim.x, b = blockIdx.x;
-  const int64_t u0 = (b * T) / G, u1 = ((b + 1) * T) / G;
+  if (warp == 0) TRACE(0);
+  const int KU = a.KU;
+  const int G = gridDim.x, b = blockIdx.x;
+  auto start_of = [&](int bb) { return bb * a.split_q + (bb < a.split_r ? bb : a.split_r); };
+  const int u0 = start_of(b), u1 = start_of(b + 1);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < a.stages; s++) {
-      mbar_init(&full[s], 1);
+      for (int w = 0; w < NW; w++) mbar_init(&full[s * NW + w], 1);
       mbar_init(&empty[s], NW);
     }
     for (int s = 0; s < RED_SLOTS; s++) {
@@ -150,33 +202,44 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const StreamArg
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  // Programmatic dependent launch: let the next kernel of the stream start its own prologue
+  // (and its weight stream) while this grid is still running. The weights never depend on a
+  // preceding kernel, so the producer warp starts at once; the warps that read activations or
+  // write outputs / the hand-over workspace first wait for the preceding grid to finish.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (warp == NW) {
     // ------------------------------------------------------------ producer warp
     if (lane == 0) {
-      int it = 0;
-      for (int64_t u = u0; u < u1;) {
-        const int64_t rt = u / KU;
-        const int ku = (int)(u - rt * KU);
-        int n = KU - ku;
-        if (n > NW) n = NW;
-        if ((int64_t)n > u1 - u) n = (int)(u1 - u);
-        const int slot = it % a.stages;
-        const uint32_t ph = (uint32_t)(it / a.stages) & 1u;
+      StageWalk w;
+      w.init(u0, u1, KU);
+      int slot = 0;
+      uint32_t ph = 0;
+      while (!w.done()) {
+        const int n = w.count();
         if (!mbar_wait(&empty[slot], ph ^ 1u, abort_flag)) break;
-        int ntiles = a.ktiles - ku * GROUP;
-        if (ntiles > n * GROUP) ntiles = n * GROUP;
-        const uint32_t bytes = (uint32_t)ntiles * TB;
-        mbar_expect_tx(&full[slot], bytes);
-        bulk_g2s(smem + sp.ring + slot * a.stage_bytes, a.tiles + (rt * a.ktiles + (int64_t)ku * GROUP) * TB, bytes,
-                 &full[slot]);
-        u += n;
-        it++;
+        // one copy per consumer warp (its tile, or its group of Q8_0 tiles), each completing on
+        // that warp's own barrier: a warp starts as soon as its bytes are there
+        const uint8_t* src = a.tiles + ((int64_t)w.rt * a.ktiles + (int64_t)w.ku * GROUP) * TB;
+        uint8_t* dst = smem + sp.ring + slot * a.stage_bytes;
+        for (int i = 0; i < n; i++) {
+          int nt = a.ktiles - (w.ku + i) * GROUP;
+          if (nt > GROUP) nt = GROUP;
+          const uint32_t bytes = (uint32_t)nt * TB;
+          mbar_expect_tx(&full[slot * NW + i], bytes);
+          bulk_g2s(dst + i * UNIT_BYTES, src + (size_t)i * UNIT_BYTES, bytes, &full[slot * NW + i]);
+        }
+        for (int i = n; i < NW; i++) mbar_arrive(&full[slot * NW + i]);  // unused this stage: keep phases in step
+        w.advance(n);
+        w.next_row_if_needed();
+        if (++slot == a.stages) { slot = 0; ph ^= 1u; }
       }
     }
   } else if (warp < NW) {
     // ------------------------------------------------------------ consumer warps
-    const int ctid = threadIdx.x;  // 0 .. NW*32-1
+    if (warp == 0) TRACE(1);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (warp == 0) TRACE(2);
     ActPack act = a.gact;
     if constexpr (FUSED) {
       int8_t* sqs = reinterpret_cast<int8_t*>(smem + sp.act_qs);
@@ -204,19 +267,41 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const StreamArg
           }
         }
       } else {
+        // Only the 256-element blocks this CTA's tiles touch: all of them when the range
+        // covers a whole row-tile, else the (cyclic) run starting at the first tile's block.
         const int nblk = a.k >> 8;
-        for (int wb = warp; wb < a.rows * nblk; wb += NW) {
-          const int row = wb / nblk, blk = wb - row * nblk;
-          float v[8];
-          load8(a.x, a.x_is_bf16, (int64_t)row * a.k + blk * 256 + lane * 8, v);
-          uint32_t w0, w1;
-          float d;
-          int s16, s32;
-          quant_block_q8k(v, lane, w0, w1, d, s16, s32);
-          *reinterpret_cast<uint2*>(sqs + row * sp.qs_stride + blk * 256 + lane * 8) = make_uint2(w0, w1);
-          if (lane == 0) sdsc[wb] = d;
-          if ((lane & 1) == 0) sb16[row * (a.k >> 4) + blk * 16 + (lane >> 1)] = (int16_t)s16;
-          if ((lane & 3) == 0) sb32[row * (a.k >> 5) + blk * 8 + (lane >> 2)] = (int16_t)s32;
+        const int span = u1 - u0 >= KU ? KU : u1 - u0;
+        const int first = u1 - u0 >= KU ? 0 : u0 % KU;
+        const int total = a.rows * span;
+        for (int base = warp; base < total; base += 2 * NW) {
+          // two blocks per pass with both loads in flight
+          const int i0 = base, i1 = base + NW;
+          const int row0 = i0 / span, row1 = i1 / span;
+          int blk0 = first + (i0 - row0 * span), blk1 = first + (i1 - row1 * span);
+          if (blk0 >= nblk) blk0 -= nblk;
+          if (blk1 >= nblk) blk1 -= nblk;
+          const bool has1 = i1 < total;
+          float v0[8], v1[8];
+          load8(a.x, a.x_is_bf16, (int64_t)row0 * a.k + blk0 * 256 + lane * 8, v0);
+          if (has1) {
+            load8(a.x, a.x_is_bf16, (int64_t)row1 * a.k + blk1 * 256 + lane * 8, v1);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 8; e++) v1[e] = 0.f;
+          }
+#pragma unroll
+          for (int h = 0; h < 2; h++) {
+            if (h == 1 && !has1) break;
+            const int row = h ? row1 : row0, blk = h ? blk1 : blk0;
+            uint32_t w0, w1;
+            float d;
+            int s16, s32;
+            quant_block_q8k(h ? v1 : v0, lane, w0, w1, d, s16, s32);
+            *reinterpret_cast<uint2*>(sqs + row * sp.qs_stride + blk * 256 + lane * 8) = make_uint2(w0, w1);
+            if (lane == 0) sdsc[row * nblk + blk] = d;
+            if ((lane & 1) == 0) sb16[row * (a.k >> 4) + blk * 16 + (lane >> 1)] = (int16_t)s16;
+            if ((lane & 3) == 0) sb32[row * (a.k >> 5) + blk * 8 + (lane >> 2)] = (int16_t)s32;
+          }
         }
       }
       act.qs = sqs;
@@ -226,6 +311,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const StreamArg
       act.qs_stride = sp.qs_stride;
       consumer_sync();
     }
+    if (warp == 0) TRACE(3);
 
     const int g = lane >> 2, c = lane & 3;
     float acc[MG][4];
@@ -233,36 +319,30 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const StreamArg
     for (int mg = 0; mg < MG; mg++)
 #pragma unroll
       for (int e = 0; e < 4; e++) acc[mg][e] = 0.f;
-    int it = 0, seg = 0;
-    bool ok = true;
-    for (int64_t u = u0; u < u1 && ok;) {
-      const int64_t rt = u / KU;
-      const int ku = (int)(u - rt * KU);
-      int n = KU - ku;
-      if (n > NW) n = NW;
-      if ((int64_t)n > u1 - u) n = (int)(u1 - u);
-      const int slot = it % a.stages;
-      const uint32_t ph = (uint32_t)(it / a.stages) & 1u;
-      ok = mbar_wait(&full[slot], ph, abort_flag);
-      if (!ok) break;
+    StageWalk w;
+    w.init(u0, u1, KU);
+    int slot = 0, rs = 0;
+    uint32_t ph = 0, rph = 0;
+    bool first = true;
+    while (!w.done()) {
+      const int n = w.count();
       if (warp < n) {
-        const int kt = (ku + warp) * GROUP;
+        if (!mbar_wait(&full[slot * NW + warp], ph, abort_flag)) break;
+        if (warp == 0 && first) TRACE(4);
+        first = false;
+        const int kt = (w.ku + warp) * GROUP;
         int left = a.ktiles - kt;
         if (left > GROUP) left = GROUP;
-        TileRegs<DT> r;
-        load_tile<DT, SharedLoader>(r, smem + sp.ring + slot * a.stage_bytes + warp * UNIT_BYTES, lane, left);
-        tile_mma<DT, MG>(r, lane, act, a.k, kt, a.rows, left, acc);
+        tile_mma<DT, MG>(smem + sp.ring + slot * a.stage_bytes + warp * UNIT_BYTES, lane, act, a.k, kt, a.rows, left, acc);
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(&empty[slot]);  // after the tile's registers have been consumed
-      u += n;
-      it++;
-      if (ku + n == KU || u == u1) {
-        // ---- segment of row-tile rt closed: hand this warp's partial sums to the epilogue warp
-        const int rs = seg % RED_SLOTS;
-        const uint32_t rph = (uint32_t)(seg / RED_SLOTS) & 1u;
-        ok = mbar_wait(&red_empty[rs], rph ^ 1u, abort_flag);
-        if (!ok) break;
+      if (lane == 0) mbar_arrive(&empty[slot]);  // after the tile's bytes have been consumed
+      if (++slot == a.stages) { slot = 0; ph ^= 1u; }
+      const bool closed = w.advance(n);
+      w.next_row_if_needed();
+      if (closed) {
+        // ---- segment closed: hand this warp's partial sums to the epilogue warp
+        if (!mbar_wait(&red_empty[rs], rph ^ 1u, abort_flag)) break;
         float* rw = red + ((rs * NW + warp) * MG) * 128;
 #pragma unroll
         for (int mg = 0; mg < MG; mg++) {
@@ -274,78 +354,97 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const StreamArg
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&red_full[rs]);
-        seg++;
+        if (++rs == RED_SLOTS) { rs = 0; rph ^= 1u; }
       }
     }
+    if (warp == 0) TRACE(5);
   } else {
     // ------------------------------------------------------------ epilogue warp
-    // Walks the same stage sequence to know where segments end; per segment adds the 16
-    // warps' partial sums in warp order and either writes y (the CTA owns the row-tile),
-    // or parks the sums in the workspace for the owner. The CTA holding the first tile of a
-    // row-tile owns it; later CTAs reach into it with the first tiles of their ranges.
-    int seg = 0;
-    int seg_ka = (int)(u0 % KU);
-    bool ok = true;
-    for (int64_t u = u0; u < u1 && ok;) {
-      const int64_t rt = u / KU;
-      const int ku = (int)(u - rt * KU);
-      int n = KU - ku;
-      if (n > NW) n = NW;
-      if ((int64_t)n > u1 - u) n = (int)(u1 - u);
-      u += n;
-      const int kb = ku + n;
-      if (kb != KU && u != u1) continue;
-      const int rs = seg % RED_SLOTS;
-      const uint32_t rph = (uint32_t)(seg / RED_SLOTS) & 1u;
-      ok = mbar_wait(&red_full[rs], rph, abort_flag);
-      if (!ok) break;
+    // Walks the same stage sequence to know where segments end; per segment adds the
+    // consumer warps' partial sums in warp order and either writes y (this CTA owns the
+    // row-tile) or parks the sums in the workspace for the owner. The CTA holding the first
+    // tile of a row-tile owns it; later CTAs reach into it with the first tiles of their
+    // ranges, so their sums are normally there long before the owner needs them.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    StageWalk w;
+    w.init(u0, u1, KU);
+    int seg_ka = w.ku;
+    int rs = 0;
+    uint32_t rph = 0;
+    while (!w.done()) {
+      const int n = w.count();
+      const int rt = w.rt;
+      const bool closed = w.advance(n);
+      const int kb = w.ku;
+      w.next_row_if_needed();
+      if (!closed) continue;
       const bool owner = seg_ka == 0;
       const bool whole = owner && kb == KU;
-      const int64_t rt_end = (rt + 1) * (int64_t)KU;
+      const int rt_end = (rt + 1) * KU;
       const int ncols = a.rows < 8 * MG ? a.rows : 8 * MG;
-      for (int idx = lane; idx < ncols * 16; idx += 32) {
-        const int col = idx >> 4, row = idx & 15;
-        const int mg = col >> 3, e = (col & 7) * 16 + row;
-        float s = 0.f;
+      constexpr int EPL = (MG * 128 + 31) / 32;  // output elements per lane
+      float other[EPL];
 #pragma unroll
-        for (int w = 0; w < NW; w++) s += red[((rs * NW + w) * MG + mg) * 128 + e];
-        if (!owner) {
-          a.partial[(b * MG + mg) * 128 + e] = s;
-          __threadfence();
-        } else {
-          if (!whole) {
-            for (int64_t bp = b + 1; bp < G && (bp * T) / G < rt_end; bp++) {
-              volatile int* fl = a.flags + bp;
-              const long long t0 = clock64();
-              while (*fl == 0) {
-                if (*abort_flag || clock64() - t0 > WAIT_CYCLES) { *abort_flag = 1; break; }
-                __nanosleep(100);
-              }
-              __threadfence();
-              s += __ldcg(a.partial + (bp * MG + mg) * 128 + e);
+      for (int j = 0; j < EPL; j++) other[j] = 0.f;
+      int ncontrib = 0;
+      if (owner && !whole) {
+        for (int bp = b + 1; bp < G && start_of(bp) < rt_end; bp++) ncontrib++;
+        const long long t0 = clock64();
+        for (int base = 0; base < ncontrib; base += 32) {
+          const int mine = base + lane;
+          for (;;) {
+            const int ready = mine < ncontrib ? *(volatile int*)(a.flags + b + 1 + mine) : 1;
+            if (__all_sync(0xFFFFFFFFu, ready != 0)) break;
+            if (*abort_flag || clock64() - t0 > WAIT_CYCLES) { *abort_flag = 1; break; }
+            __nanosleep(64);
+          }
+        }
+        __threadfence();
+        for (int cb = 0; cb < ncontrib; cb++) {
+#pragma unroll
+          for (int j = 0; j < EPL; j++) {
+            const int idx = lane + 32 * j;
+            if (idx < ncols * 16) {
+              const int col = idx >> 4, row = idx & 15;
+              other[j] += __ldcg(a.partial + ((b + 1 + cb) * MG + (col >> 3)) * 128 + (col & 7) * 16 + row);
             }
           }
-          const int64_t nn = rt * TQ_TILE_ROWS + row;
-          if (nn < a.n_rows) {
-            if (a.bias) s += a.bias[nn];
-            a.y[(int64_t)col * a.n_rows + nn] = s;
+        }
+      }
+      if (!mbar_wait(&red_full[rs], rph, abort_flag)) break;
+#pragma unroll
+      for (int j = 0; j < EPL; j++) {
+        const int idx = lane + 32 * j;
+        if (idx < ncols * 16) {
+          const int col = idx >> 4, row = idx & 15;
+          const int mg = col >> 3, e = (col & 7) * 16 + row;
+          float s = 0.f;
+#pragma unroll
+          for (int ww = 0; ww < NW; ww++) s += red[((rs * NW + ww) * MG + mg) * 128 + e];
+          if (!owner) {
+            a.partial[(b * MG + mg) * 128 + e] = s;
+          } else {
+            s += other[j];
+            const int64_t nn = (int64_t)rt * TQ_TILE_ROWS + row;
+            if (nn < a.n_rows) {
+              if (a.bias) s += a.bias[nn];
+              a.y[(int64_t)col * a.n_rows + nn] = s;
+            }
           }
         }
       }
+      if (!owner) __threadfence();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&red_empty[rs]);
-        if (!owner) {
-          __threadfence();
-          atomicExch(a.flags + b, 1);
-        } else if (!whole) {
-          for (int64_t bp = b + 1; bp < G && (bp * T) / G < rt_end; bp++)
-            atomicExch(a.flags + bp, 0);  // consumed: back to zero for the next launch
-        }
+      if (lane == 0) mbar_arrive(&red_empty[rs]);
+      if (!owner) {
+        if (lane == 0) atomicExch(a.flags + b, 1);
+      } else if (!whole) {
+        for (int cb = lane; cb < ncontrib; cb += 32) a.flags[b + 1 + cb] = 0;  // consumed: zero again for the next launch
       }
+      if (++rs == RED_SLOTS) { rs = 0; rph ^= 1u; }
       seg_ka = kb == KU ? 0 : kb;
-      seg++;
     }
+    TRACE(6);
   }
   __syncthreads();
   if (*abort_flag) {
@@ -376,23 +475,34 @@ bool gemv_int8_fuses_act(int dtype, int64_t m, int64_t k) {
   return plane <= 64 * 1024;
 }
 
-size_t gemv_workspace_bytes(int ctas) { return (size_t)ctas * 4 * 128 * 4 + (size_t)ctas * 4 + 256; }
+// partial sums [up to 4 CTAs per SM][4 groups of 8 rows][128] + one flag per CTA
+size_t gemv_workspace_bytes(int sms) { return (size_t)sms * 4 * 4 * 128 * 4 + (size_t)sms * 4 * 4 + 256; }
 
+// Launches with the programmatic-stream-serialization attribute (the kernel orders itself
+// against its predecessor with griddepcontrol.wait).
 template <int DT, int MG, bool FUSED>
 static cudaError_t launch_one(StreamArgs a, int grid, int smem_bytes, cudaStream_t s) {
-  static bool configured = false;  // per instantiation; the attribute is per device function
-  static int configured_dev = -1;
+  static int configured_dev = -1;  // per instantiation; the attribute is per device function
   int dev = 0;
   cudaGetDevice(&dev);
-  if (!configured || configured_dev != dev) {
+  if (configured_dev != dev) {
     cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<DT, MG, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          smem_budget());
     if (e != cudaSuccess) return e;
-    configured = true;
     configured_dev = dev;
   }
-  gemv_stream_kernel<DT, MG, FUSED><<<grid, THREADS, smem_bytes, s>>>(a);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = (size_t)smem_bytes;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  static const int pdl = getenv("TURQ_GEMV_PDL") ? atoi(getenv("TURQ_GEMV_PDL")) : 0;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<DT, MG, FUSED>, a);
 }
 
 template <int DT>
@@ -405,10 +515,32 @@ static cudaError_t launch_dt(const uint8_t* tiles, int64_t n_rows, int64_t k, co
   const int row_tiles = (int)((n_rows + TQ_TILE_ROWS - 1) / TQ_TILE_ROWS);
   const int KU = (ktiles + GROUP - 1) / GROUP;
   const int64_t T = (int64_t)row_tiles * KU;
-  int grid = sm_count;
-  if ((int64_t)grid > T) grid = (int)T;
+  if (T > (int64_t)1 << 30) return cudaErrorInvalidValue;
+  // The tile split (hence the summation order) must not depend on M: always two CTAs per SM.
+  static const int cps_env = getenv("TURQ_GEMV_CPS") ? atoi(getenv("TURQ_GEMV_CPS")) : 0;
+  const int ctas_per_sm = cps_env > 0 ? cps_env : 2;
+  // ...but sized so that a third CTA (of the next launch) fits beside them while they drain
+  const int share_div = m <= 8 ? 3 : 2;
   const int fmt = DT == TQ_Q8_0 ? TQ_Q8_0 : TQ_Q8_K;
-  const bool fused = gemv_int8_fuses_act(DT, m, k);
+  bool fused = gemv_int8_fuses_act(DT, m, k);
+  const int stage_bytes = NW * UNIT_BYTES;
+  // Shared memory: the ring needs at least two stages next to the activation planes. If
+  // that does not fit a CTA's share of the SM, give up in-kernel quantization first, then
+  // CTAs per SM.
+  auto stages_for = [&](bool f, int cps, int rows, int mg) {
+    if (cps < share_div) cps = share_div;
+    const int share = (smem_budget() + 1024) / cps - 1024;  // 1 KB per CTA is reserved by the system
+    int st = MAX_STAGES;
+    for (; st >= 2; st--)
+      if (plan_smem(DT, mg, f, rows, (int)k, st, stage_bytes).total <= share) break;
+    return st;
+  };
+  {
+    const int rows0 = (int)(m < 32 ? m : 32), mg0 = rows0 <= 8 ? 1 : rows0 <= 16 ? 2 : 4;
+    if (fused && stages_for(true, ctas_per_sm, rows0, mg0) < 2) fused = false;
+  }
+  int grid = sm_count * ctas_per_sm;
+  if ((int64_t)grid > T) grid = (int)T;
   const size_t x_es = x_dtype == TQ_BF16 ? 2 : 4;
   ActPackPlan plan = plan_act_pack(fmt, m, k);
   if (!fused) {
@@ -416,7 +548,6 @@ static cudaError_t launch_dt(const uint8_t* tiles, int64_t n_rows, int64_t k, co
     if (launches) (*launches)++;
     if (e != cudaSuccess) return e;
   }
-  const int stage_bytes = NW * UNIT_BYTES;
   for (int64_t m0 = 0; m0 < m; m0 += 32) {
     const int rows = (int)(m - m0 < 32 ? m - m0 : 32);
     const int mg = rows <= 8 ? 1 : rows <= 16 ? 2 : 4;
@@ -426,6 +557,9 @@ static cudaError_t launch_dt(const uint8_t* tiles, int64_t n_rows, int64_t k, co
     a.row_tiles = row_tiles;
     a.ktiles = ktiles;
     a.k = (int)k;
+    a.KU = KU;
+    a.split_q = (int)(T / grid);
+    a.split_r = (int)(T % grid);
     a.x = static_cast<const uint8_t*>(x) + (size_t)m0 * k * x_es;
     a.x_is_bf16 = x_dtype == TQ_BF16;
     if (!fused) {
@@ -440,18 +574,14 @@ static cudaError_t launch_dt(const uint8_t* tiles, int64_t n_rows, int64_t k, co
     a.y = y + m0 * n_rows;
     a.bias = bias;
     a.partial = reinterpret_cast<float*>(workspace);
-    a.flags = reinterpret_cast<int*>(workspace + (size_t)sm_count * 4 * 128 * 4);
+    a.flags = reinterpret_cast<int*>(workspace + (size_t)sm_count * 4 * 4 * 128 * 4);
     a.status = status;
-    // ring depth from what the activation planes leave free
-    int stages = MAX_STAGES;
-    SmemPlan sp{};
-    for (; stages >= 2; stages--) {
-      sp = plan_smem(DT, mg, fused, rows, (int)k, stages, stage_bytes);
-      if (sp.total <= smem_budget()) break;
-    }
+    const int stages = stages_for(fused, ctas_per_sm, rows, mg);
     if (stages < 2) return cudaErrorInvalidConfiguration;
+    const SmemPlan sp = plan_smem(DT, mg, fused, rows, (int)k, stages, stage_bytes);
     a.stages = stages;
     a.stage_bytes = stage_bytes;
+    a.sp = sp;
     cudaError_t e;
     if (fused) {
       e = launch_one<DT, 1, true>(a, grid, sp.total, s);

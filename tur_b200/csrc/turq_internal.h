@@ -34,7 +34,7 @@ cudaError_t launch_quantize_act_pack(int fmt, const void* x, int x_dtype, int64_
 // activations inside the kernel when they are small, else into `act_scratch` (which must hold
 // plan_act_pack(fmt, m, k).total bytes) with a preceding launch. `workspace` holds
 // gemv_workspace_bytes(sm_count) bytes, zero-initialised once; `status` is a device int.
-size_t gemv_workspace_bytes(int ctas);
+size_t gemv_workspace_bytes(int sms);
 bool gemv_int8_fuses_act(int dtype, int64_t m, int64_t k);
 cudaError_t launch_gemv_int8(int dtype, const uint8_t* tiles, int64_t n_rows, int64_t k, const void* x,
                              int x_dtype, uint8_t* act_scratch, int64_t m, float* y, const float* bias,
