@@ -205,6 +205,36 @@ def test_shards_reassemble_the_unsharded_result(tq, dt):
                           bits(oracle.dequantize(dt, w, k)[:, 768:1024]))
 
 
+@pytest.mark.parametrize("dt", TYPES, ids=ids)
+@pytest.mark.parametrize("n,k,m", [(128, 256, 256), (200, 512, 77), (1024, 4096, 512), (4096, 1024, 300), (272, 2560, 1024)])
+def test_tensor_core_mode_matches_f64_oracle(tq, dt, n, k, m):
+    """tcgen05 f16 path: within 2e-3 relative Frobenius error of dequantize-then-matmul."""
+    w = make_weight(dt, n, k, SEED + 2000 + n)
+    rng = np.random.default_rng(SEED + 10**6 + m)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    x[0] *= 3.0e5                     # a row that would overflow f16 without the row scaling
+    if m > 2:
+        x[2] = 0.0
+    bias = rng.standard_normal(n).astype(np.float32)
+    mm = tq.QMatMul.from_arc(tq.QTensor.new(w, tq.GgmlDType(dt), (n, k)))
+    xd = torch.from_numpy(x).cuda()
+    y = mm.forward(xd, bias=torch.from_numpy(bias).cuda(), mode=tq.Mode.TENSOR_CORE).cpu().numpy()
+    tq.context().poll_status()
+    want = oracle.matmul_f64(dt, w, n, k, x) + bias
+    assert y.shape == (m, n)
+    for rows in (slice(0, 1), slice(1, m)):      # the huge row must not hide errors elsewhere
+        assert oracle.rel_fro(y[rows], want[rows]) < TOL
+    # bf16 activations (the prefill configs feed bf16): exact in f16 for N(0,1) values
+    xb = torch.from_numpy(x[1:]).cuda().to(torch.bfloat16)
+    yb = mm.forward(xb, mode=tq.Mode.TENSOR_CORE).cpu().numpy()
+    assert oracle.rel_fro(yb, oracle.matmul_f64(dt, w, n, k, xb.float().cpu().numpy())) < TOL
+    # AUTO picks this path for prefill-sized M and results do not depend on the batch
+    if m > 64:
+        assert torch.equal(mm.forward(xd, mode=tq.Mode.AUTO), mm.forward(xd, mode=tq.Mode.TENSOR_CORE))
+        y2 = mm.forward(xd[: m // 2 + 1], mode=tq.Mode.TENSOR_CORE)
+        assert torch.equal(y2, mm.forward(xd, mode=tq.Mode.TENSOR_CORE)[: m // 2 + 1])
+
+
 def test_no_kernel_gave_up_a_wait(tq):
     tq.context().poll_status()
 

@@ -1,13 +1,457 @@
-// Tensor-core (tcgen05) prefill GEMM: placeholder translation unit, filled in next.
+// Prefill-sized QMatMul::forward on the 5th-generation tensor cores (tcgen05 / TMEM).
+//
+//   y[m, n] = sum_k x[m, k] * W[n, k]      W quantized (device fragment tiles), x f32 or bf16
+//
+// Step 1 (prep kernel): x -> f16 [M, K], each row scaled by a power of two only when its
+// magnitude would overflow f16 (the scale is undone exactly in the epilogue).
+// Step 2 (this kernel, one CTA per 128 weight rows x 256 activation rows):
+//   * warp 0        TMA producer: activation tiles (256 rows x 64 k, f16) into 128B-swizzled
+//                   shared memory (cp.async.bulk.tensor, no multicast);
+//   * warps 2..9    dequantize the weight tile (128 rows x 64 k) from the fragment tiles to
+//                   f16 - exact f32 value rounded once - and store it in the same K-major
+//                   128B-swizzled layout, then fence to the async proxy;
+//   * warp 1        one elected thread issues tcgen05.mma (M=128, N=256, K=16, f16 x f16 ->
+//                   f32 in TMEM), four per stage, and commits the stage back to the producers;
+//   * warps 2..9    epilogue: tcgen05.ld the accumulator, undo the row scale, add bias, store.
+// MMA roles: A = weights (rows = TMEM lanes), B = activations (columns).
+// Every mbarrier wait is bounded; on expiry the CTA records TURQ_E_TIMEOUT, releases its TMEM
+// and returns.
+#include <cuda.h>
+#include <cuda_fp16.h>
+
+#include <cstdio>
+
+#include "device_utils.cuh"
+#include "gemv_tile.cuh"
 #include "turq_internal.h"
 
 namespace turq {
 
-size_t gemm_tc_scratch_bytes(int64_t m, int64_t k) { return (size_t)m * (size_t)k * 2 + 256; }
+namespace {
 
-cudaError_t launch_gemm_tc(int, const uint8_t*, int64_t, int64_t, const void*, int, int64_t, float*, const float*,
-                           uint8_t*, int, cudaStream_t, int*, int*) {
-  return cudaErrorNotSupported;
+constexpr int BM = 128;      // weight rows per CTA (MMA M)
+constexpr int BN = 256;      // activation rows per CTA (MMA N)
+constexpr int BK = 64;       // k per stage (one 128-byte swizzle row of f16)
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;  // 16 KB
+constexpr int B_BYTES = BN * BK * 2;  // 32 KB
+constexpr int DQ_WARPS = 8;
+constexpr int TC_THREADS = (2 + DQ_WARPS) * 32;
+constexpr int TMEM_COLS = 256;
+constexpr long long TC_WAIT_CYCLES = 4000000000ll;
+
+__device__ __forceinline__ uint32_t s_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void bar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void bar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void bar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool bar_try(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(s_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  const long long t0 = clock64();
+  for (uint32_t i = 0;; i++) {
+    if (bar_try(bar, parity)) return true;
+    if ((i & 255u) == 255u && (*abort_flag || clock64() - t0 > TC_WAIT_CYCLES)) break;
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+// K-major, 128-byte swizzle shared-memory matrix descriptor (8-row groups 1024 B apart).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// byte offset of 16-byte chunk `ch` (8 f16 along k) of tile row r in the swizzled layout
+__device__ __forceinline__ uint32_t swz(int r, int ch) {
+  return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((ch ^ (r & 7)) << 4));
+}
+
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Dequantize this lane's share of 16 weight rows x 64 k (stage kb) and store it as f16.
+// `t` = fragment tile(s) of the 16 rows holding k0 = 64*kb; a_tile = swizzled 128 x 64 tile;
+// row0 = first of the 16 rows inside the 128-row tile.
+template <int DT>
+__device__ __forceinline__ void dequant_to_smem(const uint8_t* __restrict__ tiles_rt, int kb, int lane, uint8_t* a_tile,
+                                                int row0) {
+  const int g = lane >> 2, c = lane & 3;
+  if constexpr (DT == TQ_Q8_0) {
+#pragma unroll
+    for (int tt = 0; tt < 2; tt++) {
+      const uint8_t* t = tiles_rt + (size_t)(2 * kb + tt) * 544;
+      const uint4 q = ld_stream_v4(t + TQ_Q8_0_QS + 16 * lane);
+      const uint32_t w[2][2] = {{q.x, q.y}, {q.z, q.w}};
+#pragma unroll
+      for (int hr = 0; hr < 2; hr++) {
+        const float d = f16_bits_to_f32(ld_u16(t + 2 * (g + 8 * hr)));
+        float v[8];
+#pragma unroll
+        for (int e = 0; e < 8; e++) v[e] = mul_rn((float)(int)(int8_t)((w[hr][e >> 2] >> (8 * (e & 3))) & 0xFF), d);
+        const uint4 o = make_uint4(pack_h2(v[0], v[1]), pack_h2(v[2], v[3]), pack_h2(v[4], v[5]), pack_h2(v[6], v[7]));
+        *reinterpret_cast<uint4*>(a_tile + swz(row0 + g + 8 * hr, 4 * tt + c)) = o;
+      }
+    }
+  } else if constexpr (DT == TQ_Q4_K || DT == TQ_Q5_K) {
+    constexpr int TB = DT == TQ_Q4_K ? 2304 : 2816;
+    constexpr int QS = DT == TQ_Q4_K ? TQ_Q4K_QS : TQ_Q5K_QS;
+    const uint8_t* t = tiles_rt + (size_t)(kb >> 2) * TB;
+    const int i = kb & 3;  // 64-element group inside the super-block: sub-blocks 2i, 2i+1
+    const uint4 q = ld_stream_v4(t + QS + 512 * i + 16 * lane);
+    const uint32_t w[2][2] = {{q.x, q.y}, {q.z, q.w}};
+    uint32_t qh[2][2] = {{0, 0}, {0, 0}};
+    if constexpr (DT == TQ_Q5_K) {
+      const uint4 h = ld_v4(t + TQ_Q5K_QH + 16 * lane);
+      qh[0][0] = h.x; qh[0][1] = h.y; qh[1][0] = h.z; qh[1][1] = h.w;
+    }
+#pragma unroll
+    for (int hr = 0; hr < 2; hr++) {
+      const uint4 hdr = ld_v4(t + 16 * (g + 8 * hr));
+      const float d = f16_bits_to_f32(hdr.x), dmin = f16_bits_to_f32(hdr.x >> 16);
+#pragma unroll
+      for (int nib = 0; nib < 2; nib++) {
+        const int j = 2 * i + nib;
+        int sc, mn;
+        tq_k4_scale_min(hdr.y, hdr.z, hdr.w, j, &sc, &mn);
+        const float dl = mul_rn(d, (float)sc), ml = mul_rn(dmin, (float)mn);
+        float v[8];
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+          uint32_t qi = (w[hr][e >> 2] >> (8 * (e & 3) + 4 * nib)) & 0x0F;
+          if constexpr (DT == TQ_Q5_K) qi |= ((qh[hr][e >> 2] >> (8 * (e & 3) + j)) & 1u) << 4;
+          v[e] = sub_rn(mul_rn(dl, (float)qi), ml);
+        }
+        const uint4 o = make_uint4(pack_h2(v[0], v[1]), pack_h2(v[2], v[3]), pack_h2(v[4], v[5]), pack_h2(v[6], v[7]));
+        *reinterpret_cast<uint4*>(a_tile + swz(row0 + g + 8 * hr, 4 * nib + c)) = o;
+      }
+    }
+  } else {  // Q6_K: the stage is sub-blocks 4i .. 4i+3 (16 elements each)
+    const uint8_t* t = tiles_rt + (size_t)(kb >> 2) * 3360;
+    const int i = kb & 3;
+    const uint4 ql = ld_stream_v4(t + TQ_Q6K_QL + 512 * i + 16 * lane);
+    const uint4 qhv = ld_v4(t + TQ_Q6K_QH + 512 * (i >> 1) + 16 * lane);
+    const uint32_t qlw[2][2] = {{ql.x, ql.y}, {ql.z, ql.w}};
+    const uint32_t qhw[2] = {(i & 1) ? qhv.y : qhv.x, (i & 1) ? qhv.w : qhv.z};
+#pragma unroll
+    for (int hr = 0; hr < 2; hr++) {
+      const int r = g + 8 * hr;
+      const float d = f16_bits_to_f32(ld_u16(t + TQ_Q6K_D + 2 * r));
+      const uint32_t scw = ld_u32(t + 16 * r + 4 * i);
+#pragma unroll
+      for (int jj = 0; jj < 4; jj++) {
+        const int tw = jj >> 1, nib = jj & 1;
+        const float dl = mul_rn(d, (float)sext_byte(scw, jj));
+        float v[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          const uint32_t lo = (qlw[hr][tw] >> (8 * e + 4 * nib)) & 0x0F;
+          const uint32_t hi = (qhw[hr] >> (8 * e + 2 * jj)) & 3u;
+          v[e] = mul_rn(dl, (float)((int)(lo | (hi << 4)) - 32));
+        }
+        // elements 16*jj + 4c .. +3 of the stage: chunk 2*jj + (c >> 1), half (c & 1)
+        const uint2 o = make_uint2(pack_h2(v[0], v[1]), pack_h2(v[2], v[3]));
+        *reinterpret_cast<uint2*>(a_tile + swz(row0 + r, 2 * jj + (c >> 1)) + 8 * (c & 1)) = o;
+      }
+    }
+  }
+}
+
+struct GemmArgs {
+  const uint8_t* tiles;
+  int64_t n_rows;   // weight rows (output features)
+  int ktiles;       // fragment tiles per row-tile
+  int k;
+  int m;            // activation rows
+  const float* rscale;  // [m] factor undoing the f16 row scaling
+  float* y;         // [m, n_rows]
+  const float* bias;
+  int* status;
+};
+
+template <int DT>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
+  constexpr int TB = TileGeom<DT>::BYTES;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // 1024-byte alignment for the swizzled tiles
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_BYTES;
+  uint64_t* full_a = reinterpret_cast<uint64_t*>(smem + STAGES * (A_BYTES + B_BYTES));
+  uint64_t* full_b = full_a + STAGES;
+  uint64_t* empty = full_b + STAGES;
+  uint64_t* accum = empty + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BM;  // first weight row
+  const int m0 = blockIdx.y * BN;  // first activation row
+  const int kblocks = a.k / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) {
+      bar_init(&full_a[s], DQ_WARPS);
+      bar_init(&full_b[s], 1);
+      bar_init(&empty[s], 1);
+    }
+    bar_init(accum, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_u32(tmem_slot)), "n"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (activations)
+    if (lane == 0) {
+      for (int kb = 0; kb < kblocks; kb++) {
+        const int s = kb % STAGES;
+        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+        if (!bar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
+        bar_expect_tx(&full_b[s], B_BYTES);
+        asm volatile(
+            "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                s_u32(sB + s * B_BYTES)),
+            "l"(&xmap), "r"(kb * BK), "r"(m0), "r"(s_u32(&full_b[s]))
+            : "memory");
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      // instruction descriptor: f32 accumulate, f16 x f16, both K-major, N = 256, M = 128
+      constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      bool ok = true;
+      for (int kb = 0; kb < kblocks && ok; kb++) {
+        const int s = kb % STAGES;
+        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+        ok = bar_wait(&full_a[s], ph, abort_flag) && bar_wait(&full_b[s], ph, abort_flag);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_addr = s_u32(sA + s * A_BYTES), b_addr = s_u32(sB + s * B_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < BK / 16; kk++) {
+          const uint64_t da = smem_desc(a_addr + kk * 32), db = smem_desc(b_addr + kk * 32);
+          const uint32_t accumulate = (kb > 0 || kk > 0) ? 1u : 0u;
+          asm volatile(
+              "{\n\t.reg .pred p;\n\t"
+              "setp.ne.b32 p, %4, 0;\n\t"
+              "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_base),
+              "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+              : "memory");
+        }
+        // release the stage to the producers once these MMAs have read it
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s_u32(&empty[s]))
+                     : "memory");
+      }
+      if (ok)
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s_u32(accum))
+                     : "memory");
+    }
+  } else {
+    // ------------------------------------------------------------ dequantize producers, then epilogue
+    const int dq = warp - 2;  // 0..7: row-tile of 16 rows inside the 128-row tile
+    const int64_t rt = (int64_t)(n0 >> 4) + dq;
+    const bool live = rt * TQ_TILE_ROWS < ((a.n_rows + 15) & ~(int64_t)15);
+    const uint8_t* tiles_rt = a.tiles + rt * a.ktiles * TB;
+    bool ok = true;
+    for (int kb = 0; kb < kblocks && ok; kb++) {
+      const int s = kb % STAGES;
+      const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+      ok = bar_wait(&empty[s], ph ^ 1u, abort_flag);
+      if (!ok) break;
+      uint8_t* a_tile = sA + s * A_BYTES;
+      if (live) {
+        dequant_to_smem<DT>(tiles_rt, kb, lane, a_tile, 16 * dq);
+      } else {
+        // rows beyond the tensor: zeros
+        const int g = lane >> 2, c = lane & 3;
+#pragma unroll
+        for (int hr = 0; hr < 2; hr++)
+#pragma unroll
+          for (int h = 0; h < 2; h++)
+            *reinterpret_cast<uint4*>(a_tile + swz(16 * dq + g + 8 * hr, 4 * h + c)) = make_uint4(0, 0, 0, 0);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the MMA
+      __syncwarp();
+      if (lane == 0) bar_arrive(&full_a[s]);
+    }
+    // ---- epilogue: TMEM lanes 32*(warp%4).., columns 128*(dq/4)..
+    if (ok) ok = bar_wait(accum, 0, abort_flag);
+    if (ok) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int quarter = warp & 3;
+      const int col_half = dq >> 2;
+      const int64_t n = (int64_t)n0 + 32 * quarter + lane;
+      const float bv = (a.bias && n < a.n_rows) ? a.bias[n] : 0.f;
+#pragma unroll 1
+      for (int cb = 0; cb < 4; cb++) {
+        const int col0 = 128 * col_half + 32 * cb;
+        uint32_t v[32];
+        const uint32_t taddr = tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)col0;
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+              "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+              "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+              "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+            : "r"(taddr)
+            : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (n < a.n_rows) {
+#pragma unroll
+          for (int j = 0; j < 32; j++) {
+            const int mrow = m0 + col0 + j;
+            if (mrow < a.m) a.y[(int64_t)mrow * a.n_rows + n] = __uint_as_float(v[j]) * a.rscale[mrow] + bv;
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(TMEM_COLS) : "memory");
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(a.status, 7 /* TURQ_E_TIMEOUT */);
+}
+
+// x [m, k] (f32 / bf16) -> f16 [m, k] with a per-row power-of-two scale that is 1 unless the
+// row would overflow f16; rscale[m] undoes it. One CTA per row.
+__global__ void __launch_bounds__(256) prep_act_kernel(const void* __restrict__ x, int is_bf16, int64_t k,
+                                                        __half* __restrict__ xh, float* __restrict__ rscale) {
+  __shared__ float wmax[8];
+  const int64_t row = blockIdx.x;
+  float amax = 0.f;
+  for (int64_t i = threadIdx.x; i < k; i += blockDim.x) amax = fmaxf(amax, fabsf(load_act_f32(x, is_bf16, row * k + i)));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+  if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = wmax[0];
+#pragma unroll
+  for (int w = 1; w < 8; w++) amax = fmaxf(amax, wmax[w]);
+  float s = 1.f;
+  if (amax >= 16384.f && amax < 3.0e38f) {
+    int e;
+    frexpf(amax, &e);           // amax = f * 2^e, f in [0.5, 1)
+    s = ldexpf(1.f, 14 - e);    // scaled row maximum lands in [8192, 16384)
+  }
+  if (threadIdx.x == 0) rscale[row] = 1.f / s;
+  for (int64_t i = threadIdx.x; i < k; i += blockDim.x)
+    xh[row * k + i] = __float2half_rn(load_act_f32(x, is_bf16, row * k + i) * s);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+constexpr int TC_SMEM = STAGES * (A_BYTES + B_BYTES) + (3 * STAGES + 1) * 8 + 16 + 1024;
+
+template <int DT>
+cudaError_t launch_tc_dt(const CUtensorMap& map, const GemmArgs& a, dim3 grid, cudaStream_t s) {
+  static int configured_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (configured_dev != dev) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
+    if (e != cudaSuccess) return e;
+    configured_dev = dev;
+  }
+  gemm_tc_kernel<DT><<<grid, TC_THREADS, TC_SMEM, s>>>(map, a);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+size_t gemm_tc_scratch_bytes(int64_t m, int64_t k) {
+  return (((size_t)m * (size_t)k * 2 + 255) & ~(size_t)255) + (((size_t)m * 4 + 255) & ~(size_t)255) + 256;
+}
+
+cudaError_t launch_gemm_tc(int dtype, const uint8_t* tiles, int64_t n_rows, int64_t k, const void* x, int x_dtype,
+                           int64_t m, float* y, const float* bias, uint8_t* scratch, int sm_count, cudaStream_t s,
+                           int* launches, int* dev_status_word) {
+  (void)sm_count;
+  if (k % BK != 0 || m <= 0 || m > INT32_MAX || k > INT32_MAX) return cudaErrorInvalidValue;
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return cudaErrorNotSupported;
+  __half* xh = reinterpret_cast<__half*>(scratch);
+  float* rscale = reinterpret_cast<float*>(scratch + (((size_t)m * (size_t)k * 2 + 255) & ~(size_t)255));
+  prep_act_kernel<<<(unsigned)m, 256, 0, s>>>(x, x_dtype == TQ_BF16, k, xh, rscale);
+  if (launches) (*launches)++;
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)m};
+  const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)BN};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xh, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+
+  GemmArgs a{};
+  a.tiles = tiles;
+  a.n_rows = n_rows;
+  a.ktiles = (int)(k / tq_block_elems(dtype));
+  a.k = (int)k;
+  a.m = (int)m;
+  a.rscale = rscale;
+  a.y = y;
+  a.bias = bias;
+  a.status = dev_status_word;
+  dim3 grid((unsigned)((n_rows + BM - 1) / BM), (unsigned)((m + BN - 1) / BN));
+  switch (dtype) {
+    case TQ_Q8_0: e = launch_tc_dt<TQ_Q8_0>(map, a, grid, s); break;
+    case TQ_Q4_K: e = launch_tc_dt<TQ_Q4_K>(map, a, grid, s); break;
+    case TQ_Q5_K: e = launch_tc_dt<TQ_Q5_K>(map, a, grid, s); break;
+    case TQ_Q6_K: e = launch_tc_dt<TQ_Q6_K>(map, a, grid, s); break;
+    default: return cudaErrorInvalidValue;
+  }
+  if (launches) (*launches)++;
+  return e;
 }
 
 }  // namespace turq
