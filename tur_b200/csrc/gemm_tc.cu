@@ -8,7 +8,7 @@
 //   * warp 0        TMA producer: activation tiles (256 rows x 64 k, f16) into 128B-swizzled
 //                   shared memory (cp.async.bulk.tensor, no multicast);
 //   * warps 2..9    dequantize the weight tile (128 rows x 64 k) from the fragment tiles to
-//                   f16 - exact f32 value rounded once - and store it in the same K-major
+//                   f16 with packed half arithmetic and store it in the same K-major
 //                   128B-swizzled layout, then fence to the async proxy;
 //   * warp 1        one elected thread issues tcgen05.mma (M=128, N=256, K=16, f16 x f16 ->
 //                   f32 in TMEM), four per stage, and commits the stage back to the producers;
@@ -87,88 +87,128 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// Dequantize this lane's share of 16 weight rows x 64 k (stage kb) and store it as f16.
-// `t` = fragment tile(s) of the 16 rows holding k0 = 64*kb; a_tile = swizzled 128 x 64 tile;
-// row0 = first of the 16 rows inside the 128-row tile.
+// ---- dequantization to f16 with packed half arithmetic (two elements per instruction).
+// An integer q <= 1023 becomes the half 1024 + q by OR-ing it under the exponent 0x6400;
+// subtracting the offset is exact, so the only roundings are the f16 sub-block scale / min
+// and the final multiply-add. The error stays a few 1e-4 of the value, inside the 2e-3 budget
+// of the tensor-core mode (the bit-exact f32 decode lives in decode.cuh).
+__device__ __forceinline__ __half2 u2h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+__device__ __forceinline__ uint32_t h22u(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+// bytes (b0, b1) / (b2, b3) of a word of small integers -> half2 (1024 + b0, 1024 + b1) / ...
+__device__ __forceinline__ __half2 pair01(uint32_t w) { return u2h2(__byte_perm(w, 0x64646464u, 0x5140)); }
+__device__ __forceinline__ __half2 pair23(uint32_t w) { return u2h2(__byte_perm(w, 0x64646464u, 0x5342)); }
+
+// Raw fragment bytes of one lane for one stage (16 rows x 64 k), fetched from global memory a
+// few stages ahead of their use so that the HBM/L2 latency is off the critical path.
+template <int DT> struct StageRegs;
+template <> struct StageRegs<TQ_Q8_0> { uint4 q[2]; uint32_t d[2]; };       // d: f16 row g | row g+8 << 16, per tile
+template <> struct StageRegs<TQ_Q4_K> { uint4 q; uint4 hdr[2]; };
+template <> struct StageRegs<TQ_Q5_K> { uint4 q; uint4 qh; uint4 hdr[2]; };
+template <> struct StageRegs<TQ_Q6_K> { uint4 ql; uint4 qh; uint32_t sc[2]; uint32_t d; };
+
 template <int DT>
-__device__ __forceinline__ void dequant_to_smem(const uint8_t* __restrict__ tiles_rt, int kb, int lane, uint8_t* a_tile,
-                                                int row0) {
-  const int g = lane >> 2, c = lane & 3;
+__device__ __forceinline__ void stage_load(StageRegs<DT>& r, const uint8_t* __restrict__ tiles_rt, int kb, int lane) {
+  const int g = lane >> 2;
   if constexpr (DT == TQ_Q8_0) {
 #pragma unroll
     for (int tt = 0; tt < 2; tt++) {
       const uint8_t* t = tiles_rt + (size_t)(2 * kb + tt) * 544;
-      const uint4 q = ld_stream_v4(t + TQ_Q8_0_QS + 16 * lane);
-      const uint32_t w[2][2] = {{q.x, q.y}, {q.z, q.w}};
-#pragma unroll
-      for (int hr = 0; hr < 2; hr++) {
-        const float d = f16_bits_to_f32(ld_u16(t + 2 * (g + 8 * hr)));
-        float v[8];
-#pragma unroll
-        for (int e = 0; e < 8; e++) v[e] = mul_rn((float)(int)(int8_t)((w[hr][e >> 2] >> (8 * (e & 3))) & 0xFF), d);
-        const uint4 o = make_uint4(pack_h2(v[0], v[1]), pack_h2(v[2], v[3]), pack_h2(v[4], v[5]), pack_h2(v[6], v[7]));
-        *reinterpret_cast<uint4*>(a_tile + swz(row0 + g + 8 * hr, 4 * tt + c)) = o;
-      }
+      r.q[tt] = ld_stream_v4(t + TQ_Q8_0_QS + 16 * lane);
+      r.d[tt] = (uint32_t)ld_u16(t + 2 * g) | ((uint32_t)ld_u16(t + 2 * (g + 8)) << 16);
     }
   } else if constexpr (DT == TQ_Q4_K || DT == TQ_Q5_K) {
     constexpr int TB = DT == TQ_Q4_K ? 2304 : 2816;
     constexpr int QS = DT == TQ_Q4_K ? TQ_Q4K_QS : TQ_Q5K_QS;
     const uint8_t* t = tiles_rt + (size_t)(kb >> 2) * TB;
+    r.q = ld_stream_v4(t + QS + 512 * (kb & 3) + 16 * lane);
+    if constexpr (DT == TQ_Q5_K) r.qh = ld_v4(t + TQ_Q5K_QH + 16 * lane);
+    r.hdr[0] = ld_v4(t + 16 * g);
+    r.hdr[1] = ld_v4(t + 16 * (g + 8));
+  } else {
+    const uint8_t* t = tiles_rt + (size_t)(kb >> 2) * 3360;
+    const int i = kb & 3;
+    r.ql = ld_stream_v4(t + TQ_Q6K_QL + 512 * i + 16 * lane);
+    r.qh = ld_v4(t + TQ_Q6K_QH + 512 * (i >> 1) + 16 * lane);
+    r.sc[0] = ld_u32(t + 16 * g + 4 * i);
+    r.sc[1] = ld_u32(t + 16 * (g + 8) + 4 * i);
+    r.d = (uint32_t)ld_u16(t + TQ_Q6K_D + 2 * g) | ((uint32_t)ld_u16(t + TQ_Q6K_D + 2 * (g + 8)) << 16);
+  }
+}
+
+// Dequantize one stage from registers and store it as f16: a_tile = swizzled 128 x 64 tile,
+// row0 = first of this warp's 16 rows inside it.
+template <int DT>
+__device__ __forceinline__ void stage_dequant_store(const StageRegs<DT>& r, int kb, int lane, uint8_t* a_tile, int row0) {
+  const int g = lane >> 2, c = lane & 3;
+  if constexpr (DT == TQ_Q8_0) {
+    const __half2 off = __float2half2_rn(1152.f);  // 1024 + 128: bytes are biased by xor 0x80
+#pragma unroll
+    for (int tt = 0; tt < 2; tt++) {
+      const uint4 q = r.q[tt];
+      const uint32_t w[2][2] = {{q.x ^ 0x80808080u, q.y ^ 0x80808080u}, {q.z ^ 0x80808080u, q.w ^ 0x80808080u}};
+#pragma unroll
+      for (int hr = 0; hr < 2; hr++) {
+        const __half2 d2 = __half2half2(__ushort_as_half((unsigned short)((r.d[tt] >> (16 * hr)) & 0xFFFFu)));
+        uint4 o;
+        o.x = h22u(__hmul2(__hsub2(pair01(w[hr][0]), off), d2));
+        o.y = h22u(__hmul2(__hsub2(pair23(w[hr][0]), off), d2));
+        o.z = h22u(__hmul2(__hsub2(pair01(w[hr][1]), off), d2));
+        o.w = h22u(__hmul2(__hsub2(pair23(w[hr][1]), off), d2));
+        *reinterpret_cast<uint4*>(a_tile + swz(row0 + g + 8 * hr, 4 * tt + c)) = o;
+      }
+    }
+  } else if constexpr (DT == TQ_Q4_K || DT == TQ_Q5_K) {
     const int i = kb & 3;  // 64-element group inside the super-block: sub-blocks 2i, 2i+1
-    const uint4 q = ld_stream_v4(t + QS + 512 * i + 16 * lane);
-    const uint32_t w[2][2] = {{q.x, q.y}, {q.z, q.w}};
+    const uint32_t w[2][2] = {{r.q.x, r.q.y}, {r.q.z, r.q.w}};
     uint32_t qh[2][2] = {{0, 0}, {0, 0}};
     if constexpr (DT == TQ_Q5_K) {
-      const uint4 h = ld_v4(t + TQ_Q5K_QH + 16 * lane);
-      qh[0][0] = h.x; qh[0][1] = h.y; qh[1][0] = h.z; qh[1][1] = h.w;
+      qh[0][0] = r.qh.x; qh[0][1] = r.qh.y; qh[1][0] = r.qh.z; qh[1][1] = r.qh.w;
     }
+    const __half2 off = __float2half2_rn(1024.f);
 #pragma unroll
     for (int hr = 0; hr < 2; hr++) {
-      const uint4 hdr = ld_v4(t + 16 * (g + 8 * hr));
+      const uint4 hdr = r.hdr[hr];
       const float d = f16_bits_to_f32(hdr.x), dmin = f16_bits_to_f32(hdr.x >> 16);
 #pragma unroll
       for (int nib = 0; nib < 2; nib++) {
         const int j = 2 * i + nib;
         int sc, mn;
         tq_k4_scale_min(hdr.y, hdr.z, hdr.w, j, &sc, &mn);
-        const float dl = mul_rn(d, (float)sc), ml = mul_rn(dmin, (float)mn);
-        float v[8];
-#pragma unroll
-        for (int e = 0; e < 8; e++) {
-          uint32_t qi = (w[hr][e >> 2] >> (8 * (e & 3) + 4 * nib)) & 0x0F;
-          if constexpr (DT == TQ_Q5_K) qi |= ((qh[hr][e >> 2] >> (8 * (e & 3) + j)) & 1u) << 4;
-          v[e] = sub_rn(mul_rn(dl, (float)qi), ml);
+        const __half2 dl = __float2half2_rn(d * (float)sc), ml = __float2half2_rn(-(dmin * (float)mn));
+        uint32_t m0 = (nib ? (w[hr][0] >> 4) : w[hr][0]) & 0x0F0F0F0Fu;
+        uint32_t m1 = (nib ? (w[hr][1] >> 4) : w[hr][1]) & 0x0F0F0F0Fu;
+        if constexpr (DT == TQ_Q5_K) {
+          m0 |= ((qh[hr][0] >> j) << 4) & 0x10101010u;
+          m1 |= ((qh[hr][1] >> j) << 4) & 0x10101010u;
         }
-        const uint4 o = make_uint4(pack_h2(v[0], v[1]), pack_h2(v[2], v[3]), pack_h2(v[4], v[5]), pack_h2(v[6], v[7]));
+        uint4 o;
+        o.x = h22u(__hfma2(__hsub2(pair01(m0), off), dl, ml));
+        o.y = h22u(__hfma2(__hsub2(pair23(m0), off), dl, ml));
+        o.z = h22u(__hfma2(__hsub2(pair01(m1), off), dl, ml));
+        o.w = h22u(__hfma2(__hsub2(pair23(m1), off), dl, ml));
         *reinterpret_cast<uint4*>(a_tile + swz(row0 + g + 8 * hr, 4 * nib + c)) = o;
       }
     }
   } else {  // Q6_K: the stage is sub-blocks 4i .. 4i+3 (16 elements each)
-    const uint8_t* t = tiles_rt + (size_t)(kb >> 2) * 3360;
     const int i = kb & 3;
-    const uint4 ql = ld_stream_v4(t + TQ_Q6K_QL + 512 * i + 16 * lane);
-    const uint4 qhv = ld_v4(t + TQ_Q6K_QH + 512 * (i >> 1) + 16 * lane);
-    const uint32_t qlw[2][2] = {{ql.x, ql.y}, {ql.z, ql.w}};
-    const uint32_t qhw[2] = {(i & 1) ? qhv.y : qhv.x, (i & 1) ? qhv.w : qhv.z};
+    const uint32_t qlw[2][2] = {{r.ql.x, r.ql.y}, {r.ql.z, r.ql.w}};
+    const uint32_t qhw[2] = {(i & 1) ? r.qh.y : r.qh.x, (i & 1) ? r.qh.w : r.qh.z};
+    const __half2 off = __float2half2_rn(1056.f);  // 1024 + 32
 #pragma unroll
     for (int hr = 0; hr < 2; hr++) {
-      const int r = g + 8 * hr;
-      const float d = f16_bits_to_f32(ld_u16(t + TQ_Q6K_D + 2 * r));
-      const uint32_t scw = ld_u32(t + 16 * r + 4 * i);
+      const int rr = g + 8 * hr;
+      const float d = f16_bits_to_f32(r.d >> (16 * hr));
 #pragma unroll
       for (int jj = 0; jj < 4; jj++) {
-        const int tw = jj >> 1, nib = jj & 1;
-        const float dl = mul_rn(d, (float)sext_byte(scw, jj));
-        float v[4];
-#pragma unroll
-        for (int e = 0; e < 4; e++) {
-          const uint32_t lo = (qlw[hr][tw] >> (8 * e + 4 * nib)) & 0x0F;
-          const uint32_t hi = (qhw[hr] >> (8 * e + 2 * jj)) & 3u;
-          v[e] = mul_rn(dl, (float)((int)(lo | (hi << 4)) - 32));
-        }
+        const int tw = jj >> 1, nib = jj & 1, sh = 2 * jj;
+        const __half2 dl = __float2half2_rn(d * (float)sext_byte(r.sc[hr], jj));
+        uint32_t m = (nib ? (qlw[hr][tw] >> 4) : qlw[hr][tw]) & 0x0F0F0F0Fu;
+        m |= (sh <= 4 ? (qhw[hr] << (4 - sh)) : (qhw[hr] >> (sh - 4))) & 0x30303030u;
         // elements 16*jj + 4c .. +3 of the stage: chunk 2*jj + (c >> 1), half (c & 1)
-        const uint2 o = make_uint2(pack_h2(v[0], v[1]), pack_h2(v[2], v[3]));
-        *reinterpret_cast<uint2*>(a_tile + swz(row0 + r, 2 * jj + (c >> 1)) + 8 * (c & 1)) = o;
+        uint2 o;
+        o.x = h22u(__hmul2(__hsub2(pair01(m), off), dl));
+        o.y = h22u(__hmul2(__hsub2(pair23(m), off), dl));
+        *reinterpret_cast<uint2*>(a_tile + swz(row0 + rr, 2 * jj + (c >> 1)) + 8 * (c & 1)) = o;
       }
     }
   }
@@ -281,26 +321,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
     const bool live = rt * TQ_TILE_ROWS < ((a.n_rows + 15) & ~(int64_t)15);
     const uint8_t* tiles_rt = a.tiles + rt * a.ktiles * TB;
     bool ok = true;
-    for (int kb = 0; kb < kblocks && ok; kb++) {
-      const int s = kb % STAGES;
-      const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
-      ok = bar_wait(&empty[s], ph ^ 1u, abort_flag);
-      if (!ok) break;
-      uint8_t* a_tile = sA + s * A_BYTES;
-      if (live) {
-        dequant_to_smem<DT>(tiles_rt, kb, lane, a_tile, 16 * dq);
-      } else {
-        // rows beyond the tensor: zeros
-        const int g = lane >> 2, c = lane & 3;
+    constexpr int PF = 4;  // stages of raw weight bytes kept in registers ahead of their use
+    StageRegs<DT> pre[PF];
+    if (live) {
 #pragma unroll
-        for (int hr = 0; hr < 2; hr++)
+      for (int u = 0; u < PF - 1; u++)
+        if (u < kblocks) stage_load<DT>(pre[u], tiles_rt, u, lane);
+    }
+    for (int kb0 = 0; kb0 < kblocks && ok; kb0 += PF) {
 #pragma unroll
-          for (int h = 0; h < 2; h++)
-            *reinterpret_cast<uint4*>(a_tile + swz(16 * dq + g + 8 * hr, 4 * h + c)) = make_uint4(0, 0, 0, 0);
+      for (int u = 0; u < PF; u++) {
+        const int kb = kb0 + u;
+        if (kb >= kblocks) break;
+        if (live && kb + PF - 1 < kblocks) stage_load<DT>(pre[(u + PF - 1) % PF], tiles_rt, kb + PF - 1, lane);
+        const int s = kb % STAGES;
+        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+        ok = bar_wait(&empty[s], ph ^ 1u, abort_flag);
+        if (!ok) break;
+        uint8_t* a_tile = sA + s * A_BYTES;
+        if (live) {
+          stage_dequant_store<DT>(pre[u], kb, lane, a_tile, 16 * dq);
+        } else {
+          // rows beyond the tensor: zeros
+          const int g = lane >> 2, c = lane & 3;
+#pragma unroll
+          for (int hr = 0; hr < 2; hr++)
+#pragma unroll
+            for (int h = 0; h < 2; h++)
+              *reinterpret_cast<uint4*>(a_tile + swz(16 * dq + g + 8 * hr, 4 * h + c)) = make_uint4(0, 0, 0, 0);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the MMA
+        __syncwarp();
+        if (lane == 0) bar_arrive(&full_a[s]);
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the MMA
-      __syncwarp();
-      if (lane == 0) bar_arrive(&full_a[s]);
     }
     // ---- epilogue: TMEM lanes 32*(warp%4).., columns 128*(dq/4)..
     if (ok) ok = bar_wait(accum, 0, abort_flag);
