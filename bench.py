@@ -338,6 +338,133 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+def run_gpu_tp(args):
+    """Tensor-parallel pass of a sharded workload (cfg5): q/k/v/gate/up and the head split by
+    rows, o/down by columns with an NCCL all-reduce after each, all-gather of the logits.
+    Strong scaling: the model is fixed, every rank streams 1/N of it."""
+    import torch
+    import torch.distributed as dist
+    from tur_b200 import GgmlDType, Mode, QMatMul, QTensor, context
+    from tur_b200.tensor_parallel import TPLinear, gather_columns, row_unit_for, shard_blocks, shard_of
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    wl = WORKLOADS[args.workload]
+    m = args.m
+    mode = Mode[args.mode]
+    ctx = context(local)
+    head_dim = 128
+
+    def make(w, seed):
+        sh = shard_of(w, world, rank, row_unit_for(w, head_dim))
+        blocks = shard_blocks(gen_weight_blocks(w, seed), w, sh)
+        return sh, torch.from_numpy(blocks).to(dev)
+
+    protos = [(w,) + make(w, SEED + i) for i, w in enumerate(wl.per_layer)]
+    layers = []
+    for _ in range(wl.layers):
+        layer = []
+        for w, sh, b in protos:
+            mm = QMatMul.from_arc(QTensor.new(b, GgmlDType(w.dtype), sh.shape))
+            layer.append((w, sh, TPLinear(w, sh, mm)))
+        layers.append(layer)
+    head = None
+    if wl.head is not None:
+        sh, b = make(wl.head, SEED + 999)
+        head = (wl.head, sh, QMatMul.from_arc(QTensor.new(b, GgmlDType(wl.head.dtype), sh.shape)))
+    del protos
+    torch.cuda.synchronize()
+
+    # synthetic activations: full hidden state (replicated), this rank's slice of the
+    # attention output / MLP intermediate (they come from sharded heads / gate*up)
+    xs, ys = {}, {}
+    for w, sh, _ in layers[0]:
+        kloc = sh.shape[1]
+        if (w.source, kloc) not in xs:
+            xs[(w.source, kloc)] = torch.from_numpy(gen_activations(m, kloc, SEED + 10**6 + m + len(xs))).to(dev)
+        ys[w.name] = torch.empty((m, sh.shape[0]), dtype=torch.float32, device=dev)
+    if head:
+        ys["output"] = torch.empty((m, head[1].shape[0]), dtype=torch.float32, device=dev)
+
+    def one_pass():
+        for layer in layers:
+            for w, sh, lin in layer:
+                y = lin.matmul.forward(xs[(w.source, sh.shape[1])], mode=mode, out=ys[w.name])
+                if sh.parallel == "row" and world > 1:
+                    dist.all_reduce(y)
+        if head:
+            y = head[2].forward(xs[("hidden", wl.hidden)], mode=mode, out=ys["output"])
+            if world > 1:
+                gather_columns(y, wl.head.n, world, 16)
+
+    for _ in range(max(3, args.warmup)):
+        one_pass()
+    torch.cuda.synchronize()
+    l0 = ctx.launch_count()
+    runner, graphed = one_pass, False
+    try:
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side), torch.cuda.graph(graph, stream=side):
+            one_pass()
+        runner, graphed = graph.replay, True
+    except Exception:
+        torch.cuda.synchronize()
+    launches_per_step = (ctx.launch_count() - l0) if graphed else None
+    if not graphed:
+        l0 = ctx.launch_count()
+        one_pass()
+        launches_per_step = ctx.launch_count() - l0
+    for _ in range(3):
+        runner()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with sampler:
+        e0.record()
+        for _ in range(args.steps):
+            runner()
+        e1.record()
+        torch.cuda.synchronize()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+    if rank == 0:
+        total_bytes = wl.total_bytes()
+        peak, peak_kind = measured_peaks()
+        value = total_bytes * args.steps / (ms * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "int8" if mode in (Mode.INT8_ACT, Mode.AUTO) else "f16", "data": "synthetic",
+            "config": {"workload": f"{wl.name}: {wl.description}, M={m}, tensor-parallel x{world}", "mode": mode.name,
+                       "parallelism": f"tp{world}", "cuda_graph": graphed,
+                       "collectives": "NCCL all-reduce after attn_output and ffn_down, all-gather after the head",
+                       "weight_bytes_total": total_bytes, "tokens_per_s": m * args.steps / (ms * 1e-3)},
+            "e2e": None, "gpu_launches": launches_per_step * args.steps, "clocks": sampler.summary(),
+            "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                         "frac": value / world / peak, "traffic": None,
+                         "kernel": "whole sharded pass per GPU (GEMV kernels + NCCL collectives)"},
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -345,15 +472,18 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="turq", choices=["turq", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
-    ap.add_argument("--m", type=int, default=1, help="activation rows per linear (decode batch)")
+    ap.add_argument("--rows", dest="m", type=int, default=1, help="activation rows per linear (decode batch M)")
     ap.add_argument("--mode", default="INT8_ACT", choices=["AUTO", "INT8_ACT", "EXACT_F32", "TENSOR_CORE"])
     ap.add_argument("--e2e-steps", type=int, default=20)
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU-baseline timing")
+    ap.add_argument("--tp", action="store_true", help="tensor-parallel over all ranks (the sharded cfg5 workload)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.tp:
+        run_gpu_tp(args)
     else:
         run_gpu(args)
 

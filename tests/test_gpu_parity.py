@@ -206,7 +206,7 @@ def test_shards_reassemble_the_unsharded_result(tq, dt):
 
 
 @pytest.mark.parametrize("dt", TYPES, ids=ids)
-@pytest.mark.parametrize("n,k,m", [(128, 256, 256), (200, 512, 77), (1024, 4096, 512), (4096, 1024, 300), (272, 2560, 1024)])
+@pytest.mark.parametrize("n,k,m", [(128, 256, 256), (200, 512, 77), (304, 1024, 48), (1024, 2048, 64), (1024, 4096, 512), (4096, 1024, 300), (272, 2560, 1024)])
 def test_tensor_core_mode_matches_f64_oracle(tq, dt, n, k, m):
     """tcgen05 f16 path: within 2e-3 relative Frobenius error of dequantize-then-matmul."""
     w = make_weight(dt, n, k, SEED + 2000 + n)

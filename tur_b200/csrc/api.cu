@@ -337,7 +337,7 @@ int32_t turq_qmatmul(turq_ctx* ctx, const turq_qtensor* qt, const void* dev_x, i
   if (m > INT32_MAX / 2) return fail(ctx, TURQ_E_SHAPE, "m=%lld too large", (long long)m);
   if (qt->device != ctx->device) return fail(ctx, TURQ_E_INVALID_ARG, "tensor lives on device %d, context on %d", qt->device, ctx->device);
   if ((uintptr_t)dev_x % 16 != 0 || (uintptr_t)dev_y % 4 != 0) return fail(ctx, TURQ_E_ALIGN, "dev_x must be 16-byte aligned");
-  if (mode == TURQ_MODE_AUTO) mode = (m <= 64 || qt->n_cols % 64 != 0) ? TURQ_MODE_INT8_ACT : TURQ_MODE_TENSOR_CORE;
+  if (mode == TURQ_MODE_AUTO) mode = (m <= 16 || qt->n_cols % 64 != 0) ? TURQ_MODE_INT8_ACT : TURQ_MODE_TENSOR_CORE;
   if (mode == TURQ_MODE_TENSOR_CORE && qt->n_cols % 64 != 0)
     return fail(ctx, TURQ_E_SHAPE, "the tensor-core mode needs in-features to be a multiple of 64 (got %lld)", (long long)qt->n_cols);
   TQ_CUDA(ctx, cudaSetDevice(ctx->device));

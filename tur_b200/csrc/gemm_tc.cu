@@ -4,15 +4,15 @@
 //
 // Step 1 (prep kernel): x -> f16 [M, K], each row scaled by a power of two only when its
 // magnitude would overflow f16 (the scale is undone exactly in the epilogue).
-// Step 2 (this kernel, one CTA per 128 weight rows x 256 activation rows):
+// Step 2 (this kernel, one CTA per 128 weight rows x BN = 256 or 64 activation rows):
 //   * warp 0        TMA producer: activation tiles (256 rows x 64 k, f16) into 128B-swizzled
 //                   shared memory (cp.async.bulk.tensor, no multicast);
-//   * warps 2..9    dequantize the weight tile (128 rows x 64 k) from the fragment tiles to
+//   * warps 2..17   dequantize (two groups of eight on alternate stages) the weight tile (128 rows x 64 k) from the fragment tiles to
 //                   f16 with packed half arithmetic and store it in the same K-major
 //                   128B-swizzled layout, then fence to the async proxy;
 //   * warp 1        one elected thread issues tcgen05.mma (M=128, N=256, K=16, f16 x f16 ->
 //                   f32 in TMEM), four per stage, and commits the stage back to the producers;
-//   * warps 2..9    epilogue: tcgen05.ld the accumulator, undo the row scale, add bias, store.
+//   * warps 2..17   epilogue: tcgen05.ld the accumulator, undo the row scale, add bias, store.
 // MMA roles: A = weights (rows = TMEM lanes), B = activations (columns).
 // Every mbarrier wait is bounded; on expiry the CTA records TURQ_E_TIMEOUT, releases its TMEM
 // and returns.
@@ -30,14 +30,12 @@ namespace turq {
 namespace {
 
 constexpr int BM = 128;      // weight rows per CTA (MMA M)
-constexpr int BN = 256;      // activation rows per CTA (MMA N)
 constexpr int BK = 64;       // k per stage (one 128-byte swizzle row of f16)
 constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2;  // 16 KB
-constexpr int B_BYTES = BN * BK * 2;  // 32 KB
-constexpr int DQ_WARPS = 8;
-constexpr int TC_THREADS = (2 + DQ_WARPS) * 32;
-constexpr int TMEM_COLS = 256;
+constexpr int DQ_WARPS = 8;        // warps that together produce one stage of the weight operand
+constexpr int DQ_GROUPS = 2;       // groups of DQ_WARPS warps working on alternate stages
+constexpr int TC_THREADS = (2 + DQ_WARPS * DQ_GROUPS) * 32;
 constexpr long long TC_WAIT_CYCLES = 4000000000ll;
 
 __device__ __forceinline__ uint32_t s_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -226,10 +224,14 @@ struct GemmArgs {
   int* status;
 };
 
-template <int DT>
+// BN = activation rows per CTA (MMA N): 256 for prefill, 64 for decode batches of a few dozen
+// rows (smaller activation tiles and accumulator, two CTAs per SM).
+template <int DT, int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
   constexpr int TB = TileGeom<DT>::BYTES;
+  constexpr int B_BYTES = BN * BK * 2;
+  constexpr int TMEM_COLS = BN;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // 1024-byte alignment for the swizzled tiles
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -285,7 +287,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      // instruction descriptor: f32 accumulate, f16 x f16, both K-major, N = 256, M = 128
+      // instruction descriptor: f32 accumulate, f16 x f16, both K-major, N = BN, M = 128
       constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
       bool ok = true;
       for (int kb = 0; kb < kblocks && ok; kb++) {
@@ -316,24 +318,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
     }
   } else {
     // ------------------------------------------------------------ dequantize producers, then epilogue
-    const int dq = warp - 2;  // 0..7: row-tile of 16 rows inside the 128-row tile
+    const int dqw = warp - 2;           // 0..15
+    const int grp = dqw / DQ_WARPS;     // this warp's group takes stages kb = grp, grp + DQ_GROUPS, ...
+    const int dq = dqw % DQ_WARPS;      // row-tile of 16 rows inside the 128-row tile
     const int64_t rt = (int64_t)(n0 >> 4) + dq;
     const bool live = rt * TQ_TILE_ROWS < ((a.n_rows + 15) & ~(int64_t)15);
     const uint8_t* tiles_rt = a.tiles + rt * a.ktiles * TB;
     bool ok = true;
     constexpr int PF = 4;  // stages of raw weight bytes kept in registers ahead of their use
     StageRegs<DT> pre[PF];
+    // this warp's stages are kb = grp + DQ_GROUPS * t, t = 0, 1, ...
+    const int nmine = (kblocks - grp + DQ_GROUPS - 1) / DQ_GROUPS;
     if (live) {
 #pragma unroll
       for (int u = 0; u < PF - 1; u++)
-        if (u < kblocks) stage_load<DT>(pre[u], tiles_rt, u, lane);
+        if (u < nmine) stage_load<DT>(pre[u], tiles_rt, grp + DQ_GROUPS * u, lane);
     }
-    for (int kb0 = 0; kb0 < kblocks && ok; kb0 += PF) {
+    for (int t0 = 0; t0 < nmine && ok; t0 += PF) {
 #pragma unroll
       for (int u = 0; u < PF; u++) {
-        const int kb = kb0 + u;
-        if (kb >= kblocks) break;
-        if (live && kb + PF - 1 < kblocks) stage_load<DT>(pre[(u + PF - 1) % PF], tiles_rt, kb + PF - 1, lane);
+        const int t = t0 + u;
+        if (t >= nmine) break;
+        const int kb = grp + DQ_GROUPS * t;
+        if (live && t + PF - 1 < nmine)
+          stage_load<DT>(pre[(u + PF - 1) % PF], tiles_rt, grp + DQ_GROUPS * (t + PF - 1), lane);
         const int s = kb % STAGES;
         const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
         ok = bar_wait(&empty[s], ph ^ 1u, abort_flag);
@@ -355,17 +363,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
         if (lane == 0) bar_arrive(&full_a[s]);
       }
     }
-    // ---- epilogue: TMEM lanes 32*(warp%4).., columns 128*(dq/4)..
+    // ---- epilogue: TMEM lanes 32*(warp%4).., columns split over the warps of each lane quarter
     if (ok) ok = bar_wait(accum, 0, abort_flag);
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int quarter = warp & 3;
-      const int col_half = dq >> 2;
+      constexpr int PARTS = BN >= 128 ? 4 : 2;       // column parts shared out over the warps of a lane quarter
+      const int col_part = dqw >> 2;                  // 0..3
       const int64_t n = (int64_t)n0 + 32 * quarter + lane;
       const float bv = (a.bias && n < a.n_rows) ? a.bias[n] : 0.f;
 #pragma unroll 1
-      for (int cb = 0; cb < 4; cb++) {
-        const int col0 = 128 * col_half + 32 * cb;
+      for (int cb = 0; cb < BN / (32 * PARTS) && col_part < PARTS; cb++) {
+        const int col0 = (BN / PARTS) * col_part + 32 * cb;
         uint32_t v[32];
         const uint32_t taddr = tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)col0;
         asm volatile(
@@ -440,20 +449,25 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-constexpr int TC_SMEM = STAGES * (A_BYTES + B_BYTES) + (3 * STAGES + 1) * 8 + 16 + 1024;
-
-template <int DT>
-cudaError_t launch_tc_dt(const CUtensorMap& map, const GemmArgs& a, dim3 grid, cudaStream_t s) {
+template <int DT, int BN>
+cudaError_t launch_tc_bn(const CUtensorMap& map, const GemmArgs& a, cudaStream_t s) {
+  constexpr int SMEM = STAGES * (A_BYTES + BN * BK * 2) + (3 * STAGES + 1) * 8 + 16 + 1024;
   static int configured_dev = -1;
   int dev = 0;
   cudaGetDevice(&dev);
   if (configured_dev != dev) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<DT, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return e;
     configured_dev = dev;
   }
-  gemm_tc_kernel<DT><<<grid, TC_THREADS, TC_SMEM, s>>>(map, a);
+  dim3 grid((unsigned)((a.n_rows + BM - 1) / BM), (unsigned)((a.m + BN - 1) / BN));
+  gemm_tc_kernel<DT, BN><<<grid, TC_THREADS, SMEM, s>>>(map, a);
   return cudaGetLastError();
+}
+
+template <int DT>
+cudaError_t launch_tc_dt(const CUtensorMap& map, const GemmArgs& a, int bn, cudaStream_t s) {
+  return bn == 64 ? launch_tc_bn<DT, 64>(map, a, s) : launch_tc_bn<DT, 256>(map, a, s);
 }
 
 }  // namespace
@@ -479,7 +493,8 @@ cudaError_t launch_gemm_tc(int dtype, const uint8_t* tiles, int64_t n_rows, int6
   CUtensorMap map;
   const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)m};
   const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)BN};
+  const int bn = m <= 64 ? 64 : 256;
+  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)bn};
   const cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xh, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -495,12 +510,11 @@ cudaError_t launch_gemm_tc(int dtype, const uint8_t* tiles, int64_t n_rows, int6
   a.y = y;
   a.bias = bias;
   a.status = dev_status_word;
-  dim3 grid((unsigned)((n_rows + BM - 1) / BM), (unsigned)((m + BN - 1) / BN));
   switch (dtype) {
-    case TQ_Q8_0: e = launch_tc_dt<TQ_Q8_0>(map, a, grid, s); break;
-    case TQ_Q4_K: e = launch_tc_dt<TQ_Q4_K>(map, a, grid, s); break;
-    case TQ_Q5_K: e = launch_tc_dt<TQ_Q5_K>(map, a, grid, s); break;
-    case TQ_Q6_K: e = launch_tc_dt<TQ_Q6_K>(map, a, grid, s); break;
+    case TQ_Q8_0: e = launch_tc_dt<TQ_Q8_0>(map, a, bn, s); break;
+    case TQ_Q4_K: e = launch_tc_dt<TQ_Q4_K>(map, a, bn, s); break;
+    case TQ_Q5_K: e = launch_tc_dt<TQ_Q5_K>(map, a, bn, s); break;
+    case TQ_Q6_K: e = launch_tc_dt<TQ_Q6_K>(map, a, bn, s); break;
     default: return cudaErrorInvalidValue;
   }
   if (launches) (*launches)++;
