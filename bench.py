@@ -168,7 +168,7 @@ def run_reference(args):
 def run_gpu(args):
     import torch
     import torch.distributed as dist
-    from tur_b200 import GgmlDType, Mode, QMatMul, QTensor, context
+    from tur_b200 import GgmlDType, Mode, QMatMul, QTensor, context, new_context
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -184,13 +184,20 @@ def run_gpu(args):
     mode = Mode[args.mode]
     ctx = context(local)
 
+    # Independent projections of a layer (q|k|v read the same x, so do gate|up) are issued on
+    # parallel streams, as a caller integrating the library can: each lane has its own context
+    # (scratch + hand-over workspace), so overlapping kernels never share state.
+    lanes = {"attn_q": 0, "attn_k": 0, "attn_v": 1, "attn_output": 0, "ffn_gate": 0, "ffn_up": 0, "ffn_down": 0, "output": 0}
+    n_lanes = 2 if args.parallel else 1
+    ctxs = [ctx] + [new_context(local) for _ in range(n_lanes - 1)]
     # ---- weights: every layer gets its own device buffers so a pass streams from HBM
     protos = []
     for i, w in enumerate(wl.per_layer):
         protos.append((w, torch.from_numpy(gen_weight_blocks(w, SEED + i)).to(dev)))
     layers = []
     for _ in range(wl.layers):
-        layers.append([(w, QMatMul.from_arc(QTensor.new(b, GgmlDType(w.dtype), (w.n, w.k)))) for w, b in protos])
+        layers.append([(w, QMatMul.from_arc(QTensor.new(b, GgmlDType(w.dtype), (w.n, w.k), ctx=ctxs[lanes[w.name] % n_lanes])))
+                       for w, b in protos])
     head = None
     if wl.head is not None:
         hb = torch.from_numpy(gen_weight_blocks(wl.head, SEED + 999)).to(dev)
@@ -206,10 +213,51 @@ def run_gpu(args):
     y_dev = {w.name: torch.empty((m, w.n), dtype=torch.float32, device=dev) for w in all_w}
     y_host = {w.name: torch.empty((m, w.n), dtype=torch.float32).pin_memory() for w in all_w}
 
+    side_streams = [torch.cuda.Stream(dev) for _ in range(n_lanes - 1)]
+    groups = [["attn_q", "attn_k", "attn_v"], ["attn_output"], ["ffn_gate", "ffn_up"], ["ffn_down"]]
+
+    def run_group(members):
+        """Members of one dtype go out as a single multi-weight launch."""
+        by_dt = {}
+        for w, mm in members:
+            by_dt.setdefault(w.dtype, []).append((w, mm))
+        for same in by_dt.values():
+            if len(same) > 1 and not args.no_multi:
+                QMatMul.forward_multi([mm for _, mm in same], x_dev[same[0][0].source], mode=mode,
+                                      outs=[y_dev[w.name] for w, _ in same])
+            else:
+                for w, mm in same:
+                    mm.forward(x_dev[w.source], mode=mode, out=y_dev[w.name])
+
     def one_pass_device():
+        main = torch.cuda.current_stream()
         for layer in layers:
-            for w, mm in layer:
-                mm.forward(x_dev[w.source], mode=mode, out=y_dev[w.name])
+            by_name = {w.name: (w, mm) for w, mm in layer}
+            for grp in groups:
+                members = [by_name[n] for n in grp if n in by_name]
+                # split the group by lane: lane 0 on the main stream, the others in parallel
+                by_lane = {}
+                for w, mm in members:
+                    by_lane.setdefault(lanes[w.name] % n_lanes if not args.no_multi else lanes[w.name] % n_lanes, []).append((w, mm))
+                if len(by_lane) > 1:
+                    fork = torch.cuda.Event()
+                    fork.record(main)
+                    joins = []
+                    for lane, mem in by_lane.items():
+                        if lane == 0:
+                            run_group(mem)
+                        else:
+                            st = side_streams[lane - 1]
+                            st.wait_event(fork)
+                            with torch.cuda.stream(st):
+                                run_group(mem)
+                                j = torch.cuda.Event()
+                                j.record(st)
+                                joins.append(j)
+                    for j in joins:
+                        main.wait_event(j)
+                else:
+                    run_group(members)
         if head:
             head[1].forward(x_dev["hidden"], mode=mode, out=y_dev["output"])
 
@@ -229,14 +277,14 @@ def run_gpu(args):
     for _ in range(max(3, args.warmup)):
         one_pass_device()
     torch.cuda.synchronize()
-    l0 = ctx.launch_count()
+    l0 = sum(c.launch_count() for c in ctxs)
     graph = torch.cuda.CUDAGraph()
     side = torch.cuda.Stream(dev)
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):
         with torch.cuda.graph(graph, stream=side):
             one_pass_device()
-    launches_per_step = ctx.launch_count() - l0
+    launches_per_step = sum(c.launch_count() for c in ctxs) - l0
     for _ in range(max(3, args.warmup)):
         graph.replay()
 
@@ -318,6 +366,8 @@ def run_gpu(args):
                         + (" + lm_head" if wl.head else ""),
             "mode": mode.name, "weight_bytes_per_step_per_gpu": wl.total_bytes(), "parallelism": f"replicas x{world}",
             "l2": "weights per pass exceed L2 (distinct buffers per layer); CUDA-graph replay per step",
+            "streams": "one" if n_lanes == 1 else "attn_v beside attn_q|k on a second stream (own context)",
+            "multi_weight_launch": not args.no_multi,
             "tokens_per_s": m * world * args.steps / (ms * 1e-3),
         },
         "e2e": None if e2e_ms is None else {
@@ -477,6 +527,8 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=20)
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU-baseline timing")
     ap.add_argument("--tp", action="store_true", help="tensor-parallel over all ranks (the sharded cfg5 workload)")
+    ap.add_argument("--no-multi", action="store_true", help="one launch per weight (no q|k, gate|up multi-weight launches)")
+    ap.add_argument("--parallel", action="store_true", help="issue attn_v on a second stream beside attn_q|k")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

@@ -129,6 +129,16 @@ int32_t turq_quantize_act(turq_ctx* ctx, int32_t fmt, const void* dev_x, int32_t
 int32_t turq_qmatmul(turq_ctx* ctx, const turq_qtensor* qt, const void* dev_x, int32_t x_dtype,
                      int64_t m, float* dev_y, int32_t mode, const float* dev_bias, void* stream);
 
+/* Several linears that read the same x (attn_q|k|v: src/models/qwen3.rs:272-274; ffn_gate|up:
+ * qwen3.rs:162-166) in one call: count <= 4 weights with the same in-feature count, y[i] is
+ * [m, rows of qts[i]], biases may be NULL or hold NULL entries. Weights of the same type run as
+ * ONE kernel launch over their concatenated rows in the integer scheme; anything else falls
+ * back to one launch per weight. Results equal those of separate turq_qmatmul calls up to the
+ * f32 summation order. */
+int32_t turq_qmatmul_multi(turq_ctx* ctx, int32_t count, const turq_qtensor* const* qts,
+                           const void* dev_x, int32_t x_dtype, int64_t m, float* const* dev_ys,
+                           int32_t mode, const float* const* dev_biases, void* stream);
+
 /* The same call for a caller that keeps activations in host memory, as tur does today
  * (Device::Cpu everywhere: tests/common.rs:5): copies x to the device, runs, copies y back
  * and synchronizes. x and y are f32. */

@@ -235,6 +235,36 @@ def test_tensor_core_mode_matches_f64_oracle(tq, dt, n, k, m):
         assert torch.equal(y2, mm.forward(xd, mode=tq.Mode.TENSOR_CORE)[: m // 2 + 1])
 
 
+@pytest.mark.parametrize("dt", TYPES, ids=ids)
+@pytest.mark.parametrize("m", [1, 5, 16])
+def test_one_launch_for_linears_sharing_x(tq, dt, m):
+    """q|k|v / gate|up style call: same results as separate calls (f32 summation order aside),
+    ragged row counts, per-part bias."""
+    k = 1024
+    shapes = [272, 64, 1000]
+    rng = np.random.default_rng(SEED + 77 + m)
+    ws = [make_weight(dt, n, k, SEED + 300 + n) for n in shapes]
+    mms = [tq.QMatMul.from_arc(tq.QTensor.new(w, tq.GgmlDType(dt), (n, k))) for w, n in zip(ws, shapes)]
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    bias1 = torch.from_numpy(rng.standard_normal(shapes[1]).astype(np.float32)).cuda()
+    l0 = tq.context().launch_count()
+    ys = tq.QMatMul.forward_multi(mms, xd, biases=[None, bias1, None], mode=tq.Mode.INT8_ACT)
+    assert tq.context().launch_count() - l0 == (1 if m <= 8 else 2)   # one GEMV kernel (+ a quantization launch for larger M)
+    tq.context().poll_status()
+    for i, (w, n) in enumerate(zip(ws, shapes)):
+        want = oracle.qmatmul(dt, w, n, k, x) + (bias1.cpu().numpy() if i == 1 else 0)
+        assert ys[i].shape == (m, n)
+        assert oracle.rel_fro(ys[i].cpu().numpy(), want) < 1e-5
+    # mixed types fall back to one launch per weight and still agree
+    other = TYPES[(TYPES.index(dt) + 1) % len(TYPES)]
+    w2 = make_weight(other, 48, k, SEED + 9)
+    mixed = [mms[0], tq.QMatMul.from_arc(tq.QTensor.new(w2, tq.GgmlDType(other), (48, k)))]
+    y2 = tq.QMatMul.forward_multi(mixed, xd, mode=tq.Mode.INT8_ACT)
+    assert oracle.rel_fro(y2[1].cpu().numpy(), oracle.qmatmul(other, w2, 48, k, x)) < 1e-5
+    assert oracle.rel_fro(y2[0].cpu().numpy(), oracle.qmatmul(dt, ws[0], shapes[0], k, x)) < 1e-5
+
+
 def test_no_kernel_gave_up_a_wait(tq):
     tq.context().poll_status()
 

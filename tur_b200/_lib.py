@@ -35,6 +35,7 @@ SIGNATURES = {
     "turq_dequantize": (c_i32, [c_vp, c_vp, c_i32, c_vp, c_vp]),
     "turq_quantize_act": (c_i32, [c_vp, c_i32, c_vp, c_i32, c_i64, c_i64, c_vp, c_vp]),
     "turq_qmatmul": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i64, c_vp, c_i32, c_vp, c_vp]),
+    "turq_qmatmul_multi": (c_i32, [c_vp, c_i32, c_vp, c_vp, c_i32, c_i64, c_vp, c_i32, c_vp, c_vp]),
     "turq_qmatmul_host": (c_i32, [c_vp, c_vp, c_vp, c_i64, c_vp, c_i32, c_vp]),
     "turq_qmatmul_static": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i64, c_vp, c_vp, c_vp]),
 }

@@ -68,6 +68,40 @@ __device__ __forceinline__ void quant_block_q8k(const float (&v)[8], int lane, u
   w1 = pack4(q + 4);
 }
 
+// The same Q8_K block held 16 values per lane by one half of a warp (lane & 15 owns elements
+// 16*(lane&15) .. +15), so a warp quantizes two blocks at once. Identical results.
+__device__ __forceinline__ void quant_block_q8k_half(const float (&v)[16], int lane, uint32_t (&w)[4], float& d, int& s16,
+                                                     int& s32) {
+  const uint32_t half_mask = 0xFFFFu << (lane & 16);
+  uint32_t umax = 0;
+  float mx = 0.f;
+#pragma unroll
+  for (int e = 0; e < 16; e++) {
+    const uint32_t ua = __float_as_uint(fabsf(v[e]));
+    if (ua > umax) { umax = ua; mx = v[e]; }
+  }
+  const uint32_t wmax = __reduce_max_sync(half_mask, umax);
+  const uint32_t holders = __ballot_sync(half_mask, umax == wmax) & half_mask;
+  mx = __shfl_sync(half_mask, mx, __ffs(holders) - 1);
+  int q[16];
+  d = 0.f;
+  if (wmax == 0u) {
+#pragma unroll
+    for (int e = 0; e < 16; e++) q[e] = 0;
+  } else {
+    const float iscale = __fdiv_rn(-128.f, mx);
+#pragma unroll
+    for (int e = 0; e < 16; e++) q[e] = min(127, __float2int_rn(__fmul_rn(iscale, v[e])));
+    d = __fdiv_rn(1.f, iscale);
+  }
+  s16 = 0;
+#pragma unroll
+  for (int e = 0; e < 16; e++) s16 += q[e];
+  s32 = s16 + __shfl_xor_sync(half_mask, s16, 1);
+#pragma unroll
+  for (int i = 0; i < 4; i++) w[i] = pack4(q + 4 * i);
+}
+
 // Q8_0 block of 32 values held 8 per lane by 4 consecutive lanes: d = amax/127 in f32,
 // stored as f16; q = round-half-away(x * (1/d)).
 __device__ __forceinline__ void quant_block_q8_0(const float (&v)[8], uint32_t& w0, uint32_t& w1, __half& dh) {

@@ -367,6 +367,46 @@ int32_t turq_qmatmul(turq_ctx* ctx, const turq_qtensor* qt, const void* dev_x, i
   return TURQ_OK;
 }
 
+int32_t turq_qmatmul_multi(turq_ctx* ctx, int32_t count, const turq_qtensor* const* qts, const void* dev_x,
+                           int32_t x_dtype, int64_t m, float* const* dev_ys, int32_t mode,
+                           const float* const* dev_biases, void* stream) {
+  if (!ctx || !qts || !dev_x || !dev_ys) return fail(ctx, TURQ_E_INVALID_ARG, "null argument");
+  if (count < 1 || count > 4) return fail(ctx, TURQ_E_INVALID_ARG, "count %d outside 1..4", count);
+  for (int i = 0; i < count; i++) {
+    if (!qts[i] || !dev_ys[i]) return fail(ctx, TURQ_E_INVALID_ARG, "null argument");
+    if (qts[i]->n_cols != qts[0]->n_cols) return fail(ctx, TURQ_E_SHAPE, "weights of one call must share the in-feature count");
+  }
+  bool same = true;
+  for (int i = 1; i < count; i++) same = same && qts[i]->dtype == qts[0]->dtype && qts[i]->device == qts[0]->device;
+  int32_t eff = mode;
+  if (eff == TURQ_MODE_AUTO) eff = (m <= 16 || qts[0]->n_cols % 64 != 0) ? TURQ_MODE_INT8_ACT : TURQ_MODE_TENSOR_CORE;
+  if (!same || eff != TURQ_MODE_INT8_ACT || count == 1) {
+    for (int i = 0; i < count; i++) {
+      int32_t st = turq_qmatmul(ctx, qts[i], dev_x, x_dtype, m, dev_ys[i], mode, dev_biases ? dev_biases[i] : nullptr, stream);
+      if (st != TURQ_OK) return st;
+    }
+    return TURQ_OK;
+  }
+  if (x_dtype != TURQ_F32 && x_dtype != TURQ_BF16) return fail(ctx, TURQ_E_DTYPE, "activations must be F32 or BF16 (got %d)", x_dtype);
+  if (m <= 0 || m > INT32_MAX / 2) return fail(ctx, TURQ_E_SHAPE, "m=%lld out of range", (long long)m);
+  if (qts[0]->device != ctx->device) return fail(ctx, TURQ_E_INVALID_ARG, "tensor lives on device %d, context on %d", qts[0]->device, ctx->device);
+  if ((uintptr_t)dev_x % 16 != 0) return fail(ctx, TURQ_E_ALIGN, "dev_x must be 16-byte aligned");
+  TQ_CUDA(ctx, cudaSetDevice(ctx->device));
+  const int64_t k = qts[0]->n_cols;
+  const int fmt = qts[0]->dtype == TURQ_Q8_0 ? TQ_Q8_0 : TQ_Q8_K;
+  turq::ActPackPlan plan = turq::plan_act_pack(fmt, m, k);
+  int32_t st = ensure(ctx, &ctx->scratch, &ctx->scratch_bytes, plan.total);
+  if (st != TURQ_OK) return st;
+  turq::GemvPart parts[4];
+  for (int i = 0; i < count; i++) parts[i] = turq::GemvPart{qts[i]->tiles, qts[i]->n_rows, dev_ys[i], dev_biases ? dev_biases[i] : nullptr};
+  int launches = 0;
+  cudaError_t e = turq::launch_gemv_int8_multi(qts[0]->dtype, parts, count, k, dev_x, x_dtype, ctx->scratch, m, ctx->gemv_ws,
+                                               ctx->dev_status, ctx->sm_count, static_cast<cudaStream_t>(stream), &launches);
+  ctx->launches += launches;
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_multi launch");
+  return TURQ_OK;
+}
+
 int32_t turq_qmatmul_host(turq_ctx* ctx, const turq_qtensor* qt, const float* host_x, int64_t m, float* host_y,
                           int32_t mode, const float* host_bias) {
   if (!ctx || !qt || !host_x || !host_y) return fail(ctx, TURQ_E_INVALID_ARG, "null argument");

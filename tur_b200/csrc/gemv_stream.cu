@@ -95,18 +95,23 @@ struct SmemPlan {
   int ring, act_qs, act_dsc, act_bs16, act_bs32, red, bars, total, qs_stride;
 };
 
+constexpr int MAX_PARTS = 4;  // weights that share one activation and one launch (q|k|v, gate|up)
+
 struct StreamArgs {
-  const uint8_t* tiles;
-  int64_t n_rows;
-  int row_tiles, ktiles, k;
+  // part p covers row-tiles [rt_begin[p], rt_begin[p+1]) of the concatenated row space
+  const uint8_t* tiles[MAX_PARTS];
+  int64_t n_rows[MAX_PARTS];
+  int rt_begin[MAX_PARTS + 1];
+  float* y[MAX_PARTS];            // outputs, already offset to the pass's first row
+  const float* bias[MAX_PARTS];
+  int nparts;
+  int ktiles, k;
   int KU;               // units (tiles; groups of 4 tiles for Q8_0) per row-tile
   int split_q, split_r; // CTA b owns units [b*q + min(b,r), (b+1)*q + min(b+1,r))
   const void* x;        // activations of the pass (first row of the pass), f32 or bf16   [FUSED]
   int x_is_bf16;
   ActPack gact;         // planes in global scratch, already offset to the pass's first row [!FUSED]
   int rows;             // valid activation rows in this pass (<= 8 * MG)
-  float* y;             // output, already offset to the pass's first row
-  const float* bias;
   float* partial;       // [grid][MG * 128]: partial sums of a CTA's leading split row-tile
   int* flags;           // [grid], all zero between launches
   int* status;
@@ -220,7 +225,9 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
         if (!mbar_wait(&empty[slot], ph ^ 1u, abort_flag)) break;
         // one copy per consumer warp (its tile, or its group of Q8_0 tiles), each completing on
         // that warp's own barrier: a warp starts as soon as its bytes are there
-        const uint8_t* src = a.tiles + ((int64_t)w.rt * a.ktiles + (int64_t)w.ku * GROUP) * TB;
+        int part = 0;
+        while (part + 1 < a.nparts && w.rt >= a.rt_begin[part + 1]) part++;
+        const uint8_t* src = a.tiles[part] + ((int64_t)(w.rt - a.rt_begin[part]) * a.ktiles + (int64_t)w.ku * GROUP) * TB;
         uint8_t* dst = smem + sp.ring + slot * a.stage_bytes;
         for (int i = 0; i < n; i++) {
           int nt = a.ktiles - (w.ku + i) * GROUP;
@@ -273,34 +280,34 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
         const int span = u1 - u0 >= KU ? KU : u1 - u0;
         const int first = u1 - u0 >= KU ? 0 : u0 % KU;
         const int total = a.rows * span;
-        for (int base = warp; base < total; base += 2 * NW) {
-          // two blocks per pass with both loads in flight
-          const int i0 = base, i1 = base + NW;
-          const int row0 = i0 / span, row1 = i1 / span;
-          int blk0 = first + (i0 - row0 * span), blk1 = first + (i1 - row1 * span);
-          if (blk0 >= nblk) blk0 -= nblk;
-          if (blk1 >= nblk) blk1 -= nblk;
-          const bool has1 = i1 < total;
-          float v0[8], v1[8];
-          load8(a.x, a.x_is_bf16, (int64_t)row0 * a.k + blk0 * 256 + lane * 8, v0);
-          if (has1) {
-            load8(a.x, a.x_is_bf16, (int64_t)row1 * a.k + blk1 * 256 + lane * 8, v1);
+        for (int base = 2 * warp; base < total; base += 2 * NW) {
+          // two blocks per pass, one per half-warp (16 values per lane)
+          const int i = base + (lane >> 4);
+          const bool has = i < total;
+          const int row = has ? i / span : 0;
+          int blk = has ? first + (i - row * span) : 0;
+          if (blk >= nblk) blk -= nblk;
+          const int hl = lane & 15;
+          float v[16];
+          if (has) {
+            float v0[8], v1[8];
+            load8(a.x, a.x_is_bf16, (int64_t)row * a.k + blk * 256 + hl * 16, v0);
+            load8(a.x, a.x_is_bf16, (int64_t)row * a.k + blk * 256 + hl * 16 + 8, v1);
+#pragma unroll
+            for (int e = 0; e < 8; e++) { v[e] = v0[e]; v[8 + e] = v1[e]; }
           } else {
 #pragma unroll
-            for (int e = 0; e < 8; e++) v1[e] = 0.f;
+            for (int e = 0; e < 16; e++) v[e] = 0.f;
           }
-#pragma unroll
-          for (int h = 0; h < 2; h++) {
-            if (h == 1 && !has1) break;
-            const int row = h ? row1 : row0, blk = h ? blk1 : blk0;
-            uint32_t w0, w1;
-            float d;
-            int s16, s32;
-            quant_block_q8k(h ? v1 : v0, lane, w0, w1, d, s16, s32);
-            *reinterpret_cast<uint2*>(sqs + row * sp.qs_stride + blk * 256 + lane * 8) = make_uint2(w0, w1);
-            if (lane == 0) sdsc[row * nblk + blk] = d;
-            if ((lane & 1) == 0) sb16[row * (a.k >> 4) + blk * 16 + (lane >> 1)] = (int16_t)s16;
-            if ((lane & 3) == 0) sb32[row * (a.k >> 5) + blk * 8 + (lane >> 2)] = (int16_t)s32;
+          uint32_t w4[4];
+          float d;
+          int s16, s32;
+          quant_block_q8k_half(v, lane, w4, d, s16, s32);
+          if (has) {
+            *reinterpret_cast<uint4*>(sqs + row * sp.qs_stride + blk * 256 + hl * 16) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+            if (hl == 0) sdsc[row * nblk + blk] = d;
+            sb16[row * (a.k >> 4) + blk * 16 + hl] = (int16_t)s16;
+            if ((hl & 1) == 0) sb32[row * (a.k >> 5) + blk * 8 + (hl >> 1)] = (int16_t)s32;
           }
         }
       }
@@ -382,6 +389,12 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
       const bool whole = owner && kb == KU;
       const int rt_end = (rt + 1) * KU;
       const int ncols = a.rows < 8 * MG ? a.rows : 8 * MG;
+      int part = 0;
+      while (part + 1 < a.nparts && rt >= a.rt_begin[part + 1]) part++;
+      const int64_t part_rows = a.n_rows[part];
+      float* const part_y = a.y[part];
+      const float* const part_bias = a.bias[part];
+      const int rt_local = rt - a.rt_begin[part];
       constexpr int EPL = (MG * 128 + 31) / 32;  // output elements per lane
       float other[EPL];
 #pragma unroll
@@ -425,10 +438,10 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
             a.partial[(b * MG + mg) * 128 + e] = s;
           } else {
             s += other[j];
-            const int64_t nn = (int64_t)rt * TQ_TILE_ROWS + row;
-            if (nn < a.n_rows) {
-              if (a.bias) s += a.bias[nn];
-              a.y[(int64_t)col * a.n_rows + nn] = s;
+            const int64_t nn = (int64_t)rt_local * TQ_TILE_ROWS + row;
+            if (nn < part_rows) {
+              if (part_bias) s += part_bias[nn];
+              part_y[(int64_t)col * part_rows + nn] = s;
             }
           }
         }
@@ -506,27 +519,30 @@ static cudaError_t launch_one(StreamArgs a, int grid, int smem_bytes, cudaStream
 }
 
 template <int DT>
-static cudaError_t launch_dt(const uint8_t* tiles, int64_t n_rows, int64_t k, const void* x, int x_dtype,
-                             uint8_t* act_scratch, int64_t m, float* y, const float* bias, uint8_t* workspace,
-                             int* status, int sm_count, cudaStream_t s, int* launches) {
+static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const void* x, int x_dtype,
+                             uint8_t* act_scratch, int64_t m, uint8_t* workspace, int* status, int sm_count,
+                             cudaStream_t s, int* launches) {
   constexpr int GROUP = TileGeom<DT>::GROUP;
   constexpr int UNIT_BYTES = TileGeom<DT>::BYTES * GROUP;
+  if (nparts < 1 || nparts > MAX_PARTS) return cudaErrorInvalidValue;
   const int ktiles = (int)(k / TileGeom<DT>::ELEMS);
-  const int row_tiles = (int)((n_rows + TQ_TILE_ROWS - 1) / TQ_TILE_ROWS);
   const int KU = (ktiles + GROUP - 1) / GROUP;
-  const int64_t T = (int64_t)row_tiles * KU;
+  int rt_begin[MAX_PARTS + 1] = {0};
+  for (int p = 0; p < nparts; p++)
+    rt_begin[p + 1] = rt_begin[p] + (int)((parts[p].n_rows + TQ_TILE_ROWS - 1) / TQ_TILE_ROWS);
+  const int64_t T = (int64_t)rt_begin[nparts] * KU;
   if (T > (int64_t)1 << 30) return cudaErrorInvalidValue;
   // The tile split (hence the summation order) must not depend on M: always two CTAs per SM.
   static const int cps_env = getenv("TURQ_GEMV_CPS") ? atoi(getenv("TURQ_GEMV_CPS")) : 0;
   const int ctas_per_sm = cps_env > 0 ? cps_env : 2;
-  // ...but sized so that a third CTA (of the next launch) fits beside them while they drain
-  const int share_div = m <= 8 ? 3 : 2;
+  // ...but sized, when the activation planes allow it, so that a third CTA (of the next
+  // launch) fits beside them while they drain
+  int share_div = m <= 8 ? 3 : 2;
   const int fmt = DT == TQ_Q8_0 ? TQ_Q8_0 : TQ_Q8_K;
   bool fused = gemv_int8_fuses_act(DT, m, k);
   const int stage_bytes = NW * UNIT_BYTES;
   // Shared memory: the ring needs at least two stages next to the activation planes. If
-  // that does not fit a CTA's share of the SM, give up in-kernel quantization first, then
-  // CTAs per SM.
+  // that does not fit a CTA's share of the SM, in-kernel quantization is given up.
   auto stages_for = [&](bool f, int cps, int rows, int mg) {
     if (cps < share_div) cps = share_div;
     const int share = (smem_budget() + 1024) / cps - 1024;  // 1 KB per CTA is reserved by the system
@@ -537,6 +553,7 @@ static cudaError_t launch_dt(const uint8_t* tiles, int64_t n_rows, int64_t k, co
   };
   {
     const int rows0 = (int)(m < 32 ? m : 32), mg0 = rows0 <= 8 ? 1 : rows0 <= 16 ? 2 : 4;
+    if (fused && share_div == 3 && stages_for(true, ctas_per_sm, rows0, mg0) < 2) share_div = 2;
     if (fused && stages_for(true, ctas_per_sm, rows0, mg0) < 2) fused = false;
   }
   int grid = sm_count * ctas_per_sm;
@@ -552,9 +569,14 @@ static cudaError_t launch_dt(const uint8_t* tiles, int64_t n_rows, int64_t k, co
     const int rows = (int)(m - m0 < 32 ? m - m0 : 32);
     const int mg = rows <= 8 ? 1 : rows <= 16 ? 2 : 4;
     StreamArgs a{};
-    a.tiles = tiles;
-    a.n_rows = n_rows;
-    a.row_tiles = row_tiles;
+    for (int p = 0; p < nparts; p++) {
+      a.tiles[p] = parts[p].tiles;
+      a.n_rows[p] = parts[p].n_rows;
+      a.y[p] = parts[p].y + m0 * parts[p].n_rows;
+      a.bias[p] = parts[p].bias;
+    }
+    for (int p = 0; p <= nparts; p++) a.rt_begin[p] = rt_begin[p];
+    a.nparts = nparts;
     a.ktiles = ktiles;
     a.k = (int)k;
     a.KU = KU;
@@ -571,8 +593,6 @@ static cudaError_t launch_dt(const uint8_t* tiles, int64_t n_rows, int64_t k, co
       a.gact.qs_stride = (int)k;
     }
     a.rows = rows;
-    a.y = y + m0 * n_rows;
-    a.bias = bias;
     a.partial = reinterpret_cast<float*>(workspace);
     a.flags = reinterpret_cast<int*>(workspace + (size_t)sm_count * 4 * 4 * 128 * 4);
     a.status = status;
@@ -598,16 +618,23 @@ static cudaError_t launch_dt(const uint8_t* tiles, int64_t n_rows, int64_t k, co
   return cudaSuccess;
 }
 
+cudaError_t launch_gemv_int8_multi(int dtype, const GemvPart* parts, int nparts, int64_t k, const void* x, int x_dtype,
+                                   uint8_t* act_scratch, int64_t m, uint8_t* workspace, int* status, int sm_count,
+                                   cudaStream_t s, int* launches) {
+  switch (dtype) {
+    case TQ_Q8_0: return launch_dt<TQ_Q8_0>(parts, nparts, k, x, x_dtype, act_scratch, m, workspace, status, sm_count, s, launches);
+    case TQ_Q4_K: return launch_dt<TQ_Q4_K>(parts, nparts, k, x, x_dtype, act_scratch, m, workspace, status, sm_count, s, launches);
+    case TQ_Q5_K: return launch_dt<TQ_Q5_K>(parts, nparts, k, x, x_dtype, act_scratch, m, workspace, status, sm_count, s, launches);
+    case TQ_Q6_K: return launch_dt<TQ_Q6_K>(parts, nparts, k, x, x_dtype, act_scratch, m, workspace, status, sm_count, s, launches);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
 cudaError_t launch_gemv_int8(int dtype, const uint8_t* tiles, int64_t n_rows, int64_t k, const void* x, int x_dtype,
                              uint8_t* act_scratch, int64_t m, float* y, const float* bias, uint8_t* workspace,
                              int* status, int sm_count, cudaStream_t s, int* launches) {
-  switch (dtype) {
-    case TQ_Q8_0: return launch_dt<TQ_Q8_0>(tiles, n_rows, k, x, x_dtype, act_scratch, m, y, bias, workspace, status, sm_count, s, launches);
-    case TQ_Q4_K: return launch_dt<TQ_Q4_K>(tiles, n_rows, k, x, x_dtype, act_scratch, m, y, bias, workspace, status, sm_count, s, launches);
-    case TQ_Q5_K: return launch_dt<TQ_Q5_K>(tiles, n_rows, k, x, x_dtype, act_scratch, m, y, bias, workspace, status, sm_count, s, launches);
-    case TQ_Q6_K: return launch_dt<TQ_Q6_K>(tiles, n_rows, k, x, x_dtype, act_scratch, m, y, bias, workspace, status, sm_count, s, launches);
-    default: return cudaErrorInvalidValue;
-  }
+  GemvPart part{tiles, n_rows, y, bias};
+  return launch_gemv_int8_multi(dtype, &part, 1, k, x, x_dtype, act_scratch, m, workspace, status, sm_count, s, launches);
 }
 
 }  // namespace turq

@@ -93,6 +93,17 @@ def context(device: int | torch.device | None = None) -> _Context:
     return ctx
 
 
+def new_context(device: int | torch.device | None = None) -> _Context:
+    """An additional context on the device. A context owns the scratch and hand-over
+    workspace of the calls made through it, so kernels that may overlap on the GPU (linears
+    issued on different streams, e.g. q / k / v of one layer) must use different contexts."""
+    if device is None:
+        device = torch.cuda.current_device() if torch.cuda.is_available() else 0
+    if isinstance(device, torch.device):
+        device = device.index if device.index is not None else torch.cuda.current_device()
+    return _Context(device)
+
+
 def _stream_ptr(device: int) -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
@@ -118,21 +129,22 @@ class QTensor:
 
     @classmethod
     def new(cls, blocks: np.ndarray | bytes | torch.Tensor, dtype: GgmlDType, shape: Sequence[int],
-            device: int | torch.device | None = None) -> "QTensor":
-        """From GGUF wire-format blocks (host bytes, or a uint8 CUDA tensor)."""
+            device: int | torch.device | None = None, ctx: Optional[_Context] = None) -> "QTensor":
+        """From GGUF wire-format blocks (host bytes, or a uint8 CUDA tensor). `ctx` binds the
+        tensor (and the matmuls on it) to a specific context; default: the device's shared one."""
         if len(shape) != 2:
             raise TurqError(2, f"QTensor needs a 2-D shape, got {tuple(shape)}")
         rows, cols = int(shape[0]), int(shape[1])
         lib = _lib.load()
         out = ctypes.c_void_p()
         if isinstance(blocks, torch.Tensor) and blocks.is_cuda:
-            ctx = context(blocks.device)
+            ctx = ctx or context(blocks.device)
             blocks = blocks.contiguous().view(torch.uint8)
             ctx.check(lib.turq_qtensor_from_device(ctx.handle, int(dtype), rows, cols, ctypes.c_void_p(blocks.data_ptr()),
                                                    blocks.numel(), _stream_ptr(ctx.device), ctypes.byref(out)))
             torch.cuda.current_stream(ctx.device).synchronize()
             return cls(out, ctx)
-        ctx = context(device)
+        ctx = ctx or context(device)
         if isinstance(blocks, torch.Tensor):
             blocks = blocks.contiguous().view(torch.uint8).numpy()
         buf = np.frombuffer(blocks, dtype=np.uint8) if isinstance(blocks, (bytes, bytearray)) else np.ascontiguousarray(blocks).view(np.uint8).reshape(-1)
@@ -229,3 +241,31 @@ class QMatMul:
         return y.reshape(*lead, n)
 
     __call__ = forward
+
+    @staticmethod
+    def forward_multi(mms: Sequence["QMatMul"], x: torch.Tensor, biases: Optional[Sequence[Optional[torch.Tensor]]] = None,
+                      mode: Mode = Mode.AUTO, outs: Optional[Sequence[torch.Tensor]] = None) -> list[torch.Tensor]:
+        """Linears that read the same x (q|k|v, gate|up) in one call: weights of one type run
+        as a single kernel launch over their concatenated rows. x is a CUDA tensor [..., k]."""
+        lib = _lib.load()
+        n = len(mms)
+        ctx = mms[0].qtensor._ctx
+        k = mms[0].qtensor.shape()[1]
+        if not x.is_cuda:
+            raise TurqError(8, "forward_multi needs a CUDA tensor")
+        if x.dtype not in (torch.float32, torch.bfloat16):
+            x = x.to(torch.float32)
+        x2 = x.reshape(-1, k).contiguous()
+        m = x2.shape[0]
+        if outs is None:
+            outs = [torch.empty((m, mm.qtensor.shape()[0]), dtype=torch.float32, device=x.device) for mm in mms]
+        arr = ctypes.c_void_p * n
+        qts = arr(*[mm.qtensor._h for mm in mms])
+        ys = arr(*[ctypes.c_void_p(o.data_ptr()) for o in outs])
+        bs = None
+        if biases is not None:
+            bs = arr(*[ctypes.c_void_p(b.data_ptr()) if b is not None else None for b in biases])
+        ctx.check(lib.turq_qmatmul_multi(ctx.handle, n, qts, ctypes.c_void_p(x2.data_ptr()), int(_TORCH_TO_GGML[x2.dtype]), m,
+                                         ys, int(mode), bs, _stream_ptr(ctx.device)))
+        lead = tuple(x.shape[:-1])
+        return [o.reshape(*lead, o.shape[-1]) for o in outs]
