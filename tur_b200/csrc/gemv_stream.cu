@@ -207,11 +207,12 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  // Programmatic dependent launch: let the next kernel of the stream start its own prologue
-  // (and its weight stream) while this grid is still running. The weights never depend on a
-  // preceding kernel, so the producer warp starts at once; the warps that read activations or
-  // write outputs / the hand-over workspace first wait for the preceding grid to finish.
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // Programmatic dependent launch (when the launch carries the attribute): the next kernel of
+  // the stream may be scheduled once every CTA of this grid has issued launch_dependents, which
+  // the producer does after its last copy - the launch latency of the next kernel then hides
+  // behind this grid's tail. The weights never depend on a preceding kernel, so a producer warp
+  // starts streaming at once; the warps that read activations or write outputs / the hand-over
+  // workspace first wait (griddepcontrol.wait) for the preceding grid to finish.
 
   if (warp == NW) {
     // ------------------------------------------------------------ producer warp
@@ -242,6 +243,7 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
         if (++slot == a.stages) { slot = 0; ph ^= 1u; }
       }
     }
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   } else if (warp < NW) {
     // ------------------------------------------------------------ consumer warps
     if (warp == 0) TRACE(1);

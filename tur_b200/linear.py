@@ -45,6 +45,6 @@ def linear(in_dim: int, out_dim: int, vb: QVarBuilderLike) -> LinearX:
         raise TurqError(2, f"shape mismatch for weight, got {qweight.shape()}, expected {(out_dim, in_dim)}")
     bias = None
     if vb.contains_key("bias"):
-        b = vb.get((1, out_dim), "bias")
-        bias = b.dequantize().reshape(out_dim) if isinstance(b, QTensor) else b
+        b = vb.get(out_dim, "bias")
+        bias = b.dequantize().reshape(out_dim) if hasattr(b, "dequantize") else b
     return LinearX(QMatMul.from_arc(qweight), bias)
