@@ -140,6 +140,24 @@ def test_matmul_matches_oracle_of_same_scheme(tq, dt, n, k, m):
 
 
 @pytest.mark.parametrize("dt", TYPES, ids=ids)
+@pytest.mark.parametrize("n,k,m", [(4096, 2560, 1), (1024, 5120, 3), (2560, 6400, 16), (272, 1280, 1)])
+def test_streaming_pipeline_is_race_free_when_stages_are_partly_filled(tq, dt, n, k, m):
+    """In-features that do not fill the 8-tile stages evenly (10, 20, 25, 5 tiles per row) leave
+    consumer warps without a tile in some stages; repeated launches must stay bit-identical and
+    correct, and no kernel may give up a wait."""
+    w = make_weight(dt, n, k, SEED + 4000 + k)
+    rng = np.random.default_rng(SEED + 5)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    mm = tq.QMatMul.from_arc(tq.QTensor.new(w, tq.GgmlDType(dt), (n, k)))
+    xd = torch.from_numpy(x).cuda()
+    first = mm.forward(xd, mode=tq.Mode.INT8_ACT)
+    for _ in range(40):
+        assert torch.equal(mm.forward(xd, mode=tq.Mode.INT8_ACT), first)
+    tq.context().poll_status()
+    assert oracle.rel_fro(first.cpu().numpy(), oracle.qmatmul(dt, w, n, k, x)) < 1e-5
+
+
+@pytest.mark.parametrize("dt", TYPES, ids=ids)
 def test_rows_are_independent_of_batch_size_and_bias_is_added(tq, dt):
     """tur's tests rely on a token's result not depending on its batch neighbours
     (tests/pipeline_integration.rs:275-369, tests/engine_integration.rs:171-251)."""

@@ -335,10 +335,14 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
     bool first = true;
     while (!w.done()) {
       const int n = w.count();
+      // Every warp waits for its barrier of this stage, also when it has no tile in it (the
+      // producer completes that phase with a plain arrive): a warp that skipped the wait could
+      // run more than one phase ahead of the producer, pass a later parity test too early
+      // and release the stage twice.
+      if (!mbar_wait(&full[slot * NW + warp], ph, abort_flag)) break;
+      if (warp == 0 && first) TRACE(4);
+      first = false;
       if (warp < n) {
-        if (!mbar_wait(&full[slot * NW + warp], ph, abort_flag)) break;
-        if (warp == 0 && first) TRACE(4);
-        first = false;
         const int kt = (w.ku + warp) * GROUP;
         int left = a.ktiles - kt;
         if (left > GROUP) left = GROUP;

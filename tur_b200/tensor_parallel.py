@@ -64,14 +64,17 @@ def shard_of(w: Weight, tp: int, rank: int, row_unit: int = 16) -> Shard:
     return Shard((0, w.n), (s * unit, c * unit), "row")
 
 
-def shard_blocks(blocks: np.ndarray, w: Weight, sh: Shard) -> np.ndarray:
-    """Wire-format bytes [n, row_bytes] of the full weight -> bytes of the shard."""
+def shard_blocks(blocks, w: Weight, sh: Shard):
+    """Wire-format bytes [n, row_bytes] of the full weight (numpy array or torch uint8 tensor,
+    host or device) -> contiguous bytes of the shard, same container type."""
     be, bb = BLOCK[w.dtype]
-    full = np.ascontiguousarray(blocks).reshape(w.n, (w.k // be) * bb)
+    full = blocks.reshape(w.n, (w.k // be) * bb)
     if sh.parallel == "column":
-        return np.ascontiguousarray(full[sh.rows[0]: sh.rows[0] + sh.rows[1]])
-    b0, nb = sh.cols[0] // be, sh.cols[1] // be
-    return np.ascontiguousarray(full[:, b0 * bb: (b0 + nb) * bb])
+        part = full[sh.rows[0]: sh.rows[0] + sh.rows[1]]
+    else:
+        b0, nb = sh.cols[0] // be, sh.cols[1] // be
+        part = full[:, b0 * bb: (b0 + nb) * bb]
+    return part.contiguous() if hasattr(part, "contiguous") else np.ascontiguousarray(part)
 
 
 class TPLinear:
