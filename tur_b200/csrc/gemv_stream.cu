@@ -107,7 +107,8 @@ struct StreamArgs {
   int nparts;
   int ktiles, k;
   int KU;               // units (tiles; groups of 4 tiles for Q8_0) per row-tile
-  int split_q, split_r; // CTA b owns units [b*q + min(b,r), (b+1)*q + min(b+1,r))
+  int split_q, split_r; // CTA b owns units [b*q + min(b,r), (b+1)*q + min(b+1,r)), clamped to total_units
+  int total_units;
   const void* x;        // activations of the pass (first row of the pass), f32 or bf16   [FUSED]
   int x_is_bf16;
   ActPack gact;         // planes in global scratch, already offset to the pass's first row [!FUSED]
@@ -191,7 +192,10 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
   if (warp == 0) TRACE(0);
   const int KU = a.KU;
   const int G = gridDim.x, b = blockIdx.x;
-  auto start_of = [&](int bb) { return bb * a.split_q + (bb < a.split_r ? bb : a.split_r); };
+  auto start_of = [&](int bb) {
+    const int u = bb * a.split_q + (bb < a.split_r ? bb : a.split_r);
+    return u < a.total_units ? u : a.total_units;
+  };
   const int u0 = start_of(b), u1 = start_of(b + 1);
 
   if (threadIdx.x == 0) {
@@ -562,8 +566,29 @@ static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const
     if (fused && share_div == 3 && stages_for(true, ctas_per_sm, rows0, mg0) < 2) share_div = 2;
     if (fused && stages_for(true, ctas_per_sm, rows0, mg0) < 2) fused = false;
   }
-  int grid = sm_count * ctas_per_sm;
-  if ((int64_t)grid > T) grid = (int)T;
+  // Work split. Whole row-tiles per CTA when that keeps most CTA slots busy (or the problem
+  // is small): no row-tile is shared, so no partial sums cross CTAs. Otherwise an even split
+  // in tiles, with the hand-over of split row-tiles. Depends on the shape only, never on M.
+  const int slots = sm_count * ctas_per_sm;
+  const int row_tiles_all = rt_begin[nparts];
+  int grid = slots, split_q, split_r;
+  {
+    const int per = (row_tiles_all + slots - 1) / slots;
+    const int ga = (row_tiles_all + per - 1) / per;
+    static const int split_env = getenv("TURQ_GEMV_SPLIT") ? atoi(getenv("TURQ_GEMV_SPLIT")) : -1;
+    bool aligned = ga * 10 >= slots * 7 || T <= (int64_t)slots * 24;
+    if (split_env == 0) aligned = false;
+    if (split_env == 1) aligned = true;
+    if (aligned) {
+      grid = ga;
+      split_q = per * KU;
+      split_r = 0;
+    } else {
+      if ((int64_t)grid > T) grid = (int)T;
+      split_q = (int)(T / grid);
+      split_r = (int)(T % grid);
+    }
+  }
   const size_t x_es = x_dtype == TQ_BF16 ? 2 : 4;
   ActPackPlan plan = plan_act_pack(fmt, m, k);
   if (!fused) {
@@ -586,8 +611,9 @@ static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const
     a.ktiles = ktiles;
     a.k = (int)k;
     a.KU = KU;
-    a.split_q = (int)(T / grid);
-    a.split_r = (int)(T % grid);
+    a.split_q = split_q;
+    a.split_r = split_r;
+    a.total_units = (int)T;
     a.x = static_cast<const uint8_t*>(x) + (size_t)m0 * k * x_es;
     a.x_is_bf16 = x_dtype == TQ_BF16;
     if (!fused) {
