@@ -199,7 +199,7 @@ def run_gpu(args):
         layers.append([(w, QMatMul.from_arc(QTensor.new(b, GgmlDType(w.dtype), (w.n, w.k), ctx=ctxs[lanes[w.name] % n_lanes])))
                        for w, b in protos])
     head = None
-    if wl.head is not None:
+    if wl.head is not None and not args.no_head:
         hb = torch.from_numpy(gen_weight_blocks(wl.head, SEED + 999)).to(dev)
         head = (wl.head, QMatMul.from_arc(QTensor.new(hb, GgmlDType(wl.head.dtype), (wl.head.n, wl.head.k))))
         del hb
@@ -208,8 +208,8 @@ def run_gpu(args):
 
     srcs = sorted({(w.source, w.k) for w in wl.per_layer})
     x_host = {s: torch.from_numpy(gen_activations(m, k, SEED + 10**6 + m + j)).pin_memory() for j, (s, k) in enumerate(srcs)}
-    x_dev = {s: t.to(dev) for s, t in x_host.items()}
-    all_w = list(wl.per_layer) + ([wl.head] if wl.head else [])
+    x_dev = {s: (t.to(dev).to(torch.bfloat16) if args.xdtype == "bf16" else t.to(dev)) for s, t in x_host.items()}
+    all_w = list(wl.per_layer) + ([wl.head] if head else [])
     y_dev = {w.name: torch.empty((m, w.n), dtype=torch.float32, device=dev) for w in all_w}
     y_host = {w.name: torch.empty((m, w.n), dtype=torch.float32).pin_memory() for w in all_w}
 
@@ -350,21 +350,26 @@ def run_gpu(args):
             dist.destroy_process_group()
         return
 
-    total_bytes = wl.total_bytes() * world
+    head_w = wl.head if head else None
+    pass_bytes = wl.layers * wl.layer_bytes() + (head_w.nbytes if head_w else 0)
+    pass_flops = m * (wl.layers * sum(2 * w.n * w.k for w in wl.per_layer) + (2 * head_w.n * head_w.k if head_w else 0))
+    total_bytes = pass_bytes * world
     value = total_bytes * args.steps / (ms * 1e-3) / 1e9
     peak, peak_kind = measured_peaks()
     achieved = alg_bytes / (dom_us * 1e-6) / 1e9
     traffic = NCU_TRAFFIC_BYTES.get((dom.name, wl.name))
-    h2d = sum(m * w.k * 4 for w in wl.per_layer) * wl.layers + (m * wl.head.k * 4 if wl.head else 0)
-    d2h = sum(m * w.n * 4 for w in wl.per_layer) * wl.layers + (m * wl.head.n * 4 if wl.head else 0)
+    h2d = sum(m * w.k * 4 for w in wl.per_layer) * wl.layers + (m * head_w.k * 4 if head_w else 0)
+    d2h = sum(m * w.n * 4 for w in wl.per_layer) * wl.layers + (m * head_w.n * 4 if head_w else 0)
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "int8" if mode in (Mode.INT8_ACT, Mode.AUTO) else "f32", "data": "synthetic",
+        "dtype": ("f16" if mode == Mode.TENSOR_CORE or (mode == Mode.AUTO and m > 16) else
+                  "int8" if mode in (Mode.INT8_ACT, Mode.AUTO) else "f32"), "data": "synthetic",
         "config": {
             "workload": f"{wl.name}: {wl.description}, decode M={m}, {wl.layers} layers x 7 linears"
-                        + (" + lm_head" if wl.head else ""),
-            "mode": mode.name, "weight_bytes_per_step_per_gpu": wl.total_bytes(), "parallelism": f"replicas x{world}",
+                        + (" + lm_head" if head_w else ""),
+            "mode": mode.name, "x_dtype": args.xdtype, "weight_bytes_per_step_per_gpu": pass_bytes,
+            "tflops": pass_flops * world * args.steps / (ms * 1e-3) / 1e12, "parallelism": f"replicas x{world}",
             "l2": "weights per pass exceed L2 (distinct buffers per layer); CUDA-graph replay per step",
             "streams": "one" if n_lanes == 1 else "attn_v beside attn_q|k on a second stream (own context)",
             "multi_weight_launch": not args.no_multi,
@@ -552,6 +557,8 @@ def main():
     ap.add_argument("--no-multi", action="store_true", help="one launch per weight (no q|k, gate|up multi-weight launches)")
     ap.add_argument("--parallel", action="store_true", help="issue attn_v on a second stream beside attn_q|k")
     ap.add_argument("--no-graph", action="store_true", help="tensor-parallel arm: launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--xdtype", default="f32", choices=["f32", "bf16"], help="activation dtype on the device (prefill configs use bf16)")
+    ap.add_argument("--no-head", action="store_true", help="leave the lm_head out of the pass (prefill evaluates it for one token only)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

@@ -133,12 +133,13 @@ int32_t turq_ctx_create(int32_t device, turq_ctx** out) {
   cudaDeviceProp prop;
   if (cudaSetDevice(device) != cudaSuccess || cudaGetDeviceProperties(&prop, device) != cudaSuccess ||
       cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking) != cudaSuccess ||
-      cudaMalloc(reinterpret_cast<void**>(&ctx->dev_status), sizeof(int)) != cudaSuccess ||
-      cudaMemset(ctx->dev_status, 0, sizeof(int)) != cudaSuccess) {
+      cudaHostAlloc(reinterpret_cast<void**>(&ctx->host_status), sizeof(int), cudaHostAllocMapped) != cudaSuccess ||
+      cudaHostGetDevicePointer(reinterpret_cast<void**>(&ctx->dev_status), ctx->host_status, 0) != cudaSuccess) {
     cudaGetLastError();
     delete ctx;
     return TURQ_E_CUDA;
   }
+  *ctx->host_status = 0;
   ctx->sm_count = prop.multiProcessorCount;
   const size_t ws_bytes = turq::gemv_workspace_bytes(ctx->sm_count);
   if (cudaMalloc(reinterpret_cast<void**>(&ctx->gemv_ws), ws_bytes) != cudaSuccess ||
@@ -162,7 +163,7 @@ int32_t turq_ctx_destroy(turq_ctx* ctx) {
   cudaDeviceSynchronize();
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->io) cudaFree(ctx->io);
-  if (ctx->dev_status) cudaFree(ctx->dev_status);
+  if (ctx->host_status) cudaFreeHost(ctx->host_status);
   if (ctx->gemv_ws) cudaFree(ctx->gemv_ws);
   if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
   delete ctx;
@@ -176,12 +177,15 @@ int32_t turq_ctx_poll_status(turq_ctx* ctx, void* stream) {
   if (!ctx) return TURQ_E_INVALID_ARG;
   TQ_CUDA(ctx, cudaSetDevice(ctx->device));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  int st = 0;
-  TQ_CUDA(ctx, cudaMemcpyAsync(&st, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost, s));
   TQ_CUDA(ctx, cudaStreamSynchronize(s));
+  // The status word lives in mapped host memory: kernels store to it (rarely), the host reads it
+  // here without a copy.
+  const int st = *static_cast<volatile int*>(ctx->host_status);
   if (st != 0) {
-    TQ_CUDA(ctx, cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), s));
-    TQ_CUDA(ctx, cudaStreamSynchronize(s));
+    *static_cast<volatile int*>(ctx->host_status) = 0;
+    // a kernel that gave up may have left hand-over flags or claim counters set
+    cudaMemsetAsync(ctx->gemv_ws, 0, turq::gemv_workspace_bytes(ctx->sm_count), s);
+    cudaStreamSynchronize(s);
     return fail(ctx, st, "a kernel gave up a bounded device-side wait (status %d)", st);
   }
   return TURQ_OK;
@@ -329,6 +333,16 @@ int32_t turq_quantize_act(turq_ctx* ctx, int32_t fmt, const void* dev_x, int32_t
   return TURQ_OK;
 }
 
+// TURQ_MODE_AUTO: the integer GEMV for decode batches, the tcgen05 GEMM for prefill. In between
+// (17..64 rows) the GEMM's 128-row tiles only pay off when there are enough of them to occupy
+// the GPU; measured on B200, the integer path (32 rows per pass) is ahead up to 32 rows for
+// every shape and up to 64 rows for weights with fewer 128-row tiles than half the SMs.
+static int32_t auto_mode(const turq_ctx* ctx, int64_t n_rows, int64_t n_cols, int64_t m) {
+  if (m <= 32 || n_cols % 64 != 0) return TURQ_MODE_INT8_ACT;
+  if (m <= 64 && (n_rows + 127) / 128 < ctx->sm_count / 2) return TURQ_MODE_INT8_ACT;
+  return TURQ_MODE_TENSOR_CORE;
+}
+
 int32_t turq_qmatmul(turq_ctx* ctx, const turq_qtensor* qt, const void* dev_x, int32_t x_dtype, int64_t m,
                      float* dev_y, int32_t mode, const float* dev_bias, void* stream) {
   if (!ctx || !qt || !dev_x || !dev_y) return fail(ctx, TURQ_E_INVALID_ARG, "null argument");
@@ -337,7 +351,7 @@ int32_t turq_qmatmul(turq_ctx* ctx, const turq_qtensor* qt, const void* dev_x, i
   if (m > INT32_MAX / 2) return fail(ctx, TURQ_E_SHAPE, "m=%lld too large", (long long)m);
   if (qt->device != ctx->device) return fail(ctx, TURQ_E_INVALID_ARG, "tensor lives on device %d, context on %d", qt->device, ctx->device);
   if ((uintptr_t)dev_x % 16 != 0 || (uintptr_t)dev_y % 4 != 0) return fail(ctx, TURQ_E_ALIGN, "dev_x must be 16-byte aligned");
-  if (mode == TURQ_MODE_AUTO) mode = (m <= 16 || qt->n_cols % 64 != 0) ? TURQ_MODE_INT8_ACT : TURQ_MODE_TENSOR_CORE;
+  if (mode == TURQ_MODE_AUTO) mode = auto_mode(ctx, qt->n_rows, qt->n_cols, m);
   if (mode == TURQ_MODE_TENSOR_CORE && qt->n_cols % 64 != 0)
     return fail(ctx, TURQ_E_SHAPE, "the tensor-core mode needs in-features to be a multiple of 64 (got %lld)", (long long)qt->n_cols);
   TQ_CUDA(ctx, cudaSetDevice(ctx->device));
@@ -379,7 +393,11 @@ int32_t turq_qmatmul_multi(turq_ctx* ctx, int32_t count, const turq_qtensor* con
   bool same = true;
   for (int i = 1; i < count; i++) same = same && qts[i]->dtype == qts[0]->dtype && qts[i]->device == qts[0]->device;
   int32_t eff = mode;
-  if (eff == TURQ_MODE_AUTO) eff = (m <= 16 || qts[0]->n_cols % 64 != 0) ? TURQ_MODE_INT8_ACT : TURQ_MODE_TENSOR_CORE;
+  if (eff == TURQ_MODE_AUTO) {
+    int64_t rows_all = 0;
+    for (int i = 0; i < count; i++) rows_all += qts[i]->n_rows;
+    eff = auto_mode(ctx, rows_all, qts[0]->n_cols, m);
+  }
   if (!same || eff != TURQ_MODE_INT8_ACT || count == 1) {
     for (int i = 0; i < count; i++) {
       int32_t st = turq_qmatmul(ctx, qts[i], dev_x, x_dtype, m, dev_ys[i], mode, dev_biases ? dev_biases[i] : nullptr, stream);

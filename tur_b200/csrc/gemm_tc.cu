@@ -404,7 +404,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(TMEM_COLS) : "memory");
   }
-  if (threadIdx.x == 0 && *abort_flag) atomicExch(a.status, 7 /* TURQ_E_TIMEOUT */);
+  if (threadIdx.x == 0 && *abort_flag) {
+    *reinterpret_cast<volatile int*>(a.status) = 7;  // TURQ_E_TIMEOUT; the word may be mapped host memory
+    __threadfence_system();
+  }
 }
 
 // x [m, k] (f32 / bf16) -> f16 [m, k] with a per-row power-of-two scale that is 1 unless the

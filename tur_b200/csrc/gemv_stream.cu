@@ -109,9 +109,9 @@ struct StreamArgs {
   int KU;               // units (tiles; groups of 4 tiles for Q8_0) per row-tile
   int split_q, split_r; // CTA b owns units [b*q + min(b,r), (b+1)*q + min(b+1,r)), clamped to total_units
   int total_units;
-  const void* x;        // activations of the pass (first row of the pass), f32 or bf16   [FUSED]
+  const void* x;        // activations of the pass (first row of the pass), f32 or bf16   [ACT_FUSED]
   int x_is_bf16;
-  ActPack gact;         // planes in global scratch, already offset to the pass's first row [!FUSED]
+  ActPack gact;         // planes in global scratch, already offset to the pass's first row [other modes]
   int rows;             // valid activation rows in this pass (<= 8 * MG)
   float* partial;       // [grid][MG * 128]: partial sums of a CTA's leading split row-tile
   int* flags;           // [grid], all zero between launches
@@ -121,7 +121,7 @@ struct StreamArgs {
   SmemPlan sp;
 };
 
-inline SmemPlan plan_smem(int dtype, int mg, bool fused, int rows_cap, int k, int stages, int stage_bytes) {
+inline SmemPlan plan_smem(int dtype, int mg, bool fused /* planes in shared memory */, int rows_cap, int k, int stages, int stage_bytes) {
   auto up = [](int v) { return (v + 127) & ~127; };
   SmemPlan p{};
   p.ring = 0;
@@ -132,15 +132,15 @@ inline SmemPlan plan_smem(int dtype, int mg, bool fused, int rows_cap, int k, in
     off = up(off + rows_cap * p.qs_stride);
     p.act_dsc = off;
     off = up(off + rows_cap * (k / (dtype == TQ_Q8_0 ? 32 : 256)) * 4);
-    p.act_bs16 = off;
-    if (dtype != TQ_Q8_0) off = up(off + rows_cap * (k / 16) * 2);
+    p.act_bs16 = off;  // Q6_K reads the sums of 16, Q4_K / Q5_K the sums of 32
+    if (dtype == TQ_Q6_K) off = up(off + rows_cap * (k / 16) * 2);
     p.act_bs32 = off;
-    if (dtype != TQ_Q8_0) off = up(off + rows_cap * (k / 32) * 2);
+    if (dtype == TQ_Q4_K || dtype == TQ_Q5_K) off = up(off + rows_cap * (k / 32) * 2);
   }
   p.red = off;
   off = up(off + RED_SLOTS * NW * mg * 128 * 4);
   p.bars = off;
-  off += (MAX_STAGES * NW + MAX_STAGES + 2 * RED_SLOTS) * 8 + 16;
+  off += (MAX_STAGES * NW + MAX_STAGES + 2 * RED_SLOTS) * 8 + 8 /* abort flag */ + 8 /* act_full */ + 16;
   p.total = off;
   return p;
 }
@@ -174,7 +174,12 @@ struct StageWalk {
   }
 };
 
-template <int DT, int MG, bool FUSED>
+// Where the consumer warps find the quantized activation planes
+constexpr int ACT_GLOBAL = 0;  // in global scratch (written by a preceding quantization launch)
+constexpr int ACT_FUSED = 1;   // quantized by this CTA into shared memory
+constexpr int ACT_STAGED = 2;  // bulk-copied from global scratch into shared memory at CTA start
+
+template <int DT, int MG, int ACT>
 __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(const __grid_constant__ StreamArgs a) {
   constexpr int TB = TileGeom<DT>::BYTES;
   constexpr int GROUP = TileGeom<DT>::GROUP;
@@ -186,6 +191,7 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
   uint64_t* red_full = empty + MAX_STAGES;
   uint64_t* red_empty = red_full + RED_SLOTS;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(red_empty + RED_SLOTS);
+  uint64_t* act_full = red_empty + RED_SLOTS + 1;  // ACT_STAGED: the planes have landed
   float* red = reinterpret_cast<float*>(smem + sp.red);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -207,6 +213,7 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
       mbar_init(&red_full[s], NW);
       mbar_init(&red_empty[s], 1);
     }
+    mbar_init(act_full, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -221,6 +228,21 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
   if (warp == NW) {
     // ------------------------------------------------------------ producer warp
     if (lane == 0) {
+      if constexpr (ACT == ACT_STAGED) {
+        // the activation planes of this pass: one copy per row of quants (the shared-memory
+        // rows are padded), one per plane of scales / sums (sizes rounded up to 16 bytes; the
+        // planes are padded on both sides)
+        const int nb = DT == TQ_Q8_0 ? a.k >> 5 : a.k >> 8;
+        const uint32_t dsc_bytes = ((uint32_t)(a.rows * nb * 4) + 15u) & ~15u;
+        const uint32_t sum_bytes = DT == TQ_Q8_0 ? 0u
+                                   : (((uint32_t)(a.rows * (DT == TQ_Q6_K ? a.k >> 4 : a.k >> 5) * 2) + 15u) & ~15u);
+        mbar_expect_tx(act_full, (uint32_t)(a.rows * a.k) + dsc_bytes + sum_bytes);
+        for (int r = 0; r < a.rows; r++)
+          bulk_g2s(smem + sp.act_qs + r * sp.qs_stride, a.gact.qs + (size_t)r * a.k, (uint32_t)a.k, act_full);
+        bulk_g2s(smem + sp.act_dsc, a.gact.dsc, dsc_bytes, act_full);
+        if constexpr (DT == TQ_Q6_K) bulk_g2s(smem + sp.act_bs16, a.gact.bs16, sum_bytes, act_full);
+        if constexpr (DT == TQ_Q4_K || DT == TQ_Q5_K) bulk_g2s(smem + sp.act_bs32, a.gact.bs32, sum_bytes, act_full);
+      }
       StageWalk w;
       w.init(u0, u1, KU);
       int slot = 0;
@@ -254,7 +276,15 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (warp == 0) TRACE(2);
     ActPack act = a.gact;
-    if constexpr (FUSED) {
+    if constexpr (ACT == ACT_STAGED) {
+      mbar_wait(act_full, 0u, abort_flag);
+      act.qs = reinterpret_cast<const int8_t*>(smem + sp.act_qs);
+      act.dsc = reinterpret_cast<const float*>(smem + sp.act_dsc);
+      act.bs16 = reinterpret_cast<const int16_t*>(smem + sp.act_bs16);
+      act.bs32 = reinterpret_cast<const int16_t*>(smem + sp.act_bs32);
+      act.qs_stride = sp.qs_stride;
+    }
+    if constexpr (ACT == ACT_FUSED) {
       int8_t* sqs = reinterpret_cast<int8_t*>(smem + sp.act_qs);
       float* sdsc = reinterpret_cast<float*>(smem + sp.act_dsc);
       int16_t* sb16 = reinterpret_cast<int16_t*>(smem + sp.act_bs16);
@@ -312,8 +342,11 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
           if (has) {
             *reinterpret_cast<uint4*>(sqs + row * sp.qs_stride + blk * 256 + hl * 16) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
             if (hl == 0) sdsc[row * nblk + blk] = d;
-            sb16[row * (a.k >> 4) + blk * 16 + hl] = (int16_t)s16;
-            if ((hl & 1) == 0) sb32[row * (a.k >> 5) + blk * 8 + (hl >> 1)] = (int16_t)s32;
+            if constexpr (DT == TQ_Q6_K) {
+              sb16[row * (a.k >> 4) + blk * 16 + hl] = (int16_t)s16;
+            } else {
+              if ((hl & 1) == 0) sb32[row * (a.k >> 5) + blk * 8 + (hl >> 1)] = (int16_t)s32;
+            }
           }
         }
       }
@@ -473,7 +506,10 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
   if (*abort_flag) {
     // a wait ran out: give copies still in flight time to land in this CTA's shared memory
     for (int i = 0; i < 64; i++) __nanosleep(2000);
-    if (threadIdx.x == 0) atomicExch(a.status, 7 /* TURQ_E_TIMEOUT */);
+    if (threadIdx.x == 0) {
+      *reinterpret_cast<volatile int*>(a.status) = 7;  // TURQ_E_TIMEOUT; the word may be mapped host memory
+      __threadfence_system();
+    }
   }
 }
 
@@ -491,11 +527,16 @@ static int smem_budget() {
   return g_smem_optin;
 }
 
+// In-kernel quantization is redundant work in every CTA and every CTA reads the same few
+// cache lines of x: one pass (16 Q8_K blocks, or 64 Q8_0 blocks, per CTA) costs about as much
+// as the weight ring takes to fill, so it is only used for one row or up to two passes.
 bool gemv_int8_fuses_act(int dtype, int64_t m, int64_t k) {
   if (m > 8) return false;
   const int64_t plane = m * (k + 32) + m * (k / 16) * 4 + 1024;
-  (void)dtype;
-  return plane <= 64 * 1024;
+  if (plane > 64 * 1024) return false;
+  static const int max_passes = getenv("TURQ_GEMV_FUSE_PASSES") ? atoi(getenv("TURQ_GEMV_FUSE_PASSES")) : 2;
+  const int64_t passes = dtype == TQ_Q8_0 ? (m * ((k / 32 + 7) / 8) + NW - 1) / NW : (m * (k / 256) + 2 * NW - 1) / (2 * NW);
+  return m == 1 || passes <= max_passes;
 }
 
 // partial sums [up to 4 CTAs per SM][4 groups of 8 rows][128] + one flag per CTA
@@ -503,13 +544,13 @@ size_t gemv_workspace_bytes(int sms) { return (size_t)sms * 4 * 4 * 128 * 4 + (s
 
 // Launches with the programmatic-stream-serialization attribute (the kernel orders itself
 // against its predecessor with griddepcontrol.wait).
-template <int DT, int MG, bool FUSED>
+template <int DT, int MG, int ACT>
 static cudaError_t launch_one(StreamArgs a, int grid, int smem_bytes, cudaStream_t s) {
   static int configured_dev = -1;  // per instantiation; the attribute is per device function
   int dev = 0;
   cudaGetDevice(&dev);
   if (configured_dev != dev) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<DT, MG, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<DT, MG, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          smem_budget());
     if (e != cudaSuccess) return e;
     configured_dev = dev;
@@ -525,7 +566,7 @@ static cudaError_t launch_one(StreamArgs a, int grid, int smem_bytes, cudaStream
   cfg.attrs = attr;
   static const int pdl = getenv("TURQ_GEMV_PDL") ? atoi(getenv("TURQ_GEMV_PDL")) : 0;
   cfg.numAttrs = pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<DT, MG, FUSED>, a);
+  return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<DT, MG, ACT>, a);
 }
 
 template <int DT>
@@ -545,27 +586,32 @@ static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const
   // The tile split (hence the summation order) must not depend on M: always two CTAs per SM.
   static const int cps_env = getenv("TURQ_GEMV_CPS") ? atoi(getenv("TURQ_GEMV_CPS")) : 0;
   const int ctas_per_sm = cps_env > 0 ? cps_env : 2;
-  // ...but sized, when the activation planes allow it, so that a third CTA (of the next
-  // launch) fits beside them while they drain
-  int share_div = m <= 8 ? 3 : 2;
+  // Each CTA may use half of the SM's shared memory.
+  static const int share_env = getenv("TURQ_GEMV_SHARE") ? atoi(getenv("TURQ_GEMV_SHARE")) : 0;
+  const int share_div = share_env > 0 ? share_env : 2;
   const int fmt = DT == TQ_Q8_0 ? TQ_Q8_0 : TQ_Q8_K;
-  bool fused = gemv_int8_fuses_act(DT, m, k);
   const int stage_bytes = NW * UNIT_BYTES;
   // Shared memory: the ring needs at least two stages next to the activation planes. If
-  // that does not fit a CTA's share of the SM, in-kernel quantization is given up.
-  auto stages_for = [&](bool f, int cps, int rows, int mg) {
+  // that does not fit a CTA's share of the SM, the planes stay in global memory.
+  auto stages_for = [&](bool planes_in_smem, int cps, int rows, int mg) {
     if (cps < share_div) cps = share_div;
     const int share = (smem_budget() + 1024) / cps - 1024;  // 1 KB per CTA is reserved by the system
     int st = MAX_STAGES;
     for (; st >= 2; st--)
-      if (plan_smem(DT, mg, f, rows, (int)k, st, stage_bytes).total <= share) break;
+      if (plan_smem(DT, mg, planes_in_smem, rows, (int)k, st, stage_bytes).total <= share) break;
     return st;
   };
+  // Activation planes: quantized in the kernel (few rows), else quantized once by a launch of
+  // their own and then either bulk-copied into every CTA's shared memory (up to 16 rows, when
+  // they fit beside a two-stage ring) or read from global memory by the MMA loop.
+  int act_mode = gemv_int8_fuses_act(DT, m, k) ? ACT_FUSED : ACT_GLOBAL;
   {
     const int rows0 = (int)(m < 32 ? m : 32), mg0 = rows0 <= 8 ? 1 : rows0 <= 16 ? 2 : 4;
-    if (fused && share_div == 3 && stages_for(true, ctas_per_sm, rows0, mg0) < 2) share_div = 2;
-    if (fused && stages_for(true, ctas_per_sm, rows0, mg0) < 2) fused = false;
+    if (act_mode == ACT_FUSED && stages_for(true, ctas_per_sm, rows0, mg0) < 2) act_mode = ACT_GLOBAL;
+    static const int stage_env = getenv("TURQ_GEMV_STAGED") ? atoi(getenv("TURQ_GEMV_STAGED")) : 1;
+    if (act_mode == ACT_GLOBAL && m <= 16 && stage_env && stages_for(true, ctas_per_sm, rows0, mg0) >= 2) act_mode = ACT_STAGED;
   }
+  const bool fused = act_mode == ACT_FUSED, planes_in_smem = act_mode != ACT_GLOBAL;
   // Work split. Whole row-tiles per CTA when that keeps most CTA slots busy (or the problem
   // is small): no row-tile is shared, so no partial sums cross CTAs. Otherwise an even split
   // in tiles, with the hand-over of split row-tiles. Depends on the shape only, never on M.
@@ -628,21 +674,23 @@ static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const
     a.partial = reinterpret_cast<float*>(workspace);
     a.flags = reinterpret_cast<int*>(workspace + (size_t)sm_count * 4 * 4 * 128 * 4);
     a.status = status;
-    const int stages = stages_for(fused, ctas_per_sm, rows, mg);
+    const int stages = stages_for(planes_in_smem, ctas_per_sm, rows, mg);
     if (stages < 2) return cudaErrorInvalidConfiguration;
-    const SmemPlan sp = plan_smem(DT, mg, fused, rows, (int)k, stages, stage_bytes);
+    const SmemPlan sp = plan_smem(DT, mg, planes_in_smem, rows, (int)k, stages, stage_bytes);
     a.stages = stages;
     a.stage_bytes = stage_bytes;
     a.sp = sp;
     cudaError_t e;
-    if (fused) {
-      e = launch_one<DT, 1, true>(a, grid, sp.total, s);
+    if (act_mode == ACT_FUSED) {
+      e = launch_one<DT, 1, ACT_FUSED>(a, grid, sp.total, s);
+    } else if (act_mode == ACT_STAGED) {
+      e = mg == 1 ? launch_one<DT, 1, ACT_STAGED>(a, grid, sp.total, s) : launch_one<DT, 2, ACT_STAGED>(a, grid, sp.total, s);
     } else if (mg == 1) {
-      e = launch_one<DT, 1, false>(a, grid, sp.total, s);
+      e = launch_one<DT, 1, ACT_GLOBAL>(a, grid, sp.total, s);
     } else if (mg == 2) {
-      e = launch_one<DT, 2, false>(a, grid, sp.total, s);
+      e = launch_one<DT, 2, ACT_GLOBAL>(a, grid, sp.total, s);
     } else {
-      e = launch_one<DT, 4, false>(a, grid, sp.total, s);
+      e = launch_one<DT, 4, ACT_GLOBAL>(a, grid, sp.total, s);
     }
     if (launches) (*launches)++;
     if (e != cudaSuccess) return e;

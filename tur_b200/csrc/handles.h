@@ -13,7 +13,8 @@ struct turq_ctx {
   size_t scratch_bytes = 0;
   uint8_t* io = nullptr;  // device staging for the host-buffer entry (x, y, bias)
   size_t io_bytes = 0;
-  int* dev_status = nullptr;  // status word written by kernels with bounded waits
+  int* host_status = nullptr;  // status word in mapped pinned host memory, written by kernels with bounded waits
+  int* dev_status = nullptr;   // the same word's device address
   uint8_t* gemv_ws = nullptr;  // split row-tile workspace of the streaming GEMV (zeroed once)
   cudaStream_t own_stream = nullptr;
   int64_t launches = 0;
