@@ -39,6 +39,9 @@ struct ActOut {
 // One warp per 256-element block: lane owns elements 8*lane .. 8*lane+7.
 __global__ void __launch_bounds__(128) quant_q8k_kernel(const void* __restrict__ x, int is_bf16, int64_t m,
                                                         int64_t k, ActOut out) {
+  // A GEMV launched with programmatic stream serialization may start (and prefetch weights)
+  // while this grid runs; it waits for this grid's completion before it reads the planes.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int lane = threadIdx.x & 31;
   const int64_t nblk = k >> 8;
   const int64_t total = m * nblk;
@@ -71,6 +74,9 @@ __global__ void __launch_bounds__(128) quant_q8k_kernel(const void* __restrict__
 // Four lanes per 32-element block; a warp covers 8 consecutive blocks of one row.
 __global__ void __launch_bounds__(128) quant_q8_0_kernel(const void* __restrict__ x, int is_bf16, int64_t m,
                                                          int64_t k, ActOut out) {
+  // A GEMV launched with programmatic stream serialization may start (and prefetch weights)
+  // while this grid runs; it waits for this grid's completion before it reads the planes.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int lane = threadIdx.x & 31;
   const int64_t nblk = k >> 5;
   const int64_t groups = (nblk + 7) >> 3;  // warp-sized groups of 8 blocks per row

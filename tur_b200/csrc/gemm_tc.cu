@@ -16,6 +16,7 @@
 // MMA roles: A = weights (rows = TMEM lanes), B = activations (columns).
 // Every mbarrier wait is bounded; on expiry the CTA records TURQ_E_TIMEOUT, releases its TMEM
 // and returns.
+#include <cstdlib>
 #include <cuda.h>
 #include <cuda_fp16.h>
 
@@ -78,11 +79,6 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr) {
 // byte offset of 16-byte chunk `ch` (8 f16 along k) of tile row r in the swizzled layout
 __device__ __forceinline__ uint32_t swz(int r, int ch) {
   return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((ch ^ (r & 7)) << 4));
-}
-
-__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
-  __half2 h = __floats2half2_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&h);
 }
 
 // ---- dequantization to f16 with packed half arithmetic (two elements per instruction).
@@ -166,13 +162,21 @@ __device__ __forceinline__ void stage_dequant_store(const StageRegs<DT>& r, int 
 #pragma unroll
     for (int hr = 0; hr < 2; hr++) {
       const uint4 hdr = r.hdr[hr];
-      const float d = f16_bits_to_f32(hdr.x), dmin = f16_bits_to_f32(hdr.x >> 16);
+      // Sub-block scales in half arithmetic only (no int->float / float->half conversions, which
+      // share one narrow pipe): d * sc is exact in f32, so one f16 multiply rounds it the same way.
+      const __half2 dd = u2h2(__byte_perm(hdr.x, 0u, 0x1010)), mm = u2h2(__byte_perm(hdr.x, 0u, 0x3232));
+      // 6-bit scales / mins of sub-blocks 0..3 or 4..7, one per byte; this stage needs bytes
+      // 2*(i&1) and 2*(i&1)+1
+      const uint32_t scw = i < 2 ? (hdr.y & 0x3F3F3F3Fu) : ((hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u));
+      const uint32_t mnw = i < 2 ? (hdr.z & 0x3F3F3F3Fu) : (((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u));
+      const __half2 sc2 = __hsub2((i & 1) ? pair23(scw) : pair01(scw), off);
+      const __half2 mn2 = __hsub2((i & 1) ? pair23(mnw) : pair01(mnw), off);
+      const __half2 dl2 = __hmul2(dd, sc2), ml2 = __hneg2(__hmul2(mm, mn2));
 #pragma unroll
       for (int nib = 0; nib < 2; nib++) {
         const int j = 2 * i + nib;
-        int sc, mn;
-        tq_k4_scale_min(hdr.y, hdr.z, hdr.w, j, &sc, &mn);
-        const __half2 dl = __float2half2_rn(d * (float)sc), ml = __float2half2_rn(-(dmin * (float)mn));
+        const __half2 dl = nib ? __high2half2(dl2) : __low2half2(dl2);
+        const __half2 ml = nib ? __high2half2(ml2) : __low2half2(ml2);
         uint32_t m0 = (nib ? (w[hr][0] >> 4) : w[hr][0]) & 0x0F0F0F0Fu;
         uint32_t m1 = (nib ? (w[hr][1] >> 4) : w[hr][1]) & 0x0F0F0F0Fu;
         if constexpr (DT == TQ_Q5_K) {
@@ -192,14 +196,19 @@ __device__ __forceinline__ void stage_dequant_store(const StageRegs<DT>& r, int 
     const uint32_t qlw[2][2] = {{r.ql.x, r.ql.y}, {r.ql.z, r.ql.w}};
     const uint32_t qhw[2] = {(i & 1) ? r.qh.y : r.qh.x, (i & 1) ? r.qh.w : r.qh.z};
     const __half2 off = __float2half2_rn(1056.f);  // 1024 + 32
+    const __half2 off_sc = __float2half2_rn(1152.f);  // 1024 + 128: the int8 scales are biased by xor 0x80
 #pragma unroll
     for (int hr = 0; hr < 2; hr++) {
       const int rr = g + 8 * hr;
-      const float d = f16_bits_to_f32(r.d >> (16 * hr));
+      // d * scale in half arithmetic (exact product, one rounding - as the f32 route gives)
+      const __half2 dd = u2h2(__byte_perm(r.d, 0u, hr ? 0x3232 : 0x1010));
+      const uint32_t scb = r.sc[hr] ^ 0x80808080u;
+      const __half2 dl01 = __hmul2(dd, __hsub2(pair01(scb), off_sc)), dl23 = __hmul2(dd, __hsub2(pair23(scb), off_sc));
 #pragma unroll
       for (int jj = 0; jj < 4; jj++) {
         const int tw = jj >> 1, nib = jj & 1, sh = 2 * jj;
-        const __half2 dl = __float2half2_rn(d * (float)sext_byte(r.sc[hr], jj));
+        const __half2 dlp = jj < 2 ? dl01 : dl23;
+        const __half2 dl = (jj & 1) ? __high2half2(dlp) : __low2half2(dlp);
         uint32_t m = (nib ? (qlw[hr][tw] >> 4) : qlw[hr][tw]) & 0x0F0F0F0Fu;
         m |= (sh <= 4 ? (qhw[hr] << (4 - sh)) : (qhw[hr] >> (sh - 4))) & 0x30303030u;
         // elements 16*jj + 4c .. +3 of the stage: chunk 2*jj + (c >> 1), half (c & 1)
@@ -224,8 +233,8 @@ struct GemmArgs {
   int* status;
 };
 
-// BN = activation rows per CTA (MMA N): 256 for prefill, 64 for decode batches of a few dozen
-// rows (smaller activation tiles and accumulator, two CTAs per SM).
+// BN = activation rows per CTA (MMA N): 256 for prefill (128 when that is needed to give every
+// SM a CTA), 64 for decode batches of a few dozen rows.
 template <int DT, int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
@@ -470,7 +479,7 @@ cudaError_t launch_tc_bn(const CUtensorMap& map, const GemmArgs& a, cudaStream_t
 
 template <int DT>
 cudaError_t launch_tc_dt(const CUtensorMap& map, const GemmArgs& a, int bn, cudaStream_t s) {
-  return bn == 64 ? launch_tc_bn<DT, 64>(map, a, s) : launch_tc_bn<DT, 256>(map, a, s);
+  return bn == 64 ? launch_tc_bn<DT, 64>(map, a, s) : bn == 128 ? launch_tc_bn<DT, 128>(map, a, s) : launch_tc_bn<DT, 256>(map, a, s);
 }
 
 }  // namespace
@@ -482,7 +491,6 @@ size_t gemm_tc_scratch_bytes(int64_t m, int64_t k) {
 cudaError_t launch_gemm_tc(int dtype, const uint8_t* tiles, int64_t n_rows, int64_t k, const void* x, int x_dtype,
                            int64_t m, float* y, const float* bias, uint8_t* scratch, int sm_count, cudaStream_t s,
                            int* launches, int* dev_status_word) {
-  (void)sm_count;
   if (k % BK != 0 || m <= 0 || m > INT32_MAX || k > INT32_MAX) return cudaErrorInvalidValue;
   EncodeTiledFn enc = encode_fn();
   if (!enc) return cudaErrorNotSupported;
@@ -496,7 +504,12 @@ cudaError_t launch_gemm_tc(int dtype, const uint8_t* tiles, int64_t n_rows, int6
   CUtensorMap map;
   const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)m};
   const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
-  const int bn = m <= 64 ? 64 : 256;
+  // Activation rows per CTA: 64 for decode batches; 256 for prefill, unless that leaves fewer
+  // CTAs than SMs - then 128, which doubles the CTA count for the same work.
+  static const int bn_env = getenv("TURQ_GEMM_BN") ? atoi(getenv("TURQ_GEMM_BN")) : 0;
+  int bn = m <= 64 ? 64 : 256;
+  if (bn == 256 && ((n_rows + BM - 1) / BM) * ((m + 255) / 256) < sm_count) bn = 128;
+  if (bn_env == 64 || bn_env == 128 || bn_env == 256) bn = bn_env;
   const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)bn};
   const cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xh, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,

@@ -228,10 +228,14 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
   if (warp == NW) {
     // ------------------------------------------------------------ producer warp
     if (lane == 0) {
-      if constexpr (ACT == ACT_STAGED) {
-        // the activation planes of this pass: one copy per row of quants (the shared-memory
-        // rows are padded), one per plane of scales / sums (sizes rounded up to 16 bytes; the
-        // planes are padded on both sides)
+      // ACT_STAGED: the activation planes of this pass go first - the consumers cannot start
+      // without them. They were written by the quantization launch just before this one; with
+      // programmatic stream serialization this grid is already resident (barriers set up) when
+      // that launch ends, and griddepcontrol.wait orders the copies after it.
+      // One copy per row of quants (the shared-memory rows are padded), one per plane of
+      // scales / sums (sizes rounded up to 16 bytes; the planes are padded on both sides).
+      auto copy_planes = [&]() {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         const int nb = DT == TQ_Q8_0 ? a.k >> 5 : a.k >> 8;
         const uint32_t dsc_bytes = ((uint32_t)(a.rows * nb * 4) + 15u) & ~15u;
         const uint32_t sum_bytes = DT == TQ_Q8_0 ? 0u
@@ -242,7 +246,8 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
         bulk_g2s(smem + sp.act_dsc, a.gact.dsc, dsc_bytes, act_full);
         if constexpr (DT == TQ_Q6_K) bulk_g2s(smem + sp.act_bs16, a.gact.bs16, sum_bytes, act_full);
         if constexpr (DT == TQ_Q4_K || DT == TQ_Q5_K) bulk_g2s(smem + sp.act_bs32, a.gact.bs32, sum_bytes, act_full);
-      }
+      };
+      if constexpr (ACT == ACT_STAGED) copy_planes();
       StageWalk w;
       w.init(u0, u1, KU);
       int slot = 0;
@@ -545,7 +550,7 @@ size_t gemv_workspace_bytes(int sms) { return (size_t)sms * 4 * 4 * 128 * 4 + (s
 // Launches with the programmatic-stream-serialization attribute (the kernel orders itself
 // against its predecessor with griddepcontrol.wait).
 template <int DT, int MG, int ACT>
-static cudaError_t launch_one(StreamArgs a, int grid, int smem_bytes, cudaStream_t s) {
+static cudaError_t launch_one(StreamArgs a, int grid, int smem_bytes, cudaStream_t s, bool after_quant = false) {
   static int configured_dev = -1;  // per instantiation; the attribute is per device function
   int dev = 0;
   cudaGetDevice(&dev);
@@ -564,8 +569,11 @@ static cudaError_t launch_one(StreamArgs a, int grid, int smem_bytes, cudaStream
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
+  // Always-on variant for testing (TURQ_GEMV_PDL=1); by default only the launch that follows
+  // its own quantization launch overlaps with it (TURQ_GEMV_PDL_PAIR=0 turns that off).
   static const int pdl = getenv("TURQ_GEMV_PDL") ? atoi(getenv("TURQ_GEMV_PDL")) : 0;
-  cfg.numAttrs = pdl ? 1 : 0;
+  static const int pdl_pair = getenv("TURQ_GEMV_PDL_PAIR") ? atoi(getenv("TURQ_GEMV_PDL_PAIR")) : 1;
+  cfg.numAttrs = (pdl || (after_quant && pdl_pair)) ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<DT, MG, ACT>, a);
 }
 
@@ -684,7 +692,7 @@ static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const
     if (act_mode == ACT_FUSED) {
       e = launch_one<DT, 1, ACT_FUSED>(a, grid, sp.total, s);
     } else if (act_mode == ACT_STAGED) {
-      e = mg == 1 ? launch_one<DT, 1, ACT_STAGED>(a, grid, sp.total, s) : launch_one<DT, 2, ACT_STAGED>(a, grid, sp.total, s);
+      e = mg == 1 ? launch_one<DT, 1, ACT_STAGED>(a, grid, sp.total, s, true) : launch_one<DT, 2, ACT_STAGED>(a, grid, sp.total, s, true);
     } else if (mg == 1) {
       e = launch_one<DT, 1, ACT_GLOBAL>(a, grid, sp.total, s);
     } else if (mg == 2) {
