@@ -432,7 +432,7 @@ def run_gpu_tp(args):
             layer.append((w, sh, TPLinear(w, sh, mm)))
         layers.append(layer)
     head = None
-    if wl.head is not None:
+    if wl.head is not None and not args.no_head:
         sh, b = make(wl.head, SEED + 999)
         head = (wl.head, sh, QMatMul.from_arc(QTensor.new(b, GgmlDType(wl.head.dtype), sh.shape)))
     del protos
@@ -444,7 +444,8 @@ def run_gpu_tp(args):
     for w, sh, _ in layers[0]:
         kloc = sh.shape[1]
         if (w.source, kloc) not in xs:
-            xs[(w.source, kloc)] = torch.from_numpy(gen_activations(m, kloc, SEED + 10**6 + m + len(xs))).to(dev)
+            x = torch.from_numpy(gen_activations(m, kloc, SEED + 10**6 + m + len(xs))).to(dev)
+            xs[(w.source, kloc)] = x.to(torch.bfloat16) if args.xdtype == "bf16" else x
         ys[w.name] = torch.empty((m, sh.shape[0]), dtype=torch.float32, device=dev)
     if head:
         ys["output"] = torch.empty((m, head[1].shape[0]), dtype=torch.float32, device=dev)
@@ -521,7 +522,8 @@ def run_gpu_tp(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t[0])
     if rank == 0:
-        total_bytes = wl.total_bytes()
+        total_bytes = wl.layers * wl.layer_bytes() + (wl.head.nbytes if head else 0)
+        pass_flops = m * (wl.layers * sum(2 * w.n * w.k for w in wl.per_layer) + (2 * wl.head.n * wl.head.k if head else 0))
         peak, peak_kind = measured_peaks()
         value = total_bytes * args.steps / (ms * 1e-3) / 1e9
         print(json.dumps({
@@ -529,6 +531,7 @@ def run_gpu_tp(args):
             "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "int8" if mode in (Mode.INT8_ACT, Mode.AUTO) else "f16", "data": "synthetic",
             "config": {"workload": f"{wl.name}: {wl.description}, M={m}, tensor-parallel x{world}", "mode": mode.name,
+                       "x_dtype": args.xdtype, "lm_head": bool(head), "tflops": pass_flops * args.steps / (ms * 1e-3) / 1e12,
                        "parallelism": f"tp{world}", "cuda_graph": graphed,
                        "collectives": "NCCL all-reduce after attn_output and ffn_down, all-gather after the head",
                        "weights": "random valid blocks generated on the GPU, sharded as bytes",

@@ -58,8 +58,7 @@ typedef enum {
  *               or Q8_K (K-quant weights) and block dots run in integers.
  *   EXACT_F32   weights are dequantized on the fly to their exact f32 values, f32 FMA.
  *   TENSOR_CORE tcgen05 f16 MMA with f32 accumulation (prefill-sized M).
- *   AUTO        INT8_ACT for M <= 32 (and up to 64 rows for weights with few 128-row tiles), TENSOR_CORE above
- *               (when in-features are a multiple of 64). */
+ *   AUTO        INT8_ACT for M <= 16, TENSOR_CORE above (when in-features are a multiple of 64). */
 typedef enum {
   TURQ_MODE_AUTO = 0,
   TURQ_MODE_INT8_ACT = 1,

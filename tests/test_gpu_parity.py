@@ -251,6 +251,10 @@ def test_tensor_core_mode_matches_f64_oracle(tq, dt, n, k, m):
     yb = mm.forward(xb, mode=tq.Mode.TENSOR_CORE).cpu().numpy()
     assert oracle.rel_fro(yb, oracle.matmul_f64(dt, w, n, k, xb.float().cpu().numpy())) < TOL
     # AUTO picks this path for prefill-sized M and results do not depend on the batch
+    if 17 < m <= 64:
+        # decode batches: split-K depends on the weight's shape only, not on the batch
+        y17 = mm.forward(xd[:17], mode=tq.Mode.TENSOR_CORE)
+        assert torch.equal(y17, mm.forward(xd, mode=tq.Mode.TENSOR_CORE)[:17])
     if m > 64:
         assert torch.equal(mm.forward(xd, mode=tq.Mode.AUTO), mm.forward(xd, mode=tq.Mode.TENSOR_CORE))
         y2 = mm.forward(xd[: m // 2 + 1], mode=tq.Mode.TENSOR_CORE)

@@ -333,14 +333,13 @@ int32_t turq_quantize_act(turq_ctx* ctx, int32_t fmt, const void* dev_x, int32_t
   return TURQ_OK;
 }
 
-// TURQ_MODE_AUTO: the integer GEMV for decode batches, the tcgen05 GEMM for prefill. In between
-// (17..64 rows) the GEMM's 128-row tiles only pay off when there are enough of them to occupy
-// the GPU; measured on B200, the integer path (32 rows per pass) is ahead up to 32 rows for
-// every shape and up to 64 rows for weights with fewer 128-row tiles than half the SMs.
+// TURQ_MODE_AUTO: the integer GEMV up to 16 rows, the tcgen05 GEMM above (64-row activation
+// tiles with split-K for decode batches, 128/256-row tiles for prefill). Measured on B200 at 32
+// and 64 rows the GEMM is ahead for every weight shape of the benchmark configurations.
 static int32_t auto_mode(const turq_ctx* ctx, int64_t n_rows, int64_t n_cols, int64_t m) {
-  if (m <= 32 || n_cols % 64 != 0) return TURQ_MODE_INT8_ACT;
-  if (m <= 64 && (n_rows + 127) / 128 < ctx->sm_count / 2) return TURQ_MODE_INT8_ACT;
-  return TURQ_MODE_TENSOR_CORE;
+  (void)ctx;
+  (void)n_rows;
+  return (m <= 16 || n_cols % 64 != 0) ? TURQ_MODE_INT8_ACT : TURQ_MODE_TENSOR_CORE;
 }
 
 int32_t turq_qmatmul(turq_ctx* ctx, const turq_qtensor* qt, const void* dev_x, int32_t x_dtype, int64_t m,
@@ -369,7 +368,7 @@ int32_t turq_qmatmul(turq_ctx* ctx, const turq_qtensor* qt, const void* dev_x, i
   } else if (mode == TURQ_MODE_EXACT_F32) {
     e = turq::launch_gemv_f32(qt->dtype, qt->tiles, qt->n_rows, k, dev_x, x_dtype, m, dev_y, dev_bias, ctx->sm_count, s, &launches);
   } else if (mode == TURQ_MODE_TENSOR_CORE) {
-    int32_t st = ensure(ctx, &ctx->scratch, &ctx->scratch_bytes, turq::gemm_tc_scratch_bytes(m, k));
+    int32_t st = ensure(ctx, &ctx->scratch, &ctx->scratch_bytes, turq::gemm_tc_scratch_bytes(m, k, qt->n_rows, ctx->sm_count));
     if (st != TURQ_OK) return st;
     e = turq::launch_gemm_tc(qt->dtype, qt->tiles, qt->n_rows, k, dev_x, x_dtype, m, dev_y, dev_bias, ctx->scratch,
                              ctx->sm_count, s, &launches, ctx->dev_status);

@@ -228,9 +228,10 @@ struct GemmArgs {
   int k;
   int m;            // activation rows
   const float* rscale;  // [m] factor undoing the f16 row scaling
-  float* y;         // [m, n_rows]
+  float* y;         // [m, n_rows]; with split-K: partial sums [splits][m][n_rows]
   const float* bias;
   int* status;
+  int splits;       // CTAs along K per output tile (gridDim.z); > 1: a reduction launch follows
 };
 
 // BN = activation rows per CTA (MMA N): 256 for prefill (128 when that is needed to give every
@@ -256,7 +257,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BM;  // first weight row
   const int m0 = blockIdx.y * BN;  // first activation row
-  const int kblocks = a.k / BK;
+  // this CTA's share of the K loop (split-K: an even share of the 64-element blocks)
+  const int kb_all = a.k / BK;
+  const int kb_begin = (int)((int64_t)kb_all * blockIdx.z / a.splits);
+  const int kblocks = (int)((int64_t)kb_all * (blockIdx.z + 1) / a.splits) - kb_begin;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) {
@@ -289,7 +293,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
         asm volatile(
             "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
                 s_u32(sB + s * B_BYTES)),
-            "l"(&xmap), "r"(kb * BK), "r"(m0), "r"(s_u32(&full_b[s]))
+            "l"(&xmap), "r"((kb_begin + kb) * BK), "r"(m0), "r"(s_u32(&full_b[s]))
             : "memory");
       }
     }
@@ -341,7 +345,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
     if (live) {
 #pragma unroll
       for (int u = 0; u < PF - 1; u++)
-        if (u < nmine) stage_load<DT>(pre[u], tiles_rt, grp + DQ_GROUPS * u, lane);
+        if (u < nmine) stage_load<DT>(pre[u], tiles_rt, kb_begin + grp + DQ_GROUPS * u, lane);
     }
     for (int t0 = 0; t0 < nmine && ok; t0 += PF) {
 #pragma unroll
@@ -350,14 +354,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
         if (t >= nmine) break;
         const int kb = grp + DQ_GROUPS * t;
         if (live && t + PF - 1 < nmine)
-          stage_load<DT>(pre[(u + PF - 1) % PF], tiles_rt, grp + DQ_GROUPS * (t + PF - 1), lane);
+          stage_load<DT>(pre[(u + PF - 1) % PF], tiles_rt, kb_begin + grp + DQ_GROUPS * (t + PF - 1), lane);
         const int s = kb % STAGES;
         const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
         ok = bar_wait(&empty[s], ph ^ 1u, abort_flag);
         if (!ok) break;
         uint8_t* a_tile = sA + s * A_BYTES;
         if (live) {
-          stage_dequant_store<DT>(pre[u], kb, lane, a_tile, 16 * dq);
+          stage_dequant_store<DT>(pre[u], kb_begin + kb, lane, a_tile, 16 * dq);
         } else {
           // rows beyond the tensor: zeros
           const int g = lane >> 2, c = lane & 3;
@@ -380,7 +384,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
       constexpr int PARTS = BN >= 128 ? 4 : 2;       // column parts shared out over the warps of a lane quarter
       const int col_part = dqw >> 2;                  // 0..3
       const int64_t n = (int64_t)n0 + 32 * quarter + lane;
-      const float bv = (a.bias && n < a.n_rows) ? a.bias[n] : 0.f;
+      const float bv = (a.bias && a.splits == 1 && n < a.n_rows) ? a.bias[n] : 0.f;
+      float* const yout = a.y + (size_t)blockIdx.z * (size_t)a.m * (size_t)a.n_rows;
 #pragma unroll 1
       for (int cb = 0; cb < BN / (32 * PARTS) && col_part < PARTS; cb++) {
         const int col0 = (BN / PARTS) * col_part + 32 * cb;
@@ -401,7 +406,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
 #pragma unroll
           for (int j = 0; j < 32; j++) {
             const int mrow = m0 + col0 + j;
-            if (mrow < a.m) a.y[(int64_t)mrow * a.n_rows + n] = __uint_as_float(v[j]) * a.rscale[mrow] + bv;
+            if (mrow < a.m) yout[(int64_t)mrow * a.n_rows + n] = __uint_as_float(v[j]) * a.rscale[mrow] + bv;
           }
         }
       }
@@ -445,6 +450,33 @@ __global__ void __launch_bounds__(256) prep_act_kernel(const void* __restrict__ 
     xh[row * k + i] = __float2half_rn(load_act_f32(x, is_bf16, row * k + i) * s);
 }
 
+// y[i] = sum of the split-K partial sums (in split order) + bias
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part, int splits, int64_t total,
+                                                             int64_t n_rows, const float* __restrict__ bias,
+                                                             float* __restrict__ y) {
+  const int64_t i4 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i4 >= total) return;
+  if (i4 + 4 <= total && (n_rows & 3) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0) {
+    float4 acc = *reinterpret_cast<const float4*>(part + i4);
+    for (int z = 1; z < splits; z++) {
+      const float4 p = *reinterpret_cast<const float4*>(part + (size_t)z * total + i4);
+      acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+    }
+    if (bias) {
+      const int64_t n = i4 % n_rows;
+      acc.x += bias[n]; acc.y += bias[n + 1]; acc.z += bias[n + 2]; acc.w += bias[n + 3];
+    }
+    *reinterpret_cast<float4*>(y + i4) = acc;
+  } else {
+    for (int64_t i = i4; i < total && i < i4 + 4; i++) {
+      float acc = part[i];
+      for (int z = 1; z < splits; z++) acc += part[(size_t)z * total + i];
+      if (bias) acc += bias[i % n_rows];
+      y[i] = acc;
+    }
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -472,7 +504,7 @@ cudaError_t launch_tc_bn(const CUtensorMap& map, const GemmArgs& a, cudaStream_t
     if (e != cudaSuccess) return e;
     configured_dev = dev;
   }
-  dim3 grid((unsigned)((a.n_rows + BM - 1) / BM), (unsigned)((a.m + BN - 1) / BN));
+  dim3 grid((unsigned)((a.n_rows + BM - 1) / BM), (unsigned)((a.m + BN - 1) / BN), (unsigned)a.splits);
   gemm_tc_kernel<DT, BN><<<grid, TC_THREADS, SMEM, s>>>(map, a);
   return cudaGetLastError();
 }
@@ -484,8 +516,37 @@ cudaError_t launch_tc_dt(const CUtensorMap& map, const GemmArgs& a, int bn, cuda
 
 }  // namespace
 
-size_t gemm_tc_scratch_bytes(int64_t m, int64_t k) {
-  return (((size_t)m * (size_t)k * 2 + 255) & ~(size_t)255) + (((size_t)m * 4 + 255) & ~(size_t)255) + 256;
+// Activation rows per CTA: 64 for decode batches; 256 for prefill, unless that leaves fewer
+// CTAs than SMs - then 128, which doubles the CTA count for the same work.
+static int pick_bn(int64_t n_rows, int64_t m, int sm_count) {
+  static const int bn_env = getenv("TURQ_GEMM_BN") ? atoi(getenv("TURQ_GEMM_BN")) : 0;
+  if (bn_env == 64 || bn_env == 128 || bn_env == 256) return bn_env;
+  int bn = m <= 64 ? 64 : 256;
+  if (bn == 256 && ((n_rows + BM - 1) / BM) * ((m + 255) / 256) < sm_count) bn = 128;
+  return bn;
+}
+
+// Split-K for decode batches (one 64-row activation tile): when the 128-row weight tiles alone
+// leave SMs without a CTA, the K loop of every tile is shared out over several CTAs (at least 8
+// blocks of 64 each); their partial sums go to scratch and a small launch adds them in a fixed
+// order. The split depends on the weight's shape only, so a row's result does not depend on
+// the batch it is in; prefill (more than 64 rows) never splits.
+static int pick_splits(int64_t n_rows, int64_t m, int64_t k, int sm_count) {
+  static const int env = getenv("TURQ_GEMM_SPLITK") ? atoi(getenv("TURQ_GEMM_SPLITK")) : -1;
+  if (m > 64 || env == 0) return 1;
+  const int64_t tiles = (n_rows + BM - 1) / BM;
+  int64_t s = sm_count / tiles;
+  const int64_t by_k = (k / BK) / 8;
+  if (env > 0) s = env;
+  if (s > by_k) s = by_k;
+  if (s > 16) s = 16;
+  return s < 2 ? 1 : (int)s;
+}
+
+size_t gemm_tc_scratch_bytes(int64_t m, int64_t k, int64_t n_rows, int sm_count) {
+  const int splits = pick_splits(n_rows, m, k, sm_count);
+  const size_t part = splits > 1 ? (((size_t)splits * (size_t)m * (size_t)n_rows * 4 + 255) & ~(size_t)255) : 0;
+  return (((size_t)m * (size_t)k * 2 + 255) & ~(size_t)255) + (((size_t)m * 4 + 255) & ~(size_t)255) + 256 + part;
 }
 
 cudaError_t launch_gemm_tc(int dtype, const uint8_t* tiles, int64_t n_rows, int64_t k, const void* x, int x_dtype,
@@ -504,12 +565,10 @@ cudaError_t launch_gemm_tc(int dtype, const uint8_t* tiles, int64_t n_rows, int6
   CUtensorMap map;
   const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)m};
   const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
-  // Activation rows per CTA: 64 for decode batches; 256 for prefill, unless that leaves fewer
-  // CTAs than SMs - then 128, which doubles the CTA count for the same work.
-  static const int bn_env = getenv("TURQ_GEMM_BN") ? atoi(getenv("TURQ_GEMM_BN")) : 0;
-  int bn = m <= 64 ? 64 : 256;
-  if (bn == 256 && ((n_rows + BM - 1) / BM) * ((m + 255) / 256) < sm_count) bn = 128;
-  if (bn_env == 64 || bn_env == 128 || bn_env == 256) bn = bn_env;
+  const int bn = pick_bn(n_rows, m, sm_count);
+  const int splits = pick_splits(n_rows, m, k, sm_count);
+  float* partial = reinterpret_cast<float*>(scratch + (((size_t)m * (size_t)k * 2 + 255) & ~(size_t)255) +
+                                            (((size_t)m * 4 + 255) & ~(size_t)255) + 256);
   const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)bn};
   const cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xh, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -523,9 +582,10 @@ cudaError_t launch_gemm_tc(int dtype, const uint8_t* tiles, int64_t n_rows, int6
   a.k = (int)k;
   a.m = (int)m;
   a.rscale = rscale;
-  a.y = y;
+  a.y = splits > 1 ? partial : y;
   a.bias = bias;
   a.status = dev_status_word;
+  a.splits = splits;
   switch (dtype) {
     case TQ_Q8_0: e = launch_tc_dt<TQ_Q8_0>(map, a, bn, s); break;
     case TQ_Q4_K: e = launch_tc_dt<TQ_Q4_K>(map, a, bn, s); break;
@@ -534,7 +594,11 @@ cudaError_t launch_gemm_tc(int dtype, const uint8_t* tiles, int64_t n_rows, int6
     default: return cudaErrorInvalidValue;
   }
   if (launches) (*launches)++;
-  return e;
+  if (e != cudaSuccess || splits == 1) return e;
+  const int64_t total = m * n_rows;
+  splitk_reduce_kernel<<<(unsigned)((total + 1023) / 1024), 256, 0, s>>>(partial, splits, total, n_rows, bias, y);
+  if (launches) (*launches)++;
+  return cudaGetLastError();
 }
 
 }  // namespace turq

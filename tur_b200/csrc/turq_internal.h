@@ -56,8 +56,8 @@ cudaError_t launch_gemv_f32(int dtype, const uint8_t* tiles, int64_t n_rows, int
                             int sm_count, cudaStream_t s, int* launches);
 
 // Tensor-core GEMM (tcgen05): x [m, k] -> f16 operand in scratch, then the fused
-// dequantize + MMA kernel. scratch must hold gemm_tc_scratch_bytes(m, k).
-size_t gemm_tc_scratch_bytes(int64_t m, int64_t k);
+// dequantize + MMA kernel. scratch must hold gemm_tc_scratch_bytes(m, k, n_rows, sm_count).
+size_t gemm_tc_scratch_bytes(int64_t m, int64_t k, int64_t n_rows, int sm_count);
 cudaError_t launch_gemm_tc(int dtype, const uint8_t* tiles, int64_t n_rows, int64_t k,
                            const void* x, int x_dtype, int64_t m, float* y, const float* bias,
                            uint8_t* scratch, int sm_count, cudaStream_t s, int* launches,
