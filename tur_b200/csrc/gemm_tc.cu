@@ -32,7 +32,10 @@ namespace {
 
 constexpr int BM = 128;      // weight rows per CTA (MMA M)
 constexpr int BK = 64;       // k per stage (one 128-byte swizzle row of f16)
-constexpr int STAGES = 4;
+// Pipeline depth by activation-tile height: the ring must cover the L2 -> shared-memory latency of
+// the TMA loads (a slot is only refilled after the MMAs that read it have completed), so the
+// smaller tiles get more stages out of the same shared memory.
+constexpr int stages_for_bn(int bn) { return bn == 64 ? 8 : bn == 128 ? 6 : 4; }
 constexpr int A_BYTES = BM * BK * 2;  // 16 KB
 constexpr int DQ_WARPS = 8;        // warps that together produce one stage of the weight operand
 constexpr int DQ_GROUPS = 2;       // groups of DQ_WARPS warps working on alternate stages
@@ -62,6 +65,7 @@ __device__ __forceinline__ bool bar_try(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 __device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (bar_try(bar, parity)) return true;  // the common case costs one poll, no clock read
   const long long t0 = clock64();
   for (uint32_t i = 0;; i++) {
     if (bar_try(bar, parity)) return true;
@@ -70,6 +74,23 @@ __device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity, volatil
   *abort_flag = 1;
   return false;
 }
+
+#ifdef TURQ_TRACE
+// Debug timeline of CTA (0,0,0): global-timer stamps of one dequantize warp and of the MMA
+// thread over a few consecutive stages (built only with -DTURQ_TRACE).
+__device__ unsigned long long g_gemm_trace[64 * 8];
+__device__ __forceinline__ unsigned long long gtime_tc() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+#define TC_TRACE(row, col) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (row) >= 0 && (row) < 64) g_gemm_trace[(row) * 8 + (col)] = gtime_tc(); } while (0)
+int read_gemm_trace(unsigned long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_gemm_trace, sizeof(unsigned long long) * n);
+}
+#else
+#define TC_TRACE(row, col) do { } while (0)
+#endif
 
 // K-major, 128-byte swizzle shared-memory matrix descriptor (8-row groups 1024 B apart).
 __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr) {
@@ -242,15 +263,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
   constexpr int TB = TileGeom<DT>::BYTES;
   constexpr int B_BYTES = BN * BK * 2;
   constexpr int TMEM_COLS = BN;
+  constexpr int ST = stages_for_bn(BN);
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // 1024-byte alignment for the swizzled tiles
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = smem;
-  uint8_t* sB = smem + STAGES * A_BYTES;
-  uint64_t* full_a = reinterpret_cast<uint64_t*>(smem + STAGES * (A_BYTES + B_BYTES));
-  uint64_t* full_b = full_a + STAGES;
-  uint64_t* empty = full_b + STAGES;
-  uint64_t* accum = empty + STAGES;
+  uint8_t* sB = smem + ST * A_BYTES;
+  // full[s]: stage s holds its weight tile (one arrival per dequantize warp) and its
+  // activation tile (the TMA thread's arrival + transaction bytes)
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + ST * (A_BYTES + B_BYTES));
+  uint64_t* empty = full + ST;
+  uint64_t* accum = empty + ST;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -263,9 +286,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
   const int kblocks = (int)((int64_t)kb_all * (blockIdx.z + 1) / a.splits) - kb_begin;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; s++) {
-      bar_init(&full_a[s], DQ_WARPS);
-      bar_init(&full_b[s], 1);
+    for (int s = 0; s < ST; s++) {
+      bar_init(&full[s], DQ_WARPS + 1);
       bar_init(&empty[s], 1);
     }
     bar_init(accum, 1);
@@ -286,14 +308,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
     // ------------------------------------------------------------ TMA producer (activations)
     if (lane == 0) {
       for (int kb = 0; kb < kblocks; kb++) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+        const int s = kb % ST;
+        const uint32_t ph = (uint32_t)(kb / ST) & 1u;
         if (!bar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
-        bar_expect_tx(&full_b[s], B_BYTES);
+        bar_expect_tx(&full[s], B_BYTES);
         asm volatile(
             "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
                 s_u32(sB + s * B_BYTES)),
-            "l"(&xmap), "r"((kb_begin + kb) * BK), "r"(m0), "r"(s_u32(&full_b[s]))
+            "l"(&xmap), "r"((kb_begin + kb) * BK), "r"(m0), "r"(s_u32(&full[s]))
             : "memory");
       }
     }
@@ -302,28 +324,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
     if (lane == 0) {
       // instruction descriptor: f32 accumulate, f16 x f16, both K-major, N = BN, M = 128
       constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      // This one thread feeds the tensor core, so its own instruction count per stage is what
+      // separates consecutive stages' MMAs: descriptors are a constant high half plus a low
+      // half that advances by 2 (32 bytes >> 4) per 16-element K step, the stage index and
+      // phase are carried along, and one barrier covers both operands.
+      constexpr uint64_t desc_hi = (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+      const uint32_t a_lo0 = (s_u32(sA) & 0x3FFFFu) >> 4, b_lo0 = (s_u32(sB) & 0x3FFFFu) >> 4;
       bool ok = true;
-      for (int kb = 0; kb < kblocks && ok; kb++) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
-        ok = bar_wait(&full_a[s], ph, abort_flag) && bar_wait(&full_b[s], ph, abort_flag);
+      int s = 0;
+      uint32_t ph = 0, accumulate = 0;  // the first MMA of the tile overwrites the accumulator
+      for (int kb = 0; kb < kblocks; kb++) {
+        TC_TRACE(kb, 5);
+        ok = bar_wait(&full[s], ph, abort_flag);
         if (!ok) break;
+        TC_TRACE(kb, 6);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_addr = s_u32(sA + s * A_BYTES), b_addr = s_u32(sB + s * B_BYTES);
+        const uint64_t da0 = desc_hi | (uint64_t)(a_lo0 + (uint32_t)s * (A_BYTES >> 4));
+        const uint64_t db0 = desc_hi | (uint64_t)(b_lo0 + (uint32_t)s * (B_BYTES >> 4));
 #pragma unroll
         for (int kk = 0; kk < BK / 16; kk++) {
-          const uint64_t da = smem_desc(a_addr + kk * 32), db = smem_desc(b_addr + kk * 32);
-          const uint32_t accumulate = (kb > 0 || kk > 0) ? 1u : 0u;
           asm volatile(
               "{\n\t.reg .pred p;\n\t"
               "setp.ne.b32 p, %4, 0;\n\t"
               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_base),
-              "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+              "l"(da0 + 2 * kk), "l"(db0 + 2 * kk), "r"(idesc), "r"(kk > 0 ? 1u : accumulate)
               : "memory");
         }
+        accumulate = 1u;
         // release the stage to the producers once these MMAs have read it
         asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s_u32(&empty[s]))
                      : "memory");
+        TC_TRACE(kb, 7);
+        if (++s == ST) { s = 0; ph ^= 1u; }
       }
       if (ok)
         asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s_u32(accum))
@@ -355,10 +387,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
         const int kb = grp + DQ_GROUPS * t;
         if (live && t + PF - 1 < nmine)
           stage_load<DT>(pre[(u + PF - 1) % PF], tiles_rt, kb_begin + grp + DQ_GROUPS * (t + PF - 1), lane);
-        const int s = kb % STAGES;
-        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+        const int s = kb % ST;
+        const uint32_t ph = (uint32_t)(kb / ST) & 1u;
+        if (dq == 0 && lane == 0) TC_TRACE(kb, 0);
         ok = bar_wait(&empty[s], ph ^ 1u, abort_flag);
         if (!ok) break;
+        if (dq == 0 && lane == 0) TC_TRACE(kb, 1);
         uint8_t* a_tile = sA + s * A_BYTES;
         if (live) {
           stage_dequant_store<DT>(pre[u], kb_begin + kb, lane, a_tile, 16 * dq);
@@ -371,9 +405,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
             for (int h = 0; h < 2; h++)
               *reinterpret_cast<uint4*>(a_tile + swz(16 * dq + g + 8 * hr, 4 * h + c)) = make_uint4(0, 0, 0, 0);
         }
+        if (dq == 0 && lane == 0) TC_TRACE(kb, 2);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the MMA
         __syncwarp();
-        if (lane == 0) bar_arrive(&full_a[s]);
+        if (dq == 0 && lane == 0) TC_TRACE(kb, 3);
+        if (lane == 0) bar_arrive(&full[s]);
+        if (dq == 0 && lane == 0) TC_TRACE(kb, 4);
       }
     }
     // ---- epilogue: TMEM lanes 32*(warp%4).., columns split over the warps of each lane quarter
@@ -495,7 +532,8 @@ EncodeTiledFn encode_fn() {
 
 template <int DT, int BN>
 cudaError_t launch_tc_bn(const CUtensorMap& map, const GemmArgs& a, cudaStream_t s) {
-  constexpr int SMEM = STAGES * (A_BYTES + BN * BK * 2) + (3 * STAGES + 1) * 8 + 16 + 1024;
+  constexpr int ST = stages_for_bn(BN);
+  constexpr int SMEM = ST * (A_BYTES + BN * BK * 2) + (3 * ST + 1) * 8 + 16 + 1024;
   static int configured_dev = -1;
   int dev = 0;
   cudaGetDevice(&dev);
@@ -602,3 +640,7 @@ cudaError_t launch_gemm_tc(int dtype, const uint8_t* tiles, int64_t n_rows, int6
 }
 
 }  // namespace turq
+
+#ifdef TURQ_TRACE
+extern "C" int turq_debug_read_gemm_trace(unsigned long long* host, int n) { return turq::read_gemm_trace(host, n); }
+#endif

@@ -604,7 +604,8 @@ static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const
   auto stages_for = [&](bool planes_in_smem, int cps, int rows, int mg) {
     if (cps < share_div) cps = share_div;
     const int share = (smem_budget() + 1024) / cps - 1024;  // 1 KB per CTA is reserved by the system
-    int st = MAX_STAGES;
+    static const int gmax = getenv("TURQ_GEMV_GSTAGES") ? atoi(getenv("TURQ_GEMV_GSTAGES")) : MAX_STAGES;
+    int st = planes_in_smem ? MAX_STAGES : (gmax < MAX_STAGES ? (gmax < 2 ? 2 : gmax) : MAX_STAGES);
     for (; st >= 2; st--)
       if (plan_smem(DT, mg, planes_in_smem, rows, (int)k, st, stage_bytes).total <= share) break;
     return st;
