@@ -554,13 +554,13 @@ cudaError_t launch_tc_dt(const CUtensorMap& map, const GemmArgs& a, int bn, cuda
 
 }  // namespace
 
-// Activation rows per CTA: 64 for decode batches; 256 for prefill, unless that leaves fewer
-// CTAs than SMs - then 128, which doubles the CTA count for the same work.
+// Activation rows per CTA: 64 for decode batches; 256 for prefill, unless twice as many CTAs
+// still fit the SMs in one wave - then 128, which doubles the CTA count for the same work.
 static int pick_bn(int64_t n_rows, int64_t m, int sm_count) {
   static const int bn_env = getenv("TURQ_GEMM_BN") ? atoi(getenv("TURQ_GEMM_BN")) : 0;
   if (bn_env == 64 || bn_env == 128 || bn_env == 256) return bn_env;
   int bn = m <= 64 ? 64 : 256;
-  if (bn == 256 && ((n_rows + BM - 1) / BM) * ((m + 255) / 256) < sm_count) bn = 128;
+  if (bn == 256 && 2 * ((n_rows + BM - 1) / BM) * ((m + 255) / 256) <= sm_count) bn = 128;
   return bn;
 }
 
