@@ -217,17 +217,14 @@ def run_gpu(args):
     groups = [["attn_q", "attn_k", "attn_v"], ["attn_output"], ["ffn_gate", "ffn_up"], ["ffn_down"]]
 
     def run_group(members):
-        """Members of one dtype go out as a single multi-weight launch."""
-        by_dt = {}
-        for w, mm in members:
-            by_dt.setdefault(w.dtype, []).append((w, mm))
-        for same in by_dt.values():
-            if len(same) > 1 and not args.no_multi:
-                QMatMul.forward_multi([mm for _, mm in same], x_dev[same[0][0].source], mode=mode,
-                                      outs=[y_dev[w.name] for w, _ in same])
-            else:
-                for w, mm in same:
-                    mm.forward(x_dev[w.source], mode=mode, out=y_dev[w.name])
+        """Members that read the same x go out as one multi-weight call: a single launch per weight
+        type, and a single launch altogether for Q4_K / Q5_K beside Q6_K at decode batch sizes."""
+        if len(members) > 1 and not args.no_multi:
+            QMatMul.forward_multi([mm for _, mm in members], x_dev[members[0][0].source], mode=mode,
+                                  outs=[y_dev[w.name] for w, _ in members])
+        else:
+            for w, mm in members:
+                mm.forward(x_dev[w.source], mode=mode, out=y_dev[w.name])
 
     def one_pass_device():
         main = torch.cuda.current_stream()
@@ -456,19 +453,15 @@ def run_gpu_tp(args):
         for layer in layers:
             by_name = {w.name: (w, sh, lin) for w, sh, lin in layer}
             for grp in groups:
-                by_dt = {}
-                for n in grp:
-                    w, sh, lin = by_name[n]
-                    by_dt.setdefault(w.dtype, []).append((w, sh, lin))
-                for same in by_dt.values():
-                    w0, sh0, _ = same[0]
-                    if len(same) > 1:
-                        QMatMul.forward_multi([lin.matmul for _, _, lin in same], xs[(w0.source, sh0.shape[1])], mode=mode,
-                                              outs=[ys[w.name] for w, _, _ in same])
-                    else:
-                        y = same[0][2].matmul.forward(xs[(w0.source, sh0.shape[1])], mode=mode, out=ys[w0.name])
-                        if sh0.parallel == "row" and world > 1:
-                            dist.all_reduce(y)
+                same = [by_name[n] for n in grp]
+                w0, sh0, _ = same[0]
+                if len(same) > 1:
+                    QMatMul.forward_multi([lin.matmul for _, _, lin in same], xs[(w0.source, sh0.shape[1])], mode=mode,
+                                          outs=[ys[w.name] for w, _, _ in same])
+                else:
+                    y = same[0][2].matmul.forward(xs[(w0.source, sh0.shape[1])], mode=mode, out=ys[w0.name])
+                    if sh0.parallel == "row" and world > 1:
+                        dist.all_reduce(y)
         if head:
             y = head[2].forward(xs[("hidden", wl.hidden)], mode=mode, out=ys["output"])
             if world > 1:

@@ -282,7 +282,7 @@ def test_one_launch_for_linears_sharing_x(tq, dt, m):
         want = oracle.qmatmul(dt, w, n, k, x) + (bias1.cpu().numpy() if i == 1 else 0)
         assert ys[i].shape == (m, n)
         assert oracle.rel_fro(ys[i].cpu().numpy(), want) < 1e-5
-    # mixed types fall back to one launch per weight and still agree
+    # other type combinations go out as one launch per type (or a mixed launch) and still agree
     other = TYPES[(TYPES.index(dt) + 1) % len(TYPES)]
     w2 = make_weight(other, 48, k, SEED + 9)
     mixed = [mms[0], tq.QMatMul.from_arc(tq.QTensor.new(w2, tq.GgmlDType(other), (48, k)))]
@@ -312,6 +312,32 @@ def test_joint_launch_gives_the_same_bits_as_separate_launches(tq, dt, m):
         assert torch.equal(mm.forward(xd, mode=tq.Mode.INT8_ACT), y)
     want = oracle.qmatmul(dt, ws[1], shapes[1], k, xd.cpu().numpy())
     assert oracle.rel_fro(joint[1].cpu().numpy(), want) < 1e-5
+
+
+@pytest.mark.parametrize("dt", [oracle.Q4_K, oracle.Q5_K], ids=lambda d: oracle.NAMES[d])
+@pytest.mark.parametrize("m", [1, 3, 8, 12])
+def test_mixed_type_launch_for_attn_qkv(tq, dt, m):
+    """The K-quant mixes keep attn_v in Q6_K beside Q4_K / Q5_K attn_q and attn_k: one call, and
+    up to 8 rows one kernel launch, with the bits of the separate launches."""
+    k = 1024
+    shapes = [(dt, 272), (dt, 64), (oracle.Q6_K, 1000)]
+    rng = np.random.default_rng(SEED + 123 + m)
+    ws = [make_weight(t, n, k, SEED + 700 + n) for t, n in shapes]
+    mms = [tq.QMatMul.from_arc(tq.QTensor.new(w, tq.GgmlDType(t), (n, k))) for w, (t, n) in zip(ws, shapes)]
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    bias2 = torch.from_numpy(rng.standard_normal(1000).astype(np.float32)).cuda()
+    l0 = tq.context().launch_count()
+    ys = tq.QMatMul.forward_multi(mms, xd, biases=[None, None, bias2], mode=tq.Mode.INT8_ACT)
+    launches = tq.context().launch_count() - l0
+    if m == 1:
+        assert launches == 1
+    tq.context().poll_status()
+    for i, (mm, (t, n)) in enumerate(zip(mms, shapes)):
+        sep = mm.forward(xd, bias=bias2 if i == 2 else None, mode=tq.Mode.INT8_ACT)
+        assert torch.equal(ys[i], sep)
+        want = oracle.qmatmul(t, ws[i], n, k, x) + (bias2.cpu().numpy() if i == 2 else 0)
+        assert oracle.rel_fro(ys[i].cpu().numpy(), want) < 1e-5
 
 
 def test_no_kernel_gave_up_a_wait(tq):

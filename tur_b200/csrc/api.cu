@@ -389,8 +389,10 @@ int32_t turq_qmatmul_multi(turq_ctx* ctx, int32_t count, const turq_qtensor* con
     if (!qts[i] || !dev_ys[i]) return fail(ctx, TURQ_E_INVALID_ARG, "null argument");
     if (qts[i]->n_cols != qts[0]->n_cols) return fail(ctx, TURQ_E_SHAPE, "weights of one call must share the in-feature count");
   }
+  // One activation format per call: K-quant weights (Q8_K activations) and Q8_0 weights do not mix.
   bool same = true;
-  for (int i = 1; i < count; i++) same = same && qts[i]->dtype == qts[0]->dtype && qts[i]->device == qts[0]->device;
+  for (int i = 1; i < count; i++)
+    same = same && (qts[i]->dtype == TURQ_Q8_0) == (qts[0]->dtype == TURQ_Q8_0) && qts[i]->device == qts[0]->device;
   int32_t eff = mode;
   if (eff == TURQ_MODE_AUTO) {
     int64_t rows_all = 0;
@@ -415,7 +417,8 @@ int32_t turq_qmatmul_multi(turq_ctx* ctx, int32_t count, const turq_qtensor* con
   int32_t st = ensure(ctx, &ctx->scratch, &ctx->scratch_bytes, plan.total);
   if (st != TURQ_OK) return st;
   turq::GemvPart parts[4];
-  for (int i = 0; i < count; i++) parts[i] = turq::GemvPart{qts[i]->tiles, qts[i]->n_rows, dev_ys[i], dev_biases ? dev_biases[i] : nullptr};
+  for (int i = 0; i < count; i++)
+    parts[i] = turq::GemvPart{qts[i]->tiles, qts[i]->n_rows, dev_ys[i], dev_biases ? dev_biases[i] : nullptr, qts[i]->dtype};
   int launches = 0;
   cudaError_t e = turq::launch_gemv_int8_multi(qts[0]->dtype, parts, count, k, dev_x, x_dtype, ctx->scratch, m, ctx->gemv_ws,
                                                ctx->dev_status, ctx->sm_count, static_cast<cudaStream_t>(stream), &launches);

@@ -102,6 +102,7 @@ struct StreamArgs {
   const uint8_t* tiles[MAX_PARTS];
   int64_t n_rows[MAX_PARTS];
   int rt_begin[MAX_PARTS + 1];
+  int part_alt[MAX_PARTS];        // mixed launches: 1 = this part's tiles are of the second type (DT2)
   float* y[MAX_PARTS];            // outputs, already offset to the pass's first row
   const float* bias[MAX_PARTS];
   int nparts;
@@ -121,7 +122,8 @@ struct StreamArgs {
   SmemPlan sp;
 };
 
-inline SmemPlan plan_smem(int dtype, int mg, bool fused /* planes in shared memory */, int rows_cap, int k, int stages, int stage_bytes) {
+inline SmemPlan plan_smem(int dtype, int mg, bool fused /* planes in shared memory */, int rows_cap, int k, int stages, int stage_bytes,
+                          int dtype2 = -1) {
   auto up = [](int v) { return (v + 127) & ~127; };
   SmemPlan p{};
   p.ring = 0;
@@ -133,7 +135,7 @@ inline SmemPlan plan_smem(int dtype, int mg, bool fused /* planes in shared memo
     p.act_dsc = off;
     off = up(off + rows_cap * (k / (dtype == TQ_Q8_0 ? 32 : 256)) * 4);
     p.act_bs16 = off;  // Q6_K reads the sums of 16, Q4_K / Q5_K the sums of 32
-    if (dtype == TQ_Q6_K) off = up(off + rows_cap * (k / 16) * 2);
+    if (dtype == TQ_Q6_K || dtype2 == TQ_Q6_K) off = up(off + rows_cap * (k / 16) * 2);
     p.act_bs32 = off;
     if (dtype == TQ_Q4_K || dtype == TQ_Q5_K) off = up(off + rows_cap * (k / 32) * 2);
   }
@@ -179,11 +181,20 @@ constexpr int ACT_GLOBAL = 0;  // in global scratch (written by a preceding quan
 constexpr int ACT_FUSED = 1;   // quantized by this CTA into shared memory
 constexpr int ACT_STAGED = 2;  // bulk-copied from global scratch into shared memory at CTA start
 
-template <int DT, int MG, int ACT>
+// DT2 != DT: a mixed launch (attn_q|k in Q4_K or Q5_K beside attn_v in Q6_K, as the K-quant
+// mixes store them); parts flagged in part_alt hold DT2 tiles. Both types have one tile per
+// 256 elements, so the walk over tiles is the same; ring slots are sized for the larger tile.
+template <int DT, int MG, int ACT, int DT2 = DT>
 __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(const __grid_constant__ StreamArgs a) {
+  constexpr bool MIXED = DT2 != DT;
   constexpr int TB = TileGeom<DT>::BYTES;
+  constexpr int TB2 = TileGeom<DT2>::BYTES;
   constexpr int GROUP = TileGeom<DT>::GROUP;
-  constexpr int UNIT_BYTES = TB * GROUP;
+  static_assert(!MIXED || (GROUP == 1 && TileGeom<DT2>::GROUP == 1 && TileGeom<DT>::ELEMS == TileGeom<DT2>::ELEMS),
+                "mixed launches pair K-quant types only");
+  constexpr int UNIT_BYTES = (TB2 > TB ? TB2 : TB) * GROUP;
+  constexpr bool NEED16 = DT == TQ_Q6_K || DT2 == TQ_Q6_K;
+  constexpr bool NEED32 = DT == TQ_Q4_K || DT == TQ_Q5_K || DT2 == TQ_Q4_K || DT2 == TQ_Q5_K;
   extern __shared__ __align__(128) uint8_t smem[];
   const SmemPlan& sp = a.sp;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + sp.bars);  // [stage][consumer warp]: one tile each
@@ -238,14 +249,14 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
         asm volatile("griddepcontrol.wait;" ::: "memory");
         const int nb = DT == TQ_Q8_0 ? a.k >> 5 : a.k >> 8;
         const uint32_t dsc_bytes = ((uint32_t)(a.rows * nb * 4) + 15u) & ~15u;
-        const uint32_t sum_bytes = DT == TQ_Q8_0 ? 0u
-                                   : (((uint32_t)(a.rows * (DT == TQ_Q6_K ? a.k >> 4 : a.k >> 5) * 2) + 15u) & ~15u);
-        mbar_expect_tx(act_full, (uint32_t)(a.rows * a.k) + dsc_bytes + sum_bytes);
+        const uint32_t s16_bytes = NEED16 ? (((uint32_t)(a.rows * (a.k >> 4) * 2) + 15u) & ~15u) : 0u;
+        const uint32_t s32_bytes = NEED32 ? (((uint32_t)(a.rows * (a.k >> 5) * 2) + 15u) & ~15u) : 0u;
+        mbar_expect_tx(act_full, (uint32_t)(a.rows * a.k) + dsc_bytes + s16_bytes + s32_bytes);
         for (int r = 0; r < a.rows; r++)
           bulk_g2s(smem + sp.act_qs + r * sp.qs_stride, a.gact.qs + (size_t)r * a.k, (uint32_t)a.k, act_full);
         bulk_g2s(smem + sp.act_dsc, a.gact.dsc, dsc_bytes, act_full);
-        if constexpr (DT == TQ_Q6_K) bulk_g2s(smem + sp.act_bs16, a.gact.bs16, sum_bytes, act_full);
-        if constexpr (DT == TQ_Q4_K || DT == TQ_Q5_K) bulk_g2s(smem + sp.act_bs32, a.gact.bs32, sum_bytes, act_full);
+        if constexpr (NEED16) bulk_g2s(smem + sp.act_bs16, a.gact.bs16, s16_bytes, act_full);
+        if constexpr (NEED32) bulk_g2s(smem + sp.act_bs32, a.gact.bs32, s32_bytes, act_full);
       };
       if constexpr (ACT == ACT_STAGED) copy_planes();
       StageWalk w;
@@ -259,14 +270,15 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
         // that warp's own barrier: a warp starts as soon as its bytes are there
         int part = 0;
         while (part + 1 < a.nparts && w.rt >= a.rt_begin[part + 1]) part++;
-        const uint8_t* src = a.tiles[part] + ((int64_t)(w.rt - a.rt_begin[part]) * a.ktiles + (int64_t)w.ku * GROUP) * TB;
+        const int tb = (MIXED && a.part_alt[part]) ? TB2 : TB;
+        const uint8_t* src = a.tiles[part] + ((int64_t)(w.rt - a.rt_begin[part]) * a.ktiles + (int64_t)w.ku * GROUP) * tb;
         uint8_t* dst = smem + sp.ring + slot * a.stage_bytes;
         for (int i = 0; i < n; i++) {
           int nt = a.ktiles - (w.ku + i) * GROUP;
           if (nt > GROUP) nt = GROUP;
-          const uint32_t bytes = (uint32_t)nt * TB;
+          const uint32_t bytes = (uint32_t)nt * tb;
           mbar_expect_tx(&full[slot * NW + i], bytes);
-          bulk_g2s(dst + i * UNIT_BYTES, src + (size_t)i * UNIT_BYTES, bytes, &full[slot * NW + i]);
+          bulk_g2s(dst + i * UNIT_BYTES, src + (size_t)i * GROUP * tb, bytes, &full[slot * NW + i]);
         }
         for (int i = n; i < NW; i++) mbar_arrive(&full[slot * NW + i]);  // unused this stage: keep phases in step
         w.advance(n);
@@ -347,9 +359,8 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
           if (has) {
             *reinterpret_cast<uint4*>(sqs + row * sp.qs_stride + blk * 256 + hl * 16) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
             if (hl == 0) sdsc[row * nblk + blk] = d;
-            if constexpr (DT == TQ_Q6_K) {
-              sb16[row * (a.k >> 4) + blk * 16 + hl] = (int16_t)s16;
-            } else {
+            if constexpr (NEED16) sb16[row * (a.k >> 4) + blk * 16 + hl] = (int16_t)s16;
+            if constexpr (NEED32) {
               if ((hl & 1) == 0) sb32[row * (a.k >> 5) + blk * 8 + (hl >> 1)] = (int16_t)s32;
             }
           }
@@ -388,7 +399,18 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
         const int kt = (w.ku + warp) * GROUP;
         int left = a.ktiles - kt;
         if (left > GROUP) left = GROUP;
-        tile_mma<DT, MG>(smem + sp.ring + slot * a.stage_bytes + warp * UNIT_BYTES, lane, act, a.k, kt, a.rows, left, acc);
+        const uint8_t* tile = smem + sp.ring + slot * a.stage_bytes + warp * UNIT_BYTES;
+        bool alt = false;
+        if constexpr (MIXED) {
+          int part = 0;
+          while (part + 1 < a.nparts && w.rt >= a.rt_begin[part + 1]) part++;
+          alt = a.part_alt[part] != 0;
+        }
+        if (MIXED && alt) {
+          tile_mma<DT2, MG>(tile, lane, act, a.k, kt, a.rows, left, acc);
+        } else {
+          tile_mma<DT, MG>(tile, lane, act, a.k, kt, a.rows, left, acc);
+        }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[slot]);  // after the tile's bytes have been consumed
@@ -549,13 +571,13 @@ size_t gemv_workspace_bytes(int sms) { return (size_t)sms * 4 * 4 * 128 * 4 + (s
 
 // Launches with the programmatic-stream-serialization attribute (the kernel orders itself
 // against its predecessor with griddepcontrol.wait).
-template <int DT, int MG, int ACT>
+template <int DT, int MG, int ACT, int DT2 = DT>
 static cudaError_t launch_one(StreamArgs a, int grid, int smem_bytes, cudaStream_t s, bool after_quant = false) {
   static int configured_dev = -1;  // per instantiation; the attribute is per device function
   int dev = 0;
   cudaGetDevice(&dev);
   if (configured_dev != dev) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<DT, MG, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<DT, MG, ACT, DT2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          smem_budget());
     if (e != cudaSuccess) return e;
     configured_dev = dev;
@@ -574,15 +596,19 @@ static cudaError_t launch_one(StreamArgs a, int grid, int smem_bytes, cudaStream
   static const int pdl = getenv("TURQ_GEMV_PDL") ? atoi(getenv("TURQ_GEMV_PDL")) : 0;
   static const int pdl_pair = getenv("TURQ_GEMV_PDL_PAIR") ? atoi(getenv("TURQ_GEMV_PDL_PAIR")) : 1;
   cfg.numAttrs = (pdl || (after_quant && pdl_pair)) ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<DT, MG, ACT>, a);
+  return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<DT, MG, ACT, DT2>, a);
 }
 
-template <int DT>
+// DT2 != DT: parts whose dtype field is DT2 hold tiles of that type (one launch for the K-quant
+// mixes' attn_q|k|v). Returns cudaErrorNotSupported, before anything is launched, when a mixed
+// call would need a variant that is not instantiated (more than 8 rows, planes in global memory).
+template <int DT, int DT2 = DT>
 static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const void* x, int x_dtype,
                              uint8_t* act_scratch, int64_t m, uint8_t* workspace, int* status, int sm_count,
                              cudaStream_t s, int* launches) {
+  constexpr bool MIXED = DT2 != DT;
   constexpr int GROUP = TileGeom<DT>::GROUP;
-  constexpr int UNIT_BYTES = TileGeom<DT>::BYTES * GROUP;
+  constexpr int UNIT_BYTES = (TileGeom<DT2>::BYTES > TileGeom<DT>::BYTES ? TileGeom<DT2>::BYTES : TileGeom<DT>::BYTES) * GROUP;
   if (nparts < 1 || nparts > MAX_PARTS) return cudaErrorInvalidValue;
   const int ktiles = (int)(k / TileGeom<DT>::ELEMS);
   const int KU = (ktiles + GROUP - 1) / GROUP;
@@ -607,7 +633,7 @@ static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const
     static const int gmax = getenv("TURQ_GEMV_GSTAGES") ? atoi(getenv("TURQ_GEMV_GSTAGES")) : MAX_STAGES;
     int st = planes_in_smem ? MAX_STAGES : (gmax < MAX_STAGES ? (gmax < 2 ? 2 : gmax) : MAX_STAGES);
     for (; st >= 2; st--)
-      if (plan_smem(DT, mg, planes_in_smem, rows, (int)k, st, stage_bytes).total <= share) break;
+      if (plan_smem(DT, mg, planes_in_smem, rows, (int)k, st, stage_bytes, DT2).total <= share) break;
     return st;
   };
   // Activation planes: quantized in the kernel (few rows), else quantized once by a launch of
@@ -621,6 +647,7 @@ static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const
     if (act_mode == ACT_GLOBAL && m <= 16 && stage_env && stages_for(true, ctas_per_sm, rows0, mg0) >= 2) act_mode = ACT_STAGED;
   }
   const bool fused = act_mode == ACT_FUSED, planes_in_smem = act_mode != ACT_GLOBAL;
+  if (MIXED && (m > 8 || act_mode == ACT_GLOBAL)) return cudaErrorNotSupported;
   // Work split. Whole row-tiles per CTA when that keeps most CTA slots busy (or the problem
   // is small): no row-tile is shared, so no partial sums cross CTAs. Otherwise an even split
   // in tiles, with the hand-over of split row-tiles. Depends on the shape only, never on M.
@@ -660,6 +687,7 @@ static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const
       a.n_rows[p] = parts[p].n_rows;
       a.y[p] = parts[p].y + m0 * parts[p].n_rows;
       a.bias[p] = parts[p].bias;
+      a.part_alt[p] = (MIXED && parts[p].dtype == DT2) ? 1 : 0;
     }
     for (int p = 0; p <= nparts; p++) a.rt_begin[p] = rt_begin[p];
     a.nparts = nparts;
@@ -685,12 +713,15 @@ static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const
     a.status = status;
     const int stages = stages_for(planes_in_smem, ctas_per_sm, rows, mg);
     if (stages < 2) return cudaErrorInvalidConfiguration;
-    const SmemPlan sp = plan_smem(DT, mg, planes_in_smem, rows, (int)k, stages, stage_bytes);
+    const SmemPlan sp = plan_smem(DT, mg, planes_in_smem, rows, (int)k, stages, stage_bytes, DT2);
     a.stages = stages;
     a.stage_bytes = stage_bytes;
     a.sp = sp;
     cudaError_t e;
-    if (act_mode == ACT_FUSED) {
+    if constexpr (MIXED) {
+      e = act_mode == ACT_FUSED ? launch_one<DT, 1, ACT_FUSED, DT2>(a, grid, sp.total, s)
+                                : launch_one<DT, 1, ACT_STAGED, DT2>(a, grid, sp.total, s, true);
+    } else if (act_mode == ACT_FUSED) {
       e = launch_one<DT, 1, ACT_FUSED>(a, grid, sp.total, s);
     } else if (act_mode == ACT_STAGED) {
       e = mg == 1 ? launch_one<DT, 1, ACT_STAGED>(a, grid, sp.total, s, true) : launch_one<DT, 2, ACT_STAGED>(a, grid, sp.total, s, true);
@@ -707,22 +738,61 @@ static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const
   return cudaSuccess;
 }
 
-cudaError_t launch_gemv_int8_multi(int dtype, const GemvPart* parts, int nparts, int64_t k, const void* x, int x_dtype,
+#define TQ_LAUNCH_ARGS k, x, x_dtype, act_scratch, m, workspace, status, sm_count, s, launches
+
+static cudaError_t launch_one_type(int dtype, const GemvPart* parts, int nparts, int64_t k, const void* x, int x_dtype,
                                    uint8_t* act_scratch, int64_t m, uint8_t* workspace, int* status, int sm_count,
                                    cudaStream_t s, int* launches) {
   switch (dtype) {
-    case TQ_Q8_0: return launch_dt<TQ_Q8_0>(parts, nparts, k, x, x_dtype, act_scratch, m, workspace, status, sm_count, s, launches);
-    case TQ_Q4_K: return launch_dt<TQ_Q4_K>(parts, nparts, k, x, x_dtype, act_scratch, m, workspace, status, sm_count, s, launches);
-    case TQ_Q5_K: return launch_dt<TQ_Q5_K>(parts, nparts, k, x, x_dtype, act_scratch, m, workspace, status, sm_count, s, launches);
-    case TQ_Q6_K: return launch_dt<TQ_Q6_K>(parts, nparts, k, x, x_dtype, act_scratch, m, workspace, status, sm_count, s, launches);
+    case TQ_Q8_0: return launch_dt<TQ_Q8_0>(parts, nparts, TQ_LAUNCH_ARGS);
+    case TQ_Q4_K: return launch_dt<TQ_Q4_K>(parts, nparts, TQ_LAUNCH_ARGS);
+    case TQ_Q5_K: return launch_dt<TQ_Q5_K>(parts, nparts, TQ_LAUNCH_ARGS);
+    case TQ_Q6_K: return launch_dt<TQ_Q6_K>(parts, nparts, TQ_LAUNCH_ARGS);
     default: return cudaErrorInvalidValue;
   }
 }
 
+// parts[i].dtype = 0 means `dtype`. Parts of one type go out as one launch; Q4_K or Q5_K parts
+// together with Q6_K parts too, where the mixed kernel exists; anything else one launch per type.
+cudaError_t launch_gemv_int8_multi(int dtype, const GemvPart* parts, int nparts, int64_t k, const void* x, int x_dtype,
+                                   uint8_t* act_scratch, int64_t m, uint8_t* workspace, int* status, int sm_count,
+                                   cudaStream_t s, int* launches) {
+  if (nparts < 1 || nparts > MAX_PARTS) return cudaErrorInvalidValue;
+  GemvPart p[MAX_PARTS];
+  int types[MAX_PARTS], ntypes = 0;
+  for (int i = 0; i < nparts; i++) {
+    p[i] = parts[i];
+    if (p[i].dtype == 0) p[i].dtype = dtype;
+    bool seen = false;
+    for (int t = 0; t < ntypes; t++) seen = seen || types[t] == p[i].dtype;
+    if (!seen) types[ntypes++] = p[i].dtype;
+  }
+  if (ntypes == 1) return launch_one_type(types[0], p, nparts, TQ_LAUNCH_ARGS);
+  static const int mixed_env = getenv("TURQ_GEMV_MIXED") ? atoi(getenv("TURQ_GEMV_MIXED")) : 1;
+  if (ntypes == 2 && mixed_env) {
+    const int other = types[0] == TQ_Q6_K ? types[1] : types[0];
+    if ((types[0] == TQ_Q6_K || types[1] == TQ_Q6_K) && (other == TQ_Q4_K || other == TQ_Q5_K)) {
+      cudaError_t e = other == TQ_Q4_K ? launch_dt<TQ_Q4_K, TQ_Q6_K>(p, nparts, TQ_LAUNCH_ARGS)
+                                       : launch_dt<TQ_Q5_K, TQ_Q6_K>(p, nparts, TQ_LAUNCH_ARGS);
+      if (e != cudaErrorNotSupported) return e;
+    }
+  }
+  for (int t = 0; t < ntypes; t++) {
+    GemvPart q[MAX_PARTS];
+    int nq = 0;
+    for (int i = 0; i < nparts; i++)
+      if (p[i].dtype == types[t]) q[nq++] = p[i];
+    cudaError_t e = launch_one_type(types[t], q, nq, TQ_LAUNCH_ARGS);
+    if (e != cudaSuccess) return e;
+  }
+  return cudaSuccess;
+}
+#undef TQ_LAUNCH_ARGS
+
 cudaError_t launch_gemv_int8(int dtype, const uint8_t* tiles, int64_t n_rows, int64_t k, const void* x, int x_dtype,
                              uint8_t* act_scratch, int64_t m, float* y, const float* bias, uint8_t* workspace,
                              int* status, int sm_count, cudaStream_t s, int* launches) {
-  GemvPart part{tiles, n_rows, y, bias};
+  GemvPart part{tiles, n_rows, y, bias, dtype};
   return launch_gemv_int8_multi(dtype, &part, 1, k, x, x_dtype, act_scratch, m, workspace, status, sm_count, s, launches);
 }
 

@@ -39,13 +39,15 @@ bool gemv_int8_fuses_act(int dtype, int64_t m, int64_t k);
 cudaError_t launch_gemv_int8(int dtype, const uint8_t* tiles, int64_t n_rows, int64_t k, const void* x,
                              int x_dtype, uint8_t* act_scratch, int64_t m, float* y, const float* bias,
                              uint8_t* workspace, int* status, int sm_count, cudaStream_t s, int* launches);
-// The same for several weights of one dtype and in-feature count that share x: one launch over
-// the concatenated rows (q|k|v, gate|up), each part with its own output and bias.
+// The same for several weights of one in-feature count that share x: one launch over the
+// concatenated rows (q|k|v, gate|up) per weight type - and a single one for Q4_K or Q5_K parts
+// beside Q6_K parts at up to 8 rows - each part with its own output and bias.
 struct GemvPart {
   const uint8_t* tiles;
   int64_t n_rows;
   float* y;
   const float* bias;
+  int dtype;  // TQ_* of this part's tiles; 0 = the launch's dtype argument
 };
 cudaError_t launch_gemv_int8_multi(int dtype, const GemvPart* parts, int nparts, int64_t k, const void* x,
                                    int x_dtype, uint8_t* act_scratch, int64_t m, uint8_t* workspace, int* status,
