@@ -556,14 +556,14 @@ static int smem_budget() {
 
 // In-kernel quantization is redundant work in every CTA and every CTA reads the same few
 // cache lines of x: one pass (16 Q8_K blocks, or 64 Q8_0 blocks, per CTA) costs about as much
-// as the weight ring takes to fill, so it is only used for one row or up to two passes.
+// as the weight ring takes to fill, so it is only used for up to 4096 activation values - one
+// pass of Q8_K blocks, two of Q8_0 blocks (measured at one
+// row: Q4_K 5120x8192, two passes, 12.2 us fused against 11.4 us with the planes quantized by a
+// launch of their own and bulk-copied; Q6_K 4096x12288, three passes, 15.0 against 12.4 us).
 bool gemv_int8_fuses_act(int dtype, int64_t m, int64_t k) {
-  if (m > 8) return false;
-  const int64_t plane = m * (k + 32) + m * (k / 16) * 4 + 1024;
-  if (plane > 64 * 1024) return false;
-  static const int max_passes = getenv("TURQ_GEMV_FUSE_PASSES") ? atoi(getenv("TURQ_GEMV_FUSE_PASSES")) : 2;
-  const int64_t passes = dtype == TQ_Q8_0 ? (m * ((k / 32 + 7) / 8) + NW - 1) / NW : (m * (k / 256) + 2 * NW - 1) / (2 * NW);
-  return m == 1 || passes <= max_passes;
+  (void)dtype;
+  static const int max_elems = getenv("TURQ_GEMV_FUSE_ELEMS") ? atoi(getenv("TURQ_GEMV_FUSE_ELEMS")) : 4096;
+  return m <= 8 && m * k <= max_elems;
 }
 
 // partial sums [up to 4 CTAs per SM][4 groups of 8 rows][128] + one flag per CTA
