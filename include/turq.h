@@ -116,6 +116,14 @@ int32_t turq_qtensor_info(const turq_qtensor* qt, int32_t* dtype, int64_t* n_row
 int32_t turq_dequantize(turq_ctx* ctx, const turq_qtensor* qt, int32_t out_dtype, void* dev_out,
                         void* stream);
 
+/* Embedding lookup on a table that stays quantized (src/models/layers/mod.rs:30-48 dequantizes
+ * the whole token_embd tensor and indexes it; qwen3.rs:691-700): dev_out[i, :] =
+ * dequantize(row dev_ids[i]), [n_ids, n_cols] row-major of out_dtype, the same bits as
+ * turq_dequantize gives for that row. dev_ids are int32 on the device. An id outside the table
+ * gives a row of zeros and turq_ctx_poll_status then reports TURQ_E_INVALID_ARG. */
+int32_t turq_embedding(turq_ctx* ctx, const turq_qtensor* qt, const int32_t* dev_ids, int64_t n_ids,
+                       int32_t out_dtype, void* dev_out, void* stream);
+
 /* Activation quantization used inside QMatMul::forward (entered at
  * src/models/layers/linear.rs:24): x [m, k] (F32 or BF16) -> wire-format Q8_0 or Q8_K blocks,
  * m rows of turq_row_bytes(fmt, k) bytes. */

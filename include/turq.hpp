@@ -83,6 +83,11 @@ class QTensor {
   void dequantize(void* dev_out, GgmlDType out_dtype = GgmlDType::F32, void* stream = nullptr) const {
     ctx_->check(turq_dequantize(ctx_->handle(), h_, static_cast<int32_t>(out_dtype), dev_out, stream));
   }
+  // Embedding lookup on the quantized table: dev_out[i, :] = dequantize(row dev_ids[i]).
+  void embedding(const int32_t* dev_ids, int64_t n_ids, void* dev_out, GgmlDType out_dtype = GgmlDType::F32,
+                 void* stream = nullptr) const {
+    ctx_->check(turq_embedding(ctx_->handle(), h_, dev_ids, n_ids, static_cast<int32_t>(out_dtype), dev_out, stream));
+  }
   // Tensor-parallel shards (own memory).
   std::shared_ptr<QTensor> slice_rows(int64_t row0, int64_t n) const {
     turq_qtensor* h = nullptr;

@@ -340,6 +340,35 @@ def test_mixed_type_launch_for_attn_qkv(tq, dt, m):
         assert oracle.rel_fro(ys[i].cpu().numpy(), want) < 1e-5
 
 
+@pytest.mark.parametrize("dt", TYPES, ids=ids)
+def test_embedding_lookup_equals_dequantize_then_index(tq, dt):
+    """tur dequantizes token_embd and indexes the f32 table (src/models/layers/mod.rs:30-48);
+    the lookup on the quantized table must give those bits, for any id order and repeats."""
+    n, k = 1000, 2560
+    w = make_weight(dt, n, k, SEED + 31)
+    qt = tq.QTensor.new(w, tq.GgmlDType(dt), (n, k))
+    full = qt.dequantize()
+    rng = np.random.default_rng(SEED + 32)
+    ids = torch.from_numpy(rng.integers(0, n, size=(3, 37))).cuda()
+    ids[0, 0], ids[0, 1], ids[2, 36] = 0, n - 1, 15
+    got = qt.embedding(ids)
+    assert got.shape == (3, 37, k)
+    assert torch.equal(got, full[ids])
+    assert torch.equal(qt.embedding(ids, torch.bfloat16), full[ids].to(torch.bfloat16))
+    assert np.array_equal(got[0, 1].cpu().numpy(), oracle.dequantize(dt, w, k)[n - 1])
+    assert qt.embedding(ids[:0]).shape == (0, 37, k)
+    tq.context().poll_status()
+    # an id outside the table: zero row, reported at the next status poll, context stays usable
+    bad = torch.tensor([5, n, 7], device="cuda")
+    out = qt.embedding(bad)
+    assert torch.equal(out[0], full[5]) and torch.equal(out[2], full[7]) and not out[1].any()
+    with pytest.raises(tq.TurqError) as e:
+        tq.context().poll_status()
+    assert e.value.status == 1
+    tq.context().poll_status()
+    assert torch.equal(qt.embedding(ids), full[ids])
+
+
 def test_no_kernel_gave_up_a_wait(tq):
     tq.context().poll_status()
 

@@ -33,6 +33,7 @@ SIGNATURES = {
     "turq_qtensor_info": (c_i32, [c_vp, ctypes.POINTER(c_i32), ctypes.POINTER(c_i64),
                                   ctypes.POINTER(c_i64), ctypes.POINTER(c_sz)]),
     "turq_dequantize": (c_i32, [c_vp, c_vp, c_i32, c_vp, c_vp]),
+    "turq_embedding": (c_i32, [c_vp, c_vp, c_vp, c_i64, c_i32, c_vp, c_vp]),
     "turq_quantize_act": (c_i32, [c_vp, c_i32, c_vp, c_i32, c_i64, c_i64, c_vp, c_vp]),
     "turq_qmatmul": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i64, c_vp, c_i32, c_vp, c_vp]),
     "turq_qmatmul_multi": (c_i32, [c_vp, c_i32, c_vp, c_vp, c_i32, c_i64, c_vp, c_i32, c_vp, c_vp]),

@@ -186,6 +186,7 @@ int32_t turq_ctx_poll_status(turq_ctx* ctx, void* stream) {
     // a kernel that gave up may have left hand-over flags or claim counters set
     cudaMemsetAsync(ctx->gemv_ws, 0, turq::gemv_workspace_bytes(ctx->sm_count), s);
     cudaStreamSynchronize(s);
+    if (st == TURQ_E_INVALID_ARG) return fail(ctx, st, "an embedding lookup was given an id outside the table");
     return fail(ctx, st, "a kernel gave up a bounded device-side wait (status %d)", st);
   }
   return TURQ_OK;
@@ -314,6 +315,24 @@ int32_t turq_dequantize(turq_ctx* ctx, const turq_qtensor* qt, int32_t out_dtype
                                        static_cast<cudaStream_t>(stream));
   ctx->launches++;
   if (e != cudaSuccess) return cuda_fail(ctx, e, "dequantize launch");
+  return TURQ_OK;
+}
+
+int32_t turq_embedding(turq_ctx* ctx, const turq_qtensor* qt, const int32_t* dev_ids, int64_t n_ids, int32_t out_dtype,
+                       void* dev_out, void* stream) {
+  if (!ctx || !qt) return fail(ctx, TURQ_E_INVALID_ARG, "null argument");
+  if (n_ids < 0) return fail(ctx, TURQ_E_SHAPE, "n_ids=%lld is negative", (long long)n_ids);
+  if (n_ids == 0) return TURQ_OK;
+  if (!dev_out || !dev_ids) return fail(ctx, TURQ_E_INVALID_ARG, "null argument");
+  if (out_dtype != TURQ_F32 && out_dtype != TURQ_F16 && out_dtype != TURQ_BF16)
+    return fail(ctx, TURQ_E_DTYPE, "embedding output must be F32, F16 or BF16 (got %d)", out_dtype);
+  if (qt->device != ctx->device) return fail(ctx, TURQ_E_INVALID_ARG, "tensor lives on device %d, context on %d", qt->device, ctx->device);
+  if ((uintptr_t)dev_out % 16 != 0 || (uintptr_t)dev_ids % 4 != 0) return fail(ctx, TURQ_E_ALIGN, "dev_out must be 16-byte, dev_ids 4-byte aligned");
+  TQ_CUDA(ctx, cudaSetDevice(ctx->device));
+  cudaError_t e = turq::launch_gather_rows(qt->dtype, qt->tiles, dev_ids, dev_out, out_dtype, qt->n_rows, n_ids, qt->n_cols,
+                                           ctx->dev_status, static_cast<cudaStream_t>(stream));
+  ctx->launches++;
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "embedding launch");
   return TURQ_OK;
 }
 

@@ -74,6 +74,75 @@ static cudaError_t launch_dt(const uint8_t* tiles, void* out, int out_dtype, int
   return cudaGetLastError();
 }
 
+// Embedding lookup on the quantized table: out[i, :] = dequantize(row ids[i]). One warp per
+// (id, K-tile); the warp decodes the tile holding the row with the same code as the full
+// dequantize (so the values are the same bits) and the four lanes that own the row store it.
+// An id outside [0, n_rows) gives a row of zeros and raises the status word.
+template <int DT, class T>
+__global__ void __launch_bounds__(256) gather_rows_kernel(const uint8_t* __restrict__ tiles, const int32_t* __restrict__ ids,
+                                                          T* __restrict__ out, int64_t n_rows, int64_t n_ids, int64_t k,
+                                                          int64_t ktiles, int* __restrict__ status) {
+  constexpr int TB = 16 * (DT == TQ_Q8_0 ? 34 : DT == TQ_Q4_K ? 144 : DT == TQ_Q5_K ? 176 : 210);
+  constexpr int KE = DT == TQ_Q8_0 ? 32 : 256;
+  const int lane = threadIdx.x & 31;
+  const int g = lane >> 2;
+  int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const int64_t total = n_ids * ktiles;
+  for (int64_t u = warp; u < total; u += nwarps) {
+    const int64_t i = u / ktiles, kt = u - i * ktiles;
+    const int64_t row = ids[i];
+    T* dst = out + i * k + kt * KE;
+    if (row < 0 || row >= n_rows) {
+      for (int e = lane; e < KE; e += 32) dst[e] = cvt_out<T>(0.f);
+      if (lane == 0 && kt == 0) {
+        *reinterpret_cast<volatile int*>(status) = 1;  // TURQ_E_INVALID_ARG; the word may be mapped host memory
+        __threadfence_system();
+      }
+      continue;
+    }
+    const int r16 = (int)(row & 15);
+    const uint8_t* t = tiles + ((row >> 4) * ktiles + kt) * TB;
+    decode_tile<DT>(t, lane, [&](int hr, int off, const auto& v) {
+      if (g + 8 * hr == r16) store_run(dst + off, v);
+    });
+  }
+}
+
+template <int DT>
+static cudaError_t launch_gather_dt(const uint8_t* tiles, const int32_t* ids, void* out, int out_dtype, int64_t n_rows,
+                                    int64_t n_ids, int64_t k, int* status, cudaStream_t s) {
+  const int64_t ktiles = k / tq_block_elems(DT);
+  const int64_t total = n_ids * ktiles;
+  if (total == 0) return cudaSuccess;
+  int64_t blocks = (total + 7) / 8;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  switch (out_dtype) {
+    case TQ_F32:
+      gather_rows_kernel<DT, float><<<(unsigned)blocks, 256, 0, s>>>(tiles, ids, (float*)out, n_rows, n_ids, k, ktiles, status);
+      break;
+    case TQ_F16:
+      gather_rows_kernel<DT, __half><<<(unsigned)blocks, 256, 0, s>>>(tiles, ids, (__half*)out, n_rows, n_ids, k, ktiles, status);
+      break;
+    case TQ_BF16:
+      gather_rows_kernel<DT, __nv_bfloat16><<<(unsigned)blocks, 256, 0, s>>>(tiles, ids, (__nv_bfloat16*)out, n_rows, n_ids, k, ktiles, status);
+      break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gather_rows(int dtype, const uint8_t* dev_tiles, const int32_t* dev_ids, void* dev_out, int out_dtype,
+                               int64_t n_rows, int64_t n_ids, int64_t k, int* status, cudaStream_t s) {
+  switch (dtype) {
+    case TQ_Q8_0: return launch_gather_dt<TQ_Q8_0>(dev_tiles, dev_ids, dev_out, out_dtype, n_rows, n_ids, k, status, s);
+    case TQ_Q4_K: return launch_gather_dt<TQ_Q4_K>(dev_tiles, dev_ids, dev_out, out_dtype, n_rows, n_ids, k, status, s);
+    case TQ_Q5_K: return launch_gather_dt<TQ_Q5_K>(dev_tiles, dev_ids, dev_out, out_dtype, n_rows, n_ids, k, status, s);
+    case TQ_Q6_K: return launch_gather_dt<TQ_Q6_K>(dev_tiles, dev_ids, dev_out, out_dtype, n_rows, n_ids, k, status, s);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
 cudaError_t launch_dequant(int dtype, const uint8_t* dev_tiles, void* dev_out, int out_dtype, int64_t n_rows,
                            int64_t k, cudaStream_t s) {
   switch (dtype) {

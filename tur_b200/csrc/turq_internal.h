@@ -18,6 +18,10 @@ cudaError_t launch_repack(int dtype, const uint8_t* dev_wire, uint8_t* dev_tiles
 // device tiles -> row-major [n_rows, k]
 cudaError_t launch_dequant(int dtype, const uint8_t* dev_tiles, void* dev_out, int out_dtype,
                            int64_t n_rows, int64_t k, cudaStream_t s);
+// out[i, :] = dequantize(row dev_ids[i]) for an embedding table kept quantized; ids outside the
+// table give zero rows and raise the status word (TURQ_E_INVALID_ARG).
+cudaError_t launch_gather_rows(int dtype, const uint8_t* dev_tiles, const int32_t* dev_ids, void* dev_out, int out_dtype,
+                               int64_t n_rows, int64_t n_ids, int64_t k, int* status, cudaStream_t s);
 // copy K-tile range [kt0, kt0+nkt) of every row-tile into a new tiled tensor
 cudaError_t launch_slice_cols(int dtype, const uint8_t* src_tiles, uint8_t* dst_tiles,
                               int64_t row_tiles, int64_t src_ktiles, int64_t kt0, int64_t nkt,

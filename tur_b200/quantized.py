@@ -170,6 +170,19 @@ class QTensor:
                                                     ctypes.c_void_p(out.data_ptr()), _stream_ptr(self._ctx.device)))
         return out
 
+    def embedding(self, ids: torch.Tensor, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        """Embedding lookup on the quantized table (tur dequantizes token_embd once and indexes
+        it, src/models/layers/mod.rs:30-48): ids [...] of any integer dtype -> [..., n_cols], the
+        bits `dequantize()[ids]` would give. Ids outside the table give zero rows and make the
+        next `poll_status()` raise."""
+        dev = self.device()
+        flat = ids.reshape(-1).to(device=dev, dtype=torch.int32).contiguous()
+        out = torch.empty((flat.numel(), self._shape[1]), dtype=out_dtype, device=dev)
+        self._ctx.check(_lib.load().turq_embedding(self._ctx.handle, self._h, ctypes.c_void_p(flat.data_ptr()), flat.numel(),
+                                                   int(_TORCH_TO_GGML[out_dtype]), ctypes.c_void_p(out.data_ptr()),
+                                                   _stream_ptr(self._ctx.device)))
+        return out.reshape(*ids.shape, self._shape[1])
+
     def slice_rows(self, row0: int, n: int) -> "QTensor":
         out = ctypes.c_void_p()
         self._ctx.check(_lib.load().turq_qtensor_slice_rows(self._ctx.handle, self._h, row0, n, ctypes.byref(out)))
