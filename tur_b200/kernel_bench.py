@@ -40,7 +40,7 @@ def random_blocks(dtype: int, n: int, k: int, seed: int, device) -> torch.Tensor
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="qmatmul", choices=["qmatmul", "dequantize"])
+    ap.add_argument("--op", default="qmatmul", choices=["qmatmul", "dequantize", "embedding"])
     ap.add_argument("--dtype", default="Q4_K", choices=sorted(NAMES))
     ap.add_argument("--n", type=int, default=12288)
     ap.add_argument("--k", type=int, default=4096)
@@ -77,6 +77,16 @@ def main() -> None:
             w.forward(x, mode=mode, out=y)
         alg_bytes = wbytes + args.m * args.k * x.element_size() + args.m * args.n * 4
         flops = 2.0 * args.m * args.n * args.k
+    elif args.op == "embedding":
+        # --m ids drawn from the table's rows; algorithmic bytes = the rows read + the f32 rows written
+        ids = torch.from_numpy(rng.integers(0, args.n, size=args.m)).to(dev).to(torch.int32)
+        out = torch.empty((args.m, args.k), dtype=torch.float32, device=dev)
+
+        def call(w):
+            ctx.check(__import__("tur_b200")._lib.load().turq_embedding(
+                ctx.handle, w.qtensor._h, ids.data_ptr(), args.m, 0, out.data_ptr(), torch.cuda.current_stream().cuda_stream))
+        alg_bytes = args.m * (args.k // be) * bb + args.m * args.k * 4
+        flops = 0.0
     else:
         out = torch.empty((args.n, args.k), dtype=torch.float32, device=dev)
 
