@@ -139,10 +139,11 @@ int32_t turq_qmatmul(turq_ctx* ctx, const turq_qtensor* qt, const void* dev_x, i
 
 /* Several linears that read the same x (attn_q|k|v: src/models/qwen3.rs:272-274; ffn_gate|up:
  * qwen3.rs:162-166) in one call: count <= 4 weights with the same in-feature count, y[i] is
- * [m, rows of qts[i]], biases may be NULL or hold NULL entries. Weights of the same type run as
- * ONE kernel launch over their concatenated rows in the integer scheme; anything else falls
- * back to one launch per weight. Results equal those of separate turq_qmatmul calls up to the
- * f32 summation order. */
+ * [m, rows of qts[i]], biases may be NULL or hold NULL entries. In the integer scheme, weights
+ * of the same type run as ONE kernel launch over their concatenated rows, and so do Q4_K or
+ * Q5_K weights together with Q6_K ones (the K-quant mixes keep attn_v in Q6_K) up to m = 8;
+ * other combinations get one launch per type, other modes one call per weight. Results equal
+ * those of separate turq_qmatmul calls up to the f32 summation order. */
 int32_t turq_qmatmul_multi(turq_ctx* ctx, int32_t count, const turq_qtensor* const* qts,
                            const void* dev_x, int32_t x_dtype, int64_t m, float* const* dev_ys,
                            int32_t mode, const float* const* dev_biases, void* stream);
