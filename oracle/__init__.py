@@ -52,10 +52,17 @@ def build(force: bool = False) -> str:
     stale = (not os.path.exists(out)
              or os.path.getmtime(out) < max(os.path.getmtime(src), os.path.getmtime(hdr)))
     if force or stale:
+        # several ranks may get here at once: each compiles into a file of its own and moves it
+        # into place atomically, so nobody ever loads a half-written library
+        tmp = f"{out}.{os.getpid()}.tmp"
         cmd = ["gcc", "-O3", "-march=native", "-fopenmp", "-fPIC", "-ffp-contract=off",
-               "-fno-fast-math", "-std=c11", "-shared", "-o", out + ".tmp", src, "-lm"]
-        subprocess.run(cmd, check=True, cwd=_HERE)
-        os.replace(out + ".tmp", out)
+               "-fno-fast-math", "-std=c11", "-shared", "-o", tmp, src, "-lm"]
+        try:
+            subprocess.run(cmd, check=True, cwd=_HERE)
+            os.replace(tmp, out)
+        finally:
+            if os.path.exists(tmp):
+                os.remove(tmp)
     return out
 
 

@@ -56,9 +56,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
             if verbose and log:
                 sys.stderr.write(log)
     if jobs or force or _stale(OUT, objs):
-        run([_nvcc(), "-shared", "-o", OUT + ".tmp", *objs, "-gencode", "arch=compute_100a,code=sm_100a",
+        tmp = f"{OUT}.{os.getpid()}.tmp"   # unique per process: concurrent builders never share a file
+        run([_nvcc(), "-shared", "-o", tmp, *objs, "-gencode", "arch=compute_100a,code=sm_100a",
              "-lcudart"])
-        os.replace(OUT + ".tmp", OUT)
+        os.replace(tmp, OUT)
     return OUT
 
 
