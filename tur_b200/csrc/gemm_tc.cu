@@ -24,6 +24,7 @@
 
 #include "device_utils.cuh"
 #include "gemv_tile.cuh"
+#include "launch_plan.h"
 #include "turq_internal.h"
 
 namespace turq {
@@ -554,31 +555,14 @@ cudaError_t launch_tc_dt(const CUtensorMap& map, const GemmArgs& a, int bn, cuda
 
 }  // namespace
 
-// Activation rows per CTA: 64 for decode batches; 256 for prefill, unless twice as many CTAs
-// still fit the SMs in one wave - then 128, which doubles the CTA count for the same work.
 static int pick_bn(int64_t n_rows, int64_t m, int sm_count) {
   static const int bn_env = getenv("TURQ_GEMM_BN") ? atoi(getenv("TURQ_GEMM_BN")) : 0;
-  if (bn_env == 64 || bn_env == 128 || bn_env == 256) return bn_env;
-  int bn = m <= 64 ? 64 : 256;
-  if (bn == 256 && 2 * ((n_rows + BM - 1) / BM) * ((m + 255) / 256) <= sm_count) bn = 128;
-  return bn;
+  return plan_gemm_bn(n_rows, m, sm_count, bn_env);
 }
 
-// Split-K for decode batches (one 64-row activation tile): when the 128-row weight tiles alone
-// leave SMs without a CTA, the K loop of every tile is shared out over several CTAs (at least 8
-// blocks of 64 each); their partial sums go to scratch and a small launch adds them in a fixed
-// order. The split depends on the weight's shape only, so a row's result does not depend on
-// the batch it is in; prefill (more than 64 rows) never splits.
 static int pick_splits(int64_t n_rows, int64_t m, int64_t k, int sm_count) {
   static const int env = getenv("TURQ_GEMM_SPLITK") ? atoi(getenv("TURQ_GEMM_SPLITK")) : -1;
-  if (m > 64 || env == 0) return 1;
-  const int64_t tiles = (n_rows + BM - 1) / BM;
-  int64_t s = sm_count / tiles;
-  const int64_t by_k = (k / BK) / 8;
-  if (env > 0) s = env;
-  if (s > by_k) s = by_k;
-  if (s > 16) s = 16;
-  return s < 2 ? 1 : (int)s;
+  return plan_gemm_splits(n_rows, m, k, sm_count, env);
 }
 
 size_t gemm_tc_scratch_bytes(int64_t m, int64_t k, int64_t n_rows, int sm_count) {

@@ -24,6 +24,7 @@
 
 #include "actquant.cuh"
 #include "gemv_tile.cuh"
+#include "launch_plan.h"
 #include "turq_internal.h"
 
 namespace turq {
@@ -653,24 +654,9 @@ static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const
   // in tiles, with the hand-over of split row-tiles. Depends on the shape only, never on M.
   const int slots = sm_count * ctas_per_sm;
   const int row_tiles_all = rt_begin[nparts];
-  int grid = slots, split_q, split_r;
-  {
-    const int per = (row_tiles_all + slots - 1) / slots;
-    const int ga = (row_tiles_all + per - 1) / per;
-    static const int split_env = getenv("TURQ_GEMV_SPLIT") ? atoi(getenv("TURQ_GEMV_SPLIT")) : -1;
-    bool aligned = ga * 10 >= slots * 7 || T <= (int64_t)slots * 24;
-    if (split_env == 0) aligned = false;
-    if (split_env == 1) aligned = true;
-    if (aligned) {
-      grid = ga;
-      split_q = per * KU;
-      split_r = 0;
-    } else {
-      if ((int64_t)grid > T) grid = (int)T;
-      split_q = (int)(T / grid);
-      split_r = (int)(T % grid);
-    }
-  }
+  static const int split_env = getenv("TURQ_GEMV_SPLIT") ? atoi(getenv("TURQ_GEMV_SPLIT")) : -1;
+  const GemvSplit split = plan_gemv_split(row_tiles_all, KU, slots, split_env);
+  const int grid = split.grid, split_q = split.split_q, split_r = split.split_r;
   const size_t x_es = x_dtype == TQ_BF16 ? 2 : 4;
   ActPackPlan plan = plan_act_pack(fmt, m, k);
   if (!fused) {
