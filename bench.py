@@ -126,9 +126,12 @@ def cpu_scheme_timing(wl, m: int, budget_s: float, steps: int | None = None, war
           enumerate(sorted({(w.source, w.k) for w in wl.per_layer}))}
     layer_bytes = wl.layer_bytes()
 
+    # all host threads this process may use, also under torchrun (which sets OMP_NUM_THREADS=1)
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+
     def one_pass():
         for w, b in ws:
-            oracle.qmatmul(w.dtype, b, w.n, w.k, xs[w.source])
+            oracle.qmatmul(w.dtype, b, w.n, w.k, xs[w.source], nthreads=cores)
 
     for _ in range(max(1, warmup)):
         one_pass()
@@ -140,7 +143,7 @@ def cpu_scheme_timing(wl, m: int, budget_s: float, steps: int | None = None, war
         times.append(time.perf_counter() - t0)
     med = statistics.median(times)
     sample = f"one layer of {wl.name} (7 linears, {layer_bytes / 1e6:.1f} MB of blocks), M={m}, {len(times)} passes, median"
-    return layer_bytes / med / 1e9, oracle.num_threads(), sample, med * 1e3, len(times)
+    return layer_bytes / med / 1e9, cores, sample, med * 1e3, len(times)
 
 
 def run_reference(args):
