@@ -2,8 +2,10 @@
 """Benchmark of the quantized-linear path: one step = one decode pass (M activation rows)
 through every quantized linear of the named model's stack, weights resident in HBM.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2] [--m 1]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2] [--rows 1]
   python bench.py --impl reference ...      # the CPU scheme on the host cores
+  python bench.py --workload cfg2 --rows 2048 --mode TENSOR_CORE --xdtype bf16 --no-head   # prefill (config.tflops)
+  torchrun ... bench.py --gpus N --workload cfg5 --tp --rows 64 --mode AUTO               # tensor-parallel pass
 
 Prints ONE JSON line. `value` is weight bytes streamed per second over all GPUs (the
 "QMatMul weight GB/s" metric); `e2e` is the same pass driven through the host-buffer entry
