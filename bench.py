@@ -45,6 +45,15 @@ def measured_peaks():
         return 6650.0, "fallback"
 
 
+def measured_tensor_peak():
+    """Burst bf16/f16 dense TFLOP/s (the denominator for a kernel timed alone)."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured"
+    except Exception:
+        return 1590.0, "fallback"
+
+
 # ------------------------------------------------------------------ synthetic inputs
 
 def gen_weight_blocks(w: Weight, seed: int, max_rows: int = 16384) -> np.ndarray:
@@ -321,14 +330,19 @@ def run_gpu(args):
         barrier()
         e2e_ms = max(e0.elapsed_time(e1), wall)
 
-    # ---- dominant kernel, timed alone over the layers' distinct buffers
-    dom = max(wl.per_layer, key=lambda w: w.nbytes * (2 if w.name in ("ffn_gate", "ffn_up") else 1))
-    di = list(wl.per_layer).index(dom)
+    # ---- dominant launch, timed alone over the layers' distinct buffers: the group of linears
+    # sharing one x that moves the most bytes (ffn_gate|up in the decoder stacks), issued exactly
+    # as the pass issues it (one multi-weight launch unless --no-multi)
+    dom_names = max(groups, key=lambda g: sum(w.nbytes for w in wl.per_layer if w.name in g))
+    dom_ws = [w for w in wl.per_layer if w.name in dom_names]
+    dom = dom_ws[0]
     dg = torch.cuda.CUDAGraph()
+    l0 = sum(c.launch_count() for c in ctxs)
     with torch.cuda.stream(side):
         with torch.cuda.graph(dg, stream=side):
             for layer in layers:
-                layer[di][1].forward(x_dev[dom.source], mode=mode, out=y_dev[dom.name])
+                run_group([(w, mm) for w, mm in layer if w.name in dom_names])
+    dom_launches = (sum(c.launch_count() for c in ctxs) - l0) / len(layers)
     for _ in range(3):
         dg.replay()
     torch.cuda.synchronize()
@@ -338,9 +352,11 @@ def run_gpu(args):
         dg.replay()
     e1.record()
     torch.cuda.synchronize()
-    # each forward = activation-quantization launch + GEMV launch; the pair is timed together
+    # per group: the GEMV launch plus, where the activations are not quantized in the kernel,
+    # their quantization launch; timed together. x is read once for the whole group.
     dom_us = e0.elapsed_time(e1) * 1e3 / (reps * len(layers))
-    alg_bytes = dom.nbytes + m * dom.k * 4 + m * dom.n * 4
+    x_es = 2 if args.xdtype == "bf16" else 4
+    alg_bytes = sum(w.nbytes + m * w.n * 4 for w in dom_ws) + m * dom.k * x_es
 
     # ---- reduce over ranks
     if world > 1:
@@ -359,9 +375,29 @@ def run_gpu(args):
     value = total_bytes * args.steps / (ms * 1e-3) / 1e9
     peak, peak_kind = measured_peaks()
     achieved = alg_bytes / (dom_us * 1e-6) / 1e9
-    traffic = NCU_TRAFFIC_BYTES.get((dom.name, wl.name))
+    one = NCU_TRAFFIC_BYTES.get((dom.name, wl.name))
+    traffic = one * len(dom_ws) if one is not None and all((w.n, w.k, w.dtype) == (dom.n, dom.k, dom.dtype) for w in dom_ws) else None
     h2d = sum(m * w.k * 4 for w in wl.per_layer) * wl.layers + (m * head_w.k * 4 if head_w else 0)
     d2h = sum(m * w.n * 4 for w in wl.per_layer) * wl.layers + (m * head_w.n * 4 if head_w else 0)
+    members = " | ".join(f"{w.name} {TYPE_NAMES[w.dtype]} {w.n}x{w.k}" for w in dom_ws)
+    tensor_path = mode == Mode.TENSOR_CORE or (mode == Mode.AUTO and m > 16)
+    if tensor_path and m > 64:
+        # prefill runs the tcgen05 GEMM: bound by the tensor cores (decode batches of up to 64 rows
+        # stay bound by the weight stream whichever path computes them)
+        dom_flops = 2.0 * m * sum(w.n * w.k for w in dom_ws)
+        tpeak, tkind = measured_tensor_peak()
+        tf = dom_flops / (dom_us * 1e-6) / 1e12
+        roofline = {"bound": "tensor", "kernel": "gemm_tc (+ activation prep) " + members + " as issued in the pass",
+                    "achieved": tf, "peak": tpeak, "peak_kind": tkind, "unit": "TFLOP/s", "frac": tf / tpeak,
+                    "us_per_launch": dom_us, "launches": dom_launches, "algorithmic_flops": dom_flops, "traffic": None}
+    else:
+        roofline = {"bound": "hbm",
+                    "kernel": ("gemm_tc (+ activation prep, split-K reduction) " if tensor_path else "gemv_stream ") + members
+                              + " as issued in the pass (one multi-weight launch where the path has one; activation "
+                              "quantization included)",
+                    "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                    "us_per_launch": dom_us, "launches": dom_launches, "algorithmic_bytes": alg_bytes, "traffic": traffic,
+                    "traffic_note": "ncu capture of one member's launch scaled by the members of the group"}
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -383,9 +419,7 @@ def run_gpu(args):
             "api": "turq_qmatmul_host per linear (pinned host x and y)"},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": sampler.summary(),
-        "roofline": {"bound": "hbm", "kernel": f"gemv_int8 {TYPE_NAMES[dom.dtype]} {dom.n}x{dom.k} ({dom.name}) + its activation quantization",
-                     "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
-                     "us_per_launch": dom_us, "algorithmic_bytes": alg_bytes, "traffic": traffic},
+        "roofline": roofline,
     }
     if not args.no_cpu and world == 1:
         gbs, cores, sample, _, _ = cpu_scheme_timing(wl, m, budget_s=args.cpu_budget)
