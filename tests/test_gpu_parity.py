@@ -369,6 +369,28 @@ def test_embedding_lookup_equals_dequantize_then_index(tq, dt):
     assert torch.equal(qt.embedding(ids), full[ids])
 
 
+@pytest.mark.parametrize("second", [oracle.Q4_K, oracle.Q6_K], ids=["same_type", "mixed_types"])
+@pytest.mark.parametrize("m", [1, 5])
+def test_joint_launch_with_row_tiles_cut_between_ctas(tq, second, m):
+    """601 row-tiles of 16 K-tiles on 296 CTA slots: whole row-tiles per CTA would idle a third of
+    the slots, so the tiles are dealt out evenly and row-tiles are cut between CTAs (partial sums
+    handed over) - here across two weights of one launch, of one type or of two."""
+    k = 4096
+    shapes = [(oracle.Q4_K, 5000), (second, 4600)]
+    rng = np.random.default_rng(SEED + 555 + m)
+    ws = [make_weight(t, n, k, SEED + 900 + n) for t, n in shapes]
+    mms = [tq.QMatMul.from_arc(tq.QTensor.new(w, tq.GgmlDType(t), (n, k))) for w, (t, n) in zip(ws, shapes)]
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    first = [y.clone() for y in tq.QMatMul.forward_multi(mms, xd, mode=tq.Mode.INT8_ACT)]
+    for _ in range(3):
+        again = tq.QMatMul.forward_multi(mms, xd, mode=tq.Mode.INT8_ACT)
+        assert all(torch.equal(a, b) for a, b in zip(again, first))
+    tq.context().poll_status()
+    for y, w, (t, n) in zip(first, ws, shapes):
+        assert oracle.rel_fro(y.cpu().numpy(), oracle.qmatmul(t, w, n, k, x)) < 1e-5
+
+
 def test_no_kernel_gave_up_a_wait(tq):
     tq.context().poll_status()
 
