@@ -1,21 +1,25 @@
 // Decode-sized QMatMul::forward in the integer scheme, built to stay HBM-bound on B200.
 //
-//   * Persistent CTAs, two or three per SM: a producer warp streams device tiles (contiguous
-//     bytes) into a shared-memory ring with bulk async copies (cp.async.bulk, no multicast)
-//     that complete on mbarriers; 8 consumer warps each take one tile of a stage, read their
-//     fragment chunks from shared memory with 128-bit loads and run the integer MMAs of
-//     gemv_tile.cuh; an epilogue warp adds the consumers' partial sums and writes outputs, so
-//     consumers never meet at a CTA-wide barrier. The bytes in flight per SM are set by the
-//     ring, not by registers.
-//   * Programmatic dependent launch: the weight stream of a launch starts while the preceding
-//     kernel of the stream is still draining; only activations and outputs wait for it.
-//   * Work is split evenly over the CTAs in units of tiles (not rows): a CTA owns a
-//     contiguous tile range that may start or end inside a row-tile. The partial sums of a
-//     split row-tile go through a small global workspace and are added in CTA order by the
-//     CTA that holds the row-tile's first tile, so results are deterministic.
-//   * For small M*K the CTA quantizes the activations itself into shared memory while the
-//     first weight stages are in flight (no separate launch); otherwise it reads the planes a
-//     preceding activation-quantization launch left in global scratch.
+//   * Persistent CTAs, two per SM: a producer warp streams device tiles (contiguous bytes) into
+//     a shared-memory ring with bulk async copies (cp.async.bulk, no multicast) that complete
+//     on mbarriers; 8 consumer warps each take one tile of a stage, read their fragment chunks
+//     from shared memory with 128-bit loads and run the integer MMAs of gemv_tile.cuh; an
+//     epilogue warp adds the consumers' partial sums and writes outputs, so consumers never
+//     meet at a CTA-wide barrier. The bytes in flight per SM are set by the ring, not by
+//     registers.
+//   * Work split (launch_plan.h): whole row-tiles per CTA when that keeps the CTA slots busy,
+//     else an even split in tiles where a CTA's range may start or end inside a row-tile. The
+//     partial sums of a cut row-tile go through a small global workspace and are added in CTA
+//     order by the CTA that holds the row-tile's first tile, so results are deterministic.
+//   * Quantized activations (template parameter ACT): up to 4096 values the CTA quantizes
+//     them itself into shared memory while the first weight stages are in flight; otherwise a
+//     launch of its own quantizes them once into global scratch and the CTAs either bulk-copy
+//     the planes into shared memory (up to 16 rows, when they fit) or read them from global
+//     memory in the MMA loop. The GEMV that follows its quantization launch is started with
+//     programmatic stream serialization: its CTAs set up while that launch still runs and
+//     order themselves behind it with griddepcontrol.wait.
+//   * Several weights that share x run as one launch over their concatenated row-tiles, also
+//     Q4_K / Q5_K weights beside Q6_K ones (template parameter DT2).
 //
 // Every wait (mbarrier, cross-CTA flag) is bounded: on expiry the kernel records
 // TURQ_E_TIMEOUT in the status word, stops issuing work and returns.
