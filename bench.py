@@ -27,13 +27,13 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-from tur_b200.workloads import BLOCK, SEED, TYPE_NAMES, WORKLOADS, Weight  # noqa: E402
+from tur_b200.workloads import SEED, TYPE_NAMES, WORKLOADS, Weight  # noqa: E402
 
 METRIC = "qmatmul_decode_weight_bandwidth"
 UNIT = "GB/s"
-# per-launch DRAM traffic of the dominant kernel from the ncu capture summarised under
-# profiles/ (bytes; None until a capture exists for that kernel/shape)
-NCU_TRAFFIC_BYTES = {("ffn_gate", "cfg2"): 28365568}  # profiles/gemv_stream_q4k_12288x4096_m1.md
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, keyed by
+# (members of the launch, workload, rows); absent = never captured = reported as null
+NCU_TRAFFIC_BYTES = {}
 
 
 def measured_peaks():
@@ -128,14 +128,27 @@ class ClockSampler:
 
 # ------------------------------------------------------------------ CPU arm
 
-def cpu_scheme_timing(wl, m: int, budget_s: float, steps: int | None = None, warmup: int = 1):
-    """Times the CPU restatement of the reference's QMatMul::forward scheme (oracle/) on one
-    layer's seven linears with all host threads. Returns (GB/s of weight bytes, cores, sample)."""
-    import oracle
+def cpu_sample_weights(wl):
+    """The bounded sample both CPU legs time: 1/layers of a pass, i.e. one layer's seven linears
+    plus the same share of the head's rows, so that the weight mix of the pass is kept."""
     ws = [(w, gen_weight_blocks(w, SEED + i)) for i, w in enumerate(wl.per_layer)]
+    if wl.head is not None:
+        rows = max(16, (wl.head.n // wl.layers) // 16 * 16)
+        hw = Weight(wl.head.name, rows, wl.head.k, wl.head.dtype, wl.head.source, wl.head.parallel)
+        ws.append((hw, gen_weight_blocks(hw, SEED + 999)))
+    return ws
+
+
+def cpu_scheme_timing(wl, m: int, steps: int, warmup: int = 2, step_seconds: float = 0.5):
+    """Times the CPU restatement of the reference's QMatMul::forward scheme (oracle/) with all
+    host threads. One step = the bounded sample repeated `reps` times, reps chosen during the
+    warm-up so that a step takes about `step_seconds`; exactly `steps` steps are timed as one
+    region. Returns (GB/s of weight bytes, cores, sample text, ms per step, bytes per step)."""
+    import oracle
+    ws = cpu_sample_weights(wl)
     xs = {src: gen_activations(m, k, SEED + 10**6 + m + j) for j, (src, k) in
-          enumerate(sorted({(w.source, w.k) for w in wl.per_layer}))}
-    layer_bytes = wl.layer_bytes()
+          enumerate(sorted({(w.source, w.k) for w, _ in ws}))}
+    sample_bytes = sum(w.nbytes for w, _ in ws)
 
     # all host threads this process may use, also under torchrun (which sets OMP_NUM_THREADS=1)
     cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
@@ -144,17 +157,26 @@ def cpu_scheme_timing(wl, m: int, budget_s: float, steps: int | None = None, war
         for w, b in ws:
             oracle.qmatmul(w.dtype, b, w.n, w.k, xs[w.source], nthreads=cores)
 
+    one_pass()
+    t0 = time.perf_counter()
+    one_pass()
+    reps = int(min(100, max(1, round(step_seconds / max(time.perf_counter() - t0, 1e-6)))))
     for _ in range(max(1, warmup)):
-        one_pass()
-    times = []
-    t_end = time.perf_counter() + budget_s
-    while (steps is None and time.perf_counter() < t_end and len(times) < 200) or (steps is not None and len(times) < steps):
-        t0 = time.perf_counter()
-        one_pass()
-        times.append(time.perf_counter() - t0)
-    med = statistics.median(times)
-    sample = f"one layer of {wl.name} (7 linears, {layer_bytes / 1e6:.1f} MB of blocks), M={m}, {len(times)} passes, median"
-    return layer_bytes / med / 1e9, cores, sample, med * 1e3, len(times)
+        for _ in range(reps):
+            one_pass()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        for _ in range(reps):
+            one_pass()
+    per_step = (time.perf_counter() - t0) / steps
+    sample = (f"{reps} x 1/{wl.layers} of a {wl.name} pass per step: one layer's 7 linears"
+              + (f" + {ws[-1][0].n} of the lm_head's {wl.head.n} rows" if wl.head is not None else "")
+              + f" ({sample_bytes / 1e6:.1f} MB of blocks each), M={m}, {steps} steps timed as one region")
+    return reps * sample_bytes / per_step / 1e9, cores, sample, per_step * 1e3, reps * sample_bytes
+
+
+def workload_text(wl, m: int, head: bool) -> str:
+    return f"{wl.name}: {wl.description}, decode M={m}, {wl.layers} layers x 7 linears" + (" + lm_head" if head else "")
 
 
 def run_reference(args):
@@ -162,27 +184,182 @@ def run_reference(args):
     if rank != 0:
         return
     wl = WORKLOADS[args.workload]
-    gbs, cores, sample, ms, n = cpu_scheme_timing(wl, args.m, budget_s=1e9, steps=args.steps, warmup=args.warmup)
+    n = max(1, args.steps)
+    gbs, cores, sample, ms, _ = cpu_scheme_timing(wl, args.m, steps=n, warmup=args.warmup)
     line = {
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": n,
-        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "warmup": max(1, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8", "data": "synthetic",
-        "config": {"workload": f"{wl.name}: {wl.description}, decode M={args.m}", "sample": sample},
+        "config": {"workload": workload_text(wl, args.m, wl.head is not None and not args.no_head), "sample": sample},
         "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
         "note": "CPU restatement of the reference's quantized matmul scheme (candle-core is not vendored and no "
-                "Rust toolchain exists here); each step is one layer's seven linears on all host threads",
+                "Rust toolchain exists here) on all host threads; each step is the bounded sample named in "
+                "cpu_baseline.sample, value = its weight bytes per second",
     }
     print(json.dumps(line))
 
 
 # ------------------------------------------------------------------ GPU arm
 
+GROUPS = [["attn_q", "attn_k", "attn_v"], ["attn_output"], ["ffn_gate", "ffn_up"], ["ffn_down"]]
+
+
+class Stack:
+    """The quantized linears of a workload resident on one GPU: every layer in buffers of its own,
+    so a pass streams from HBM. gen = "oracle": seeded N(0, 0.02) weights through the CPU
+    quantizer (host copies kept for the parity check); "random": valid random blocks made on the
+    GPU (timing input for the secondary configurations)."""
+
+    def __init__(self, wl, dev, gen="oracle", head=True, ctx=None):
+        import torch
+        from tur_b200 import GgmlDType, QMatMul, QTensor
+        from tur_b200.workloads import random_blocks
+        self.wl, self.dev, self.host_blocks = wl, dev, {}
+        protos = []
+        for i, w in enumerate(wl.per_layer):
+            if gen == "oracle":
+                hb = gen_weight_blocks(w, SEED + i)
+                self.host_blocks[w.name] = hb
+                protos.append((w, torch.from_numpy(hb).to(dev)))
+            else:
+                protos.append((w, random_blocks(w.dtype, w.n, w.k, SEED + i, dev)))
+        self.layers = [[(w, QMatMul.from_arc(QTensor.new(b, GgmlDType(w.dtype), (w.n, w.k), ctx=ctx))) for w, b in protos]
+                       for _ in range(wl.layers)]
+        self.head = None
+        if wl.head is not None and head:
+            if gen == "oracle":
+                hb = gen_weight_blocks(wl.head, SEED + 999)
+                self.host_blocks[wl.head.name] = hb
+                b = torch.from_numpy(hb).to(dev)
+            else:
+                b = random_blocks(wl.head.dtype, wl.head.n, wl.head.k, SEED + 999, dev)
+            self.head = (wl.head, QMatMul.from_arc(QTensor.new(b, GgmlDType(wl.head.dtype), (wl.head.n, wl.head.k), ctx=ctx)))
+        del protos
+        torch.cuda.synchronize()
+
+    def weights(self):
+        return list(self.wl.per_layer) + ([self.wl.head] if self.head else [])
+
+    def pass_bytes(self):
+        return self.wl.layers * self.wl.layer_bytes() + (self.wl.head.nbytes if self.head else 0)
+
+    def pass_flops(self, m):
+        return m * (self.wl.layers * sum(2 * w.n * w.k for w in self.wl.per_layer)
+                    + (2 * self.wl.head.n * self.wl.head.k if self.head else 0))
+
+    def buffers(self, m, xdtype="f32", host=False):
+        """Seeded activations per source and output buffers per weight: device tensors, or
+        page-locked host tensors for the end-to-end arm."""
+        import torch
+        srcs = sorted({(w.source, w.k) for w in self.wl.per_layer})
+        xs = {s: torch.from_numpy(gen_activations(m, k, SEED + 10**6 + m + j)) for j, (s, k) in enumerate(srcs)}
+        if host:
+            x = {s: t.pin_memory() for s, t in xs.items()}
+            y = {w.name: torch.empty((m, w.n), dtype=torch.float32).pin_memory() for w in self.weights()}
+        else:
+            x = {s: (t.to(self.dev).to(torch.bfloat16) if xdtype == "bf16" else t.to(self.dev)) for s, t in xs.items()}
+            y = {w.name: torch.empty((m, w.n), dtype=torch.float32, device=self.dev) for w in self.weights()}
+        return x, y
+
+    def make_pass(self, x, y, mode, multi=True):
+        """One pass over every linear of the stack, issued as a caller integrating the library
+        would: linears that read the same x (attn_q|k|v, ffn_gate|up) as one multi-weight call."""
+        from tur_b200 import QMatMul
+
+        def run():
+            for layer in self.layers:
+                by_name = {w.name: (w, mm) for w, mm in layer}
+                for grp in GROUPS:
+                    members = [by_name[n] for n in grp if n in by_name]
+                    if len(members) > 1 and multi:
+                        QMatMul.forward_multi([mm for _, mm in members], x[members[0][0].source], mode=mode,
+                                              outs=[y[w.name] for w, _ in members])
+                    else:
+                        for w, mm in members:
+                            mm.forward(x[w.source], mode=mode, out=y[w.name])
+            if self.head:
+                self.head[1].forward(x["hidden"], mode=mode, out=y[self.head[0].name])
+        return run
+
+
+def graph_of(fn, dev, ctx, warm=3):
+    """Warm-up runs (they also size the context's scratch), then the pass captured as one CUDA
+    graph. Returns (graph, launches per pass)."""
+    import torch
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    l0 = ctx.launch_count()
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            fn()
+    launches = ctx.launch_count() - l0
+    for _ in range(warm):
+        g.replay()
+    torch.cuda.synchronize()
+    return g, launches
+
+
+def time_replays(g, steps):
+    import torch
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def sampled_rows(n, count, rng):
+    rows = {r for r in (0, 15, 16, n // 2, n - 17, n - 16, n - 1) if 0 <= r < n}
+    while len(rows) < min(count, n):
+        rows.add(int(rng.integers(0, n)))
+    return np.array(sorted(rows))
+
+
+def parity_of_pass(stack, x, y, mode_name, m):
+    """Compares what the timed pass left in its output buffers (the last layer's results; every
+    layer holds the same weights and reads the same x, so they are layer 0's too) with the CPU
+    oracle of the same scheme on a sample of weight rows. Outside every timed region."""
+    import oracle
+    import torch
+    from tur_b200 import Mode
+    rng = np.random.default_rng(SEED + 7)
+    worst, checked, cross = 0.0, [], 0.0
+    if mode_name == "EXACT_F32":
+        mode_name = "F64"
+    for w in stack.weights():
+        if w.name not in stack.host_blocks:
+            continue
+        rows = sampled_rows(w.n, 128, rng)
+        wb = stack.host_blocks[w.name][rows]
+        xh = x[w.source].float().cpu().numpy()
+        got = y[w.name][:, torch.from_numpy(rows).to(stack.dev)].cpu().numpy()
+        want = oracle.qmatmul(w.dtype, wb, len(rows), w.k, xh) if mode_name == "INT8_ACT" else oracle.matmul_f64(w.dtype, wb, len(rows), w.k, xh)
+        err = oracle.rel_fro(got, want)
+        worst = max(worst, err)
+        checked.append(f"{w.name} {TYPE_NAMES[w.dtype]} {w.n}x{w.k}")
+    # cross-scheme distance on layer 0 (what AUTO's switch between 16 and 17 rows would change)
+    for w, mm in stack.layers[0]:
+        if w.k % 64:
+            continue
+        a = mm.forward(x[w.source], mode=Mode.INT8_ACT)
+        b = mm.forward(x[w.source], mode=Mode.TENSOR_CORE)
+        cross = max(cross, oracle.rel_fro(a.cpu().numpy(), b.cpu().numpy()))
+    return {"rel_fro_max": worst, "tolerance": 2e-3, "oracle": "cpu scheme (oracle.qmatmul)" if mode_name == "INT8_ACT" else "f64 dequantize-then-matmul",
+            "rows_sampled_per_weight": 128, "checked": checked, "int8_vs_f16_scheme_rel_fro_max": cross}
+
+
 def run_gpu(args):
     import torch
     import torch.distributed as dist
-    from tur_b200 import GgmlDType, Mode, QMatMul, QTensor, context, new_context
+    from tur_b200 import Mode, QMatMul, context
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -197,108 +374,19 @@ def run_gpu(args):
     m = args.m
     mode = Mode[args.mode]
     ctx = context(local)
+    peak, peak_kind = measured_peaks()
+    tpeak, tkind = measured_tensor_peak()
 
-    # Independent projections of a layer (q|k|v read the same x, so do gate|up) are issued on
-    # parallel streams, as a caller integrating the library can: each lane has its own context
-    # (scratch + hand-over workspace), so overlapping kernels never share state.
-    lanes = {"attn_q": 0, "attn_k": 0, "attn_v": 1, "attn_output": 0, "ffn_gate": 0, "ffn_up": 0, "ffn_down": 0, "output": 0}
-    n_lanes = 2 if args.parallel else 1
-    ctxs = [ctx] + [new_context(local) for _ in range(n_lanes - 1)]
-    # ---- weights: every layer gets its own device buffers so a pass streams from HBM
-    protos = []
-    for i, w in enumerate(wl.per_layer):
-        protos.append((w, torch.from_numpy(gen_weight_blocks(w, SEED + i)).to(dev)))
-    layers = []
-    for _ in range(wl.layers):
-        layers.append([(w, QMatMul.from_arc(QTensor.new(b, GgmlDType(w.dtype), (w.n, w.k), ctx=ctxs[lanes[w.name] % n_lanes])))
-                       for w, b in protos])
-    head = None
-    if wl.head is not None and not args.no_head:
-        hb = torch.from_numpy(gen_weight_blocks(wl.head, SEED + 999)).to(dev)
-        head = (wl.head, QMatMul.from_arc(QTensor.new(hb, GgmlDType(wl.head.dtype), (wl.head.n, wl.head.k))))
-        del hb
-    del protos
-    torch.cuda.synchronize()
-
-    srcs = sorted({(w.source, w.k) for w in wl.per_layer})
-    x_host = {s: torch.from_numpy(gen_activations(m, k, SEED + 10**6 + m + j)).pin_memory() for j, (s, k) in enumerate(srcs)}
-    x_dev = {s: (t.to(dev).to(torch.bfloat16) if args.xdtype == "bf16" else t.to(dev)) for s, t in x_host.items()}
-    all_w = list(wl.per_layer) + ([wl.head] if head else [])
-    y_dev = {w.name: torch.empty((m, w.n), dtype=torch.float32, device=dev) for w in all_w}
-    y_host = {w.name: torch.empty((m, w.n), dtype=torch.float32).pin_memory() for w in all_w}
-
-    side_streams = [torch.cuda.Stream(dev) for _ in range(n_lanes - 1)]
-    groups = [["attn_q", "attn_k", "attn_v"], ["attn_output"], ["ffn_gate", "ffn_up"], ["ffn_down"]]
-
-    def run_group(members):
-        """Members that read the same x go out as one multi-weight call: a single launch per weight
-        type, and a single launch altogether for Q4_K / Q5_K beside Q6_K at decode batch sizes."""
-        if len(members) > 1 and not args.no_multi:
-            QMatMul.forward_multi([mm for _, mm in members], x_dev[members[0][0].source], mode=mode,
-                                  outs=[y_dev[w.name] for w, _ in members])
-        else:
-            for w, mm in members:
-                mm.forward(x_dev[w.source], mode=mode, out=y_dev[w.name])
-
-    def one_pass_device():
-        main = torch.cuda.current_stream()
-        for layer in layers:
-            by_name = {w.name: (w, mm) for w, mm in layer}
-            for grp in groups:
-                members = [by_name[n] for n in grp if n in by_name]
-                # split the group by lane: lane 0 on the main stream, the others in parallel
-                by_lane = {}
-                for w, mm in members:
-                    by_lane.setdefault(lanes[w.name] % n_lanes if not args.no_multi else lanes[w.name] % n_lanes, []).append((w, mm))
-                if len(by_lane) > 1:
-                    fork = torch.cuda.Event()
-                    fork.record(main)
-                    joins = []
-                    for lane, mem in by_lane.items():
-                        if lane == 0:
-                            run_group(mem)
-                        else:
-                            st = side_streams[lane - 1]
-                            st.wait_event(fork)
-                            with torch.cuda.stream(st):
-                                run_group(mem)
-                                j = torch.cuda.Event()
-                                j.record(st)
-                                joins.append(j)
-                    for j in joins:
-                        main.wait_event(j)
-                else:
-                    run_group(members)
-        if head:
-            head[1].forward(x_dev["hidden"], mode=mode, out=y_dev["output"])
-
-    def one_pass_host():
-        for layer in layers:
-            for w, mm in layer:
-                mm.forward(x_host[w.source], mode=mode, out=y_host[w.name])
-        if head:
-            head[1].forward(x_host["hidden"], mode=mode, out=y_host["output"])
+    stack = Stack(wl, dev, gen="oracle", head=not args.no_head)
+    x_dev, y_dev = stack.buffers(m, args.xdtype)
+    one_pass_device = stack.make_pass(x_dev, y_dev, mode, multi=not args.no_multi)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- warm-up (also sizes the scratch buffers before graph capture)
-    for _ in range(max(3, args.warmup)):
-        one_pass_device()
-    torch.cuda.synchronize()
-    l0 = sum(c.launch_count() for c in ctxs)
-    graph = torch.cuda.CUDAGraph()
-    side = torch.cuda.Stream(dev)
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-        with torch.cuda.graph(graph, stream=side):
-            one_pass_device()
-    launches_per_step = sum(c.launch_count() for c in ctxs) - l0
-    for _ in range(max(3, args.warmup)):
-        graph.replay()
-
+    graph, launches_per_step = graph_of(one_pass_device, dev, ctx, warm=max(3, args.warmup))
     sampler = ClockSampler(local)
     # ---- timed region: K graph replays, device timed
     barrier()
@@ -311,11 +399,17 @@ def run_gpu(args):
         torch.cuda.synchronize()
     barrier()
     ms = e0.elapsed_time(e1)
+    tensor_path = mode == Mode.TENSOR_CORE or (mode == Mode.AUTO and m > 16)
+    parity = parity_of_pass(stack, x_dev, y_dev, "TENSOR_CORE" if tensor_path else ("INT8_ACT" if mode != Mode.EXACT_F32 else "EXACT_F32"), m) \
+        if rank == 0 and not args.no_parity else None
 
-    # ---- end to end through the host-buffer entry (H2D x, kernels, D2H y, per linear)
+    # ---- end to end through the host-buffer entries: page-locked host x in, page-locked host y
+    # out, one call per group of linears that share x, a synchronize inside every call
     e2e_ms = None
     e2e_steps = max(1, min(args.steps, args.e2e_steps))
     if not args.no_e2e:
+        x_host, y_host = stack.buffers(m, host=True)
+        one_pass_host = stack.make_pass(x_host, y_host, mode, multi=not args.no_multi)
         for _ in range(3):
             one_pass_host()
         barrier()
@@ -329,34 +423,37 @@ def run_gpu(args):
             wall = (time.perf_counter() - t0) * 1e3
         barrier()
         e2e_ms = max(e0.elapsed_time(e1), wall)
+        if rank == 0 and parity is not None and not tensor_path:
+            # the host route must give what the device route gave
+            parity["e2e_equals_device_route"] = all(torch.equal(y_host[w.name], y_dev[w.name].cpu()) for w in stack.weights())
 
     # ---- dominant launch, timed alone over the layers' distinct buffers: the group of linears
     # sharing one x that moves the most bytes (ffn_gate|up in the decoder stacks), issued exactly
     # as the pass issues it (one multi-weight launch unless --no-multi)
-    dom_names = max(groups, key=lambda g: sum(w.nbytes for w in wl.per_layer if w.name in g))
+    dom_names = max(GROUPS, key=lambda g: sum(w.nbytes for w in wl.per_layer if w.name in g))
     dom_ws = [w for w in wl.per_layer if w.name in dom_names]
     dom = dom_ws[0]
-    dg = torch.cuda.CUDAGraph()
-    l0 = sum(c.launch_count() for c in ctxs)
-    with torch.cuda.stream(side):
-        with torch.cuda.graph(dg, stream=side):
-            for layer in layers:
-                run_group([(w, mm) for w, mm in layer if w.name in dom_names])
-    dom_launches = (sum(c.launch_count() for c in ctxs) - l0) / len(layers)
-    for _ in range(3):
-        dg.replay()
-    torch.cuda.synchronize()
-    reps = 20
-    e0.record()
-    for _ in range(reps):
-        dg.replay()
-    e1.record()
-    torch.cuda.synchronize()
+
+    def dom_pass():
+        for layer in stack.layers:
+            members = [(w, mm) for w, mm in layer if w.name in dom_names]
+            if len(members) > 1 and not args.no_multi:
+                QMatMul.forward_multi([mm for _, mm in members], x_dev[dom.source], mode=mode, outs=[y_dev[w.name] for w, _ in members])
+            else:
+                for w, mm in members:
+                    mm.forward(x_dev[w.source], mode=mode, out=y_dev[w.name])
+
+    dg, dl = graph_of(dom_pass, dev, ctx)
+    dom_launches = dl / len(stack.layers)
     # per group: the GEMV launch plus, where the activations are not quantized in the kernel,
     # their quantization launch; timed together. x is read once for the whole group.
-    dom_us = e0.elapsed_time(e1) * 1e3 / (reps * len(layers))
+    dom_us = time_replays(dg, 20) * 1e3 / len(stack.layers)
     x_es = 2 if args.xdtype == "bf16" else 4
     alg_bytes = sum(w.nbytes + m * w.n * 4 for w in dom_ws) + m * dom.k * x_es
+
+    extras = {}
+    if rank == 0 and args.workload == "cfg2" and m == 1 and not args.no_extras:
+        extras = run_extras(stack, dev, ctx, peak, tpeak, local)
 
     # ---- reduce over ranks
     if world > 1:
@@ -368,24 +465,20 @@ def run_gpu(args):
             dist.destroy_process_group()
         return
 
-    head_w = wl.head if head else None
-    pass_bytes = wl.layers * wl.layer_bytes() + (head_w.nbytes if head_w else 0)
-    pass_flops = m * (wl.layers * sum(2 * w.n * w.k for w in wl.per_layer) + (2 * head_w.n * head_w.k if head_w else 0))
+    pass_bytes = stack.pass_bytes()
+    pass_flops = stack.pass_flops(m)
     total_bytes = pass_bytes * world
     value = total_bytes * args.steps / (ms * 1e-3) / 1e9
-    peak, peak_kind = measured_peaks()
     achieved = alg_bytes / (dom_us * 1e-6) / 1e9
-    one = NCU_TRAFFIC_BYTES.get((dom.name, wl.name))
-    traffic = one * len(dom_ws) if one is not None and all((w.n, w.k, w.dtype) == (dom.n, dom.k, dom.dtype) for w in dom_ws) else None
-    h2d = sum(m * w.k * 4 for w in wl.per_layer) * wl.layers + (m * head_w.k * 4 if head_w else 0)
-    d2h = sum(m * w.n * 4 for w in wl.per_layer) * wl.layers + (m * head_w.n * 4 if head_w else 0)
+    traffic = NCU_TRAFFIC_BYTES.get((tuple(w.name for w in dom_ws), wl.name, m))
+    grp_x = [max(w.k for w in wl.per_layer if w.name in g) for g in GROUPS]
+    h2d = m * 4 * (sum(grp_x) * wl.layers + (stack.head[0].k if stack.head else 0))
+    d2h = sum(m * w.n * 4 for w in wl.per_layer) * wl.layers + (m * stack.head[0].n * 4 if stack.head else 0)
     members = " | ".join(f"{w.name} {TYPE_NAMES[w.dtype]} {w.n}x{w.k}" for w in dom_ws)
-    tensor_path = mode == Mode.TENSOR_CORE or (mode == Mode.AUTO and m > 16)
     if tensor_path and m > 64:
         # prefill runs the tcgen05 GEMM: bound by the tensor cores (decode batches of up to 64 rows
         # stay bound by the weight stream whichever path computes them)
         dom_flops = 2.0 * m * sum(w.n * w.k for w in dom_ws)
-        tpeak, tkind = measured_tensor_peak()
         tf = dom_flops / (dom_us * 1e-6) / 1e12
         roofline = {"bound": "tensor", "kernel": "gemm_tc (+ activation prep) " + members + " as issued in the pass",
                     "achieved": tf, "peak": tpeak, "peak_kind": tkind, "unit": "TFLOP/s", "frac": tf / tpeak,
@@ -397,36 +490,97 @@ def run_gpu(args):
                               "quantization included)",
                     "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
                     "us_per_launch": dom_us, "launches": dom_launches, "algorithmic_bytes": alg_bytes, "traffic": traffic,
-                    "traffic_note": "ncu capture of one member's launch scaled by the members of the group"}
+                    "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum of this launch from one ncu capture"
+                                    if traffic is not None else "no ncu capture of this launch"}
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": ("f16" if mode == Mode.TENSOR_CORE or (mode == Mode.AUTO and m > 16) else
-                  "int8" if mode in (Mode.INT8_ACT, Mode.AUTO) else "f32"), "data": "synthetic",
+        "dtype": ("f16" if tensor_path else "int8" if mode in (Mode.INT8_ACT, Mode.AUTO) else "f32"), "data": "synthetic",
         "config": {
-            "workload": f"{wl.name}: {wl.description}, decode M={m}, {wl.layers} layers x 7 linears"
-                        + (" + lm_head" if head_w else ""),
+            "workload": workload_text(wl, m, stack.head is not None),
             "mode": mode.name, "x_dtype": args.xdtype, "weight_bytes_per_step_per_gpu": pass_bytes,
             "tflops": pass_flops * world * args.steps / (ms * 1e-3) / 1e12, "parallelism": f"replicas x{world}",
             "l2": "weights per pass exceed L2 (distinct buffers per layer); CUDA-graph replay per step",
-            "streams": "one" if n_lanes == 1 else "attn_v beside attn_q|k on a second stream (own context)",
             "multi_weight_launch": not args.no_multi,
             "tokens_per_s": m * world * args.steps / (ms * 1e-3),
         },
         "e2e": None if e2e_ms is None else {
             "value": total_bytes * e2e_steps / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "steps": e2e_steps,
             "ms_per_step": e2e_ms / e2e_steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-            "api": "turq_qmatmul_host per linear (pinned host x and y)"},
+            "api": "turq_qmatmul_multi_host / turq_qmatmul_host per group of linears sharing x: page-locked host x in, "
+                   "page-locked host y out, one synchronize per call; the activation rows cross the bus once per "
+                   "call (read in place by the quantization launch), every output once (written in place by the GEMV)"},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": sampler.summary(),
         "roofline": roofline,
     }
+    if parity is not None:
+        line["parity"] = parity
+    line.update(extras)
     if not args.no_cpu and world == 1:
-        gbs, cores, sample, _, _ = cpu_scheme_timing(wl, m, budget_s=args.cpu_budget)
+        gbs, cores, sample, _, _ = cpu_scheme_timing(wl, m, steps=args.cpu_steps)
         line["cpu_baseline"] = {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_extras(stack, dev, ctx, peak, tpeak, local):
+    """The other contract points of the benchmark configurations, measured in the same run with
+    the weights already resident: the decode sweep M = 2..16, a prefill pass on the tensor cores,
+    and the small / 3B stacks at M = 1. Each is a CUDA-graph replay timed with CUDA events."""
+    import torch
+    from tur_b200 import Mode
+    out = {}
+    wl = stack.wl
+    sweep = []
+    for mm_rows in (2, 4, 8, 16):
+        x, y = stack.buffers(mm_rows)
+        g, _ = graph_of(stack.make_pass(x, y, Mode.INT8_ACT), dev, ctx)
+        t = time_replays(g, 10)
+        gbs = stack.pass_bytes() / (t * 1e-3) / 1e9
+        sweep.append({"rows": mm_rows, "ms_per_step": t, "weight_gbs": gbs, "frac_of_hbm_peak": gbs / peak,
+                      "tokens_per_s": mm_rows / (t * 1e-3)})
+        del g, x, y
+    out["sweep"] = {"workload": f"{wl.name} decode, integer scheme, rows per pass 2..16 (same weights as the headline)", "points": sweep}
+    # prefill: the same layers, no head (prefill evaluates it for one token), bf16 activations
+    head, stack.head = stack.head, None
+    try:
+        pre = []
+        for rows in (512, 2048):
+            x, y = stack.buffers(rows, "bf16")
+            sampler = ClockSampler(local)
+            g, _ = graph_of(stack.make_pass(x, y, Mode.TENSOR_CORE), dev, ctx, warm=2)
+            with sampler:
+                t = time_replays(g, 5)
+            tf = stack.pass_flops(rows) / (t * 1e-3) / 1e12
+            sustained = None
+            try:
+                with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                    sustained = float(json.load(f)["bf16_tflops_sustained"])
+            except Exception:
+                pass
+            pre.append({"rows": rows, "ms_per_step": t, "tflops": tf, "frac_of_burst_peak": tf / tpeak,
+                        "frac_of_sustained_peak": (tf / sustained) if sustained else None, "clocks": sampler.summary()})
+            del g, x, y
+        out["prefill"] = {"workload": f"{wl.name} prefill, 36 layers x 7 linears, bf16 activations, tcgen05 f16 GEMM, no lm_head",
+                          "points": pre}
+    finally:
+        stack.head = head
+    torch.cuda.empty_cache()
+    cfgs = []
+    for name in ("cfg1", "cfg4-q5", "cfg4-q8"):
+        st = Stack(WORKLOADS[name], dev, gen="random", head=False)
+        x, y = st.buffers(1)
+        g, launches = graph_of(st.make_pass(x, y, Mode.INT8_ACT), dev, ctx)
+        t = time_replays(g, 10)
+        gbs = st.pass_bytes() / (t * 1e-3) / 1e9
+        cfgs.append({"workload": workload_text(st.wl, 1, False), "weights": "valid random blocks generated on the GPU",
+                     "ms_per_step": t, "weight_gbs": gbs, "frac_of_hbm_peak": gbs / peak, "launches": launches})
+        del g, x, y, st
+        torch.cuda.empty_cache()
+    out["configs"] = cfgs
+    return out
 
 
 def run_gpu_tp(args):
@@ -451,7 +605,7 @@ def run_gpu_tp(args):
     ctx = context(local)
     head_dim = 128
 
-    from tur_b200.kernel_bench import random_blocks
+    from tur_b200.workloads import random_blocks
 
     def make(w, seed):
         # random valid blocks generated on the GPU (same on every rank), sharded as bytes:
@@ -512,9 +666,8 @@ def run_gpu_tp(args):
     l0 = ctx.launch_count()
     runner, graphed = one_pass, False
     try:
-        # With more than one rank the pass is launched eagerly: a captured graph containing the
-        # NCCL collectives did not finish its first replays at 2 ranks (ended by `timeout`,
-        # twice, GPUs answered afterwards); the cause was not found by reading.
+        # NCCL collectives are never captured into the graph: beyond one rank the pass is
+        # launched eagerly
         if args.no_graph or world > 1:
             raise RuntimeError("graph capture disabled")
         graph = torch.cuda.CUDAGraph()
@@ -587,10 +740,11 @@ def main():
     ap.add_argument("--rows", dest="m", type=int, default=1, help="activation rows per linear (decode batch M)")
     ap.add_argument("--mode", default="INT8_ACT", choices=["AUTO", "INT8_ACT", "EXACT_F32", "TENSOR_CORE"])
     ap.add_argument("--e2e-steps", type=int, default=20)
-    ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU-baseline timing")
+    ap.add_argument("--cpu-steps", type=int, default=20, help="steps of about half a second each in the cpu_baseline leg")
     ap.add_argument("--tp", action="store_true", help="tensor-parallel over all ranks (the sharded cfg5 workload)")
     ap.add_argument("--no-multi", action="store_true", help="one launch per weight (no q|k, gate|up multi-weight launches)")
-    ap.add_argument("--parallel", action="store_true", help="issue attn_v on a second stream beside attn_q|k")
+    ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of the timed pass's outputs")
+    ap.add_argument("--no-extras", action="store_true", help="skip the sweep / prefill / other-config objects of the default run")
     ap.add_argument("--no-graph", action="store_true", help="tensor-parallel arm: launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--xdtype", default="f32", choices=["f32", "bf16"], help="activation dtype on the device (prefill configs use bf16)")
     ap.add_argument("--no-head", action="store_true", help="leave the lm_head out of the pass (prefill evaluates it for one token only)")

@@ -58,7 +58,13 @@ typedef enum {
  *               or Q8_K (K-quant weights) and block dots run in integers.
  *   EXACT_F32   weights are dequantized on the fly to their exact f32 values, f32 FMA.
  *   TENSOR_CORE tcgen05 f16 MMA with f32 accumulation (prefill-sized M).
- *   AUTO        INT8_ACT for M <= 16, TENSOR_CORE above (when in-features are a multiple of 64). */
+ *   AUTO        INT8_ACT for M <= 16, TENSOR_CORE above (when in-features are a multiple of 64).
+ *               The two schemes differ by the rounding of the activations to int8 (5-8e-3
+ *               relative), so under the default policy a row's result changes when its batch
+ *               grows from 16 to 17 rows. A host that needs a token's result to be independent
+ *               of the batch or chunk it arrives in (tur's tests/pipeline_integration.rs:275-369
+ *               do) pins one scheme for all row counts with turq_ctx_set_auto_policy or passes
+ *               an explicit mode. Within one mode results never depend on the other rows. */
 typedef enum {
   TURQ_MODE_AUTO = 0,
   TURQ_MODE_INT8_ACT = 1,
@@ -70,6 +76,11 @@ typedef struct turq_ctx turq_ctx;         /* one device + its scratch memory */
 typedef struct turq_qtensor turq_qtensor; /* immutable quantized weight on the device */
 
 int32_t turq_version(void);
+/* How this build quantizes activations to Q8_K (compile-time switches TURQ_Q8K_*): the divisor
+ * (127 or 128) | 0x100 when the scale is -divisor / (signed element of largest magnitude)
+ * | 0x200 when ties round to even. Default 0x180: candle-core's published quantizer
+ * (-128 / max, ties away from zero, clamp at 127). */
+int32_t turq_q8k_variant(void);
 const char* turq_status_string(int32_t status);
 
 /* Block geometry of the wire format (candle: GgmlDType::block_size / type_size). */
@@ -82,6 +93,16 @@ size_t turq_row_bytes(int32_t dtype, int64_t k);
 int32_t turq_ctx_create(int32_t device, turq_ctx** out);
 int32_t turq_ctx_destroy(turq_ctx* ctx);
 const char* turq_last_error(const turq_ctx* ctx);
+/* The context owns scratch memory that grows on demand: a call with more rows (or a wider weight)
+ * than any before it synchronizes the device, frees the old buffer and allocates a larger one.
+ * That is not allowed during stream capture and stalls a serving thread, so a host that knows
+ * its largest call reserves once, up front: afterwards no call with m <= max_m rows, in-features
+ * <= max_k and out-features <= max_n allocates (turq_qmatmul, _multi, _host, _multi_host). */
+int32_t turq_ctx_reserve(turq_ctx* ctx, int64_t max_m, int64_t max_k, int64_t max_n);
+/* What TURQ_MODE_AUTO means on this context: TURQ_MODE_AUTO (default) = by row count as described
+ * above; INT8_ACT, EXACT_F32 or TENSOR_CORE = that scheme for every row count (TENSOR_CORE still
+ * falls back to INT8_ACT for in-features that are not a multiple of 64). */
+int32_t turq_ctx_set_auto_policy(turq_ctx* ctx, int32_t mode);
 /* Kernels never trap: a device-side wait that runs out (mbarrier, cross-CTA hand-over) stops
  * the kernel and records a status word. This call synchronizes `stream`, returns TURQ_OK or
  * the recorded status (TURQ_E_TIMEOUT) and clears it. */
@@ -149,18 +170,28 @@ int32_t turq_qmatmul_multi(turq_ctx* ctx, int32_t count, const turq_qtensor* con
                            int32_t mode, const float* const* dev_biases, void* stream);
 
 /* The same call for a caller that keeps activations in host memory, as tur does today
- * (Device::Cpu everywhere: tests/common.rs:5): copies x to the device, runs, copies y back
- * and synchronizes. x and y are f32. */
+ * (Device::Cpu everywhere: tests/common.rs:5): x in, y out, one synchronize; x and y are f32.
+ * With page-locked buffers (cudaHostAlloc / cudaHostRegister), 16-byte aligned x, no bias, the
+ * integer scheme and at most 2 MiB per output, nothing is copied: one small launch reads x from
+ * the caller's memory and the GEMV writes y into it. Otherwise x is copied in and y copied
+ * back. Runs on the context's own stream. */
 int32_t turq_qmatmul_host(turq_ctx* ctx, const turq_qtensor* qt, const float* host_x, int64_t m,
                           float* host_y, int32_t mode, const float* host_bias);
+/* turq_qmatmul_multi with host buffers: attn_q|k|v or ffn_gate|up read one host x and cost one
+ * round trip instead of three or two. host_ys[i] is [m, rows of qts[i]]. */
+int32_t turq_qmatmul_multi_host(turq_ctx* ctx, int32_t count, const turq_qtensor* const* qts,
+                                const float* host_x, int64_t m, float* const* host_ys, int32_t mode,
+                                const float* const* host_biases);
 
 /* Integer-scheme QMatMul for hosts that must not allocate device memory during a call
  * (a process whose memory pool already owns the GPU, a plugin inside a foreign runtime).
  * No counterpart in the reference. Same arguments and results as turq_qmatmul with
  * TURQ_MODE_INT8_ACT, but the quantized activation planes live in a fixed buffer inside the
  * library image (TURQ_STATIC_SCRATCH_BYTES on every GPU that loads the library) instead of
- * the context's growable scratch: the call performs no cudaMalloc/cudaFree. Requests whose
- * planes do not fit (about m * k * 1.2 bytes) fail with TURQ_E_LIMIT. All calls on a GPU
+ * the context's growable scratch: the call performs no cudaMalloc/cudaFree. The tail of the
+ * buffer is the GEMV's hand-over workspace (about 1.2 MB on a 148-SM GPU), so the planes of one
+ * call (about m * k * 1.2 bytes) may use the remaining ~2.8 MiB; larger requests fail with
+ * TURQ_E_LIMIT and the message gives both figures. All calls on a GPU
  * share that buffer, so calls that can overlap on the GPU (different streams) race and must
  * be ordered by the caller. The first call on each device looks up the buffer's device
  * address; make that call before starting any stream capture. */

@@ -44,9 +44,16 @@ def lib_path() -> str:
     return os.path.join(_HERE, f"libturq_oracle.{_cpu_tag()}.so")
 
 
-def build(force: bool = False) -> str:
-    """Compile turq_oracle.c for this host; returns the path of the shared library."""
+def build(force: bool = False, defines: dict | None = None) -> str:
+    """Compile turq_oracle.c for this host; returns the path of the shared library.
+    `defines` (e.g. {"TQO_Q8K_DIVISOR": 127}) builds a variant of the Q8_K activation quantizer
+    into a file of its own, named after the switches."""
     out = lib_path()
+    dflags = []
+    if defines:
+        tag = "_".join(f"{k}{v}" for k, v in sorted(defines.items()))
+        out = out[:-3] + "." + tag + ".so"
+        dflags = [f"-D{k}={v}" for k, v in sorted(defines.items())]
     src = os.path.join(_HERE, "turq_oracle.c")
     hdr = os.path.join(_HERE, "turq_oracle.h")
     stale = (not os.path.exists(out)
@@ -56,7 +63,7 @@ def build(force: bool = False) -> str:
         # into place atomically, so nobody ever loads a half-written library
         tmp = f"{out}.{os.getpid()}.tmp"
         cmd = ["gcc", "-O3", "-march=native", "-fopenmp", "-fPIC", "-ffp-contract=off",
-               "-fno-fast-math", "-std=c11", "-shared", "-o", tmp, src, "-lm"]
+               "-fno-fast-math", "-std=c11", *dflags, "-shared", "-o", tmp, src, "-lm"]
         try:
             subprocess.run(cmd, check=True, cwd=_HERE)
             os.replace(tmp, out)
@@ -66,11 +73,8 @@ def build(force: bool = False) -> str:
     return out
 
 
-def _load():
-    global _lib
-    if _lib is not None:
-        return _lib
-    lib = ctypes.CDLL(build())
+def _bind(path: str):
+    lib = ctypes.CDLL(path)
     i64, vp, ci = ctypes.c_int64, ctypes.c_void_p, ctypes.c_int
     lib.tqo_block_elems.argtypes = [ci]
     lib.tqo_block_bytes.argtypes = [ci]
@@ -87,8 +91,32 @@ def _load():
     lib.tqo_f16_to_f32.argtypes = [ctypes.c_uint16]
     lib.tqo_f16_to_f32.restype = ctypes.c_float
     lib.tqo_num_threads.restype = ci
-    _lib = lib
+    lib.tqo_q8k_variant.restype = ci
     return lib
+
+
+def _load():
+    global _lib
+    if _lib is None:
+        _lib = _bind(build())
+    return _lib
+
+
+def q8k_variant() -> int:
+    """Q8_K quantizer switches this oracle was built with: divisor | 0x100 (negative-scale
+    convention) | 0x200 (ties to even). The CUDA library reports the same word."""
+    return _load().tqo_q8k_variant()
+
+
+def quantize_q8k_variant(x: np.ndarray, **defines) -> np.ndarray:
+    """Q8_K blocks of x [nrows, k] from an oracle built with other TQO_Q8K_* switches."""
+    lib = _bind(build(defines=defines))
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    nrows, k = x.shape
+    out = np.empty((nrows, (k // 256) * 292), dtype=np.uint8)
+    if lib.tqo_quantize(Q8_K, _ptr(x), _ptr(out), nrows, k) != 0:
+        raise ValueError("tqo_quantize failed")
+    return out
 
 
 def _ptr(a: np.ndarray):

@@ -13,7 +13,8 @@
  *
  * Pinned bit-exact against that package: dequantize of all four weight types and the
  * Q8_0 quantizer. PARITY UNPINNED against candle itself: the Q8_K activation quantizer
- * (GGML reference semantics chosen: iscale = -128/max, round-half-even, clamp to 127),
+ * (candle-core's published quantizer restated: iscale = -128/max, ties away from zero, clamp
+ * to 127; divisor, scale sign and rounding are the compile-time switches TQO_Q8K_*),
  * the K-quant weight quantizers (own deterministic min/max + least-squares search; they
  * only have to emit valid blocks) and the f32 summation order of the block dots.
  */
@@ -316,9 +317,31 @@ static void quant_row_q8_0(const float* x, uint8_t* b, int64_t k) {
   }
 }
 
-/* Q8_K activation blocks: f32 d, 256 int8, 16 int16 group sums. GGML reference semantics:
- * the element of largest magnitude maps to -128 (then clamps to 127 when positive),
- * rounding is to-nearest-even, d = 1/iscale. UNPINNED against candle 0.10.2. */
+/* Q8_K activation blocks: f32 d, 256 int8, 16 int16 group sums.
+ * Three choices differ between GGML revisions and candle; they are compile-time switches
+ * (the CUDA library has the same three under the TURQ_ prefix and must be built alike):
+ *   TQO_Q8K_DIVISOR          128 (default) | 127   magnitude the block maximum maps to
+ *   TQO_Q8K_NEG_SCALE        1 (default): iscale = -DIVISOR / (signed element of largest
+ *                            magnitude, first on ties); 0: iscale = DIVISOR / amax
+ *   TQO_Q8K_ROUND_HALF_EVEN  0 (default): ties away from zero, which is what Rust's
+ *                            f32::round does and candle-core's BlockQ8K::from_float applies;
+ *                            1: ties to even (GGML's nearest_int)
+ * The result is clamped at 127 and d = 1/iscale. The defaults restate candle-core's published
+ * quantizer; UNPINNED against candle 0.10.2 itself (its source is not in the reference tree). */
+#ifndef TQO_Q8K_DIVISOR
+#define TQO_Q8K_DIVISOR 128
+#endif
+#ifndef TQO_Q8K_NEG_SCALE
+#define TQO_Q8K_NEG_SCALE 1
+#endif
+#ifndef TQO_Q8K_ROUND_HALF_EVEN
+#define TQO_Q8K_ROUND_HALF_EVEN 0
+#endif
+
+int tqo_q8k_variant(void) {
+  return TQO_Q8K_DIVISOR | (TQO_Q8K_NEG_SCALE ? 0x100 : 0) | (TQO_Q8K_ROUND_HALF_EVEN ? 0x200 : 0);
+}
+
 static void quant_row_q8k(const float* x, uint8_t* b, int64_t k) {
   for (int64_t ib = 0; ib < k / QK_K; ib++, b += 292, x += QK_K) {
     float amax = 0.f, mx = 0.f;
@@ -335,10 +358,18 @@ static void quant_row_q8k(const float* x, uint8_t* b, int64_t k) {
       memset(b, 0, 292);
       continue;
     }
-    float iscale = -128.f / mx;
+#if TQO_Q8K_NEG_SCALE
+    float iscale = -(float)TQO_Q8K_DIVISOR / mx;
+#else
+    float iscale = (float)TQO_Q8K_DIVISOR / amax;
+#endif
     for (int i = 0; i < QK_K; i++) {
       float v = iscale * x[i];
+#if TQO_Q8K_ROUND_HALF_EVEN
       long r = lrintf(v); /* default rounding mode: ties to even */
+#else
+      long r = (long)roundf(v); /* ties away from zero */
+#endif
       qs[i] = (int8_t)(r > 127 ? 127 : r);
     }
     for (int j = 0; j < 16; j++) {

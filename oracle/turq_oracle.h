@@ -12,8 +12,9 @@
  *   - dequantize Q8_0/Q4_K/Q5_K/Q6_K and quantize Q8_0: pinned bit-exact against the
  *     independent numpy codec of the `gguf` 0.19.0 package (golden vectors in tests/golden).
  *   - Q8_K activation quantizer, K-quant weight quantizers, vec_dot summation order:
- *     PARITY UNPINNED against candle 0.10.2 (no source, no toolchain); they follow the
- *     GGML reference semantics (Q8_K: iscale = -128/max, round-half-even, clamp 127).
+ *     PARITY UNPINNED against candle 0.10.2 (no source, no toolchain). The Q8_K quantizer
+ *     restates candle-core's published one (iscale = -128/max, ties away from zero, clamp
+ *     127); divisor, scale sign and rounding are compile-time switches (TQO_Q8K_*).
  *
  * Only tests, the smoke check and the benchmark's CPU-baseline leg may link or call this.
  */
@@ -70,6 +71,8 @@ int tqo_matmul_f64(int dtype, const void* w, int64_t n, int64_t k, const float* 
                    float* y, int nthreads);
 
 int tqo_num_threads(void);
+/* Q8_K quantizer build switches: divisor | 0x100 (negative-scale convention) | 0x200 (ties to even) */
+int tqo_q8k_variant(void);
 
 #ifdef __cplusplus
 }

@@ -109,6 +109,9 @@ def main() -> None:
     xa[2, :256] = 0.0
     xa[3, 7] = -xa[3].max() * 2            # largest magnitude negative
     xa[4, 9] = np.abs(xa[4]).max() * 2     # largest magnitude positive -> clamps at 127
+    # exact .5 ties after scaling: block maximum +1.0 gives iscale = -128 and -(2j+1)/2 products
+    xa[0, :255] = ((2 * np.arange(255) + 1) % 255 + 0.0).astype(np.float32) / np.float32(256.0) * np.where(np.arange(255) % 3 == 0, -1, 1)
+    xa[0, 255] = 1.0
     frozen["act_x"] = xa
     frozen["act_q8k"] = oracle.quantize(oracle.Q8_K, xa)
     frozen["act_q8_0"] = oracle.quantize(oracle.Q8_0, xa)

@@ -415,3 +415,142 @@ def test_error_paths_return_status_not_crash(tq):
     with pytest.raises(tq.TurqError) as e:
         qt.slice_cols(0, 100)
     assert e.value.status == 2
+
+
+def test_q8k_ties_round_as_the_oracle_does_and_the_build_switches_agree(tq):
+    """Exact .5 ties after scaling (common for bf16 and low-mantissa inputs): the library and the
+    oracle must have been built with the same Q8_K switches and then agree bit for bit."""
+    from tur_b200 import _lib
+    assert _lib.load().turq_q8k_variant() == oracle.q8k_variant()
+    k = 512
+    j = np.arange(255)
+    x = np.zeros((4, k), np.float32)
+    x[0, :255] = ((2 * j + 1) % 255) / np.float32(256.0) * np.where(j % 3 == 0, -1, 1)
+    x[0, 255] = 1.0
+    x[1, :255] = -x[0, :255]
+    x[1, 255] = -1.0
+    x[2, 256:511] = (j + 0.5) / np.float32(128.0) * np.where(j % 2 == 0, -1, 1)
+    x[2, 511] = -2.0
+    x[3] = np.round(np.random.default_rng(SEED).standard_normal(k) * 8) / 16     # low-mantissa values
+    xd = torch.from_numpy(x).cuda()
+    assert np.array_equal(tq.quantize_act(xd, tq.GgmlDType.Q8K).cpu().numpy(), oracle.quantize(oracle.Q8_K, x))
+    xb = xd.to(torch.bfloat16)
+    assert np.array_equal(tq.quantize_act(xb, tq.GgmlDType.Q8K).cpu().numpy(),
+                          oracle.quantize(oracle.Q8_K, xb.float().cpu().numpy()))
+    # the GEMV's own quantization (in-kernel for one row, staged planes for more) follows suit
+    for dt in (oracle.Q4_K, oracle.Q6_K):
+        w = make_weight(dt, 64, k, SEED + 41)
+        mm = tq.QMatMul.from_arc(tq.QTensor.new(w, tq.GgmlDType(dt), (64, k)))
+        for rows in (slice(0, 1), slice(0, 4)):
+            y = mm.forward(xd[rows], mode=tq.Mode.INT8_ACT).cpu().numpy()
+            assert oracle.rel_fro(y, oracle.qmatmul(dt, w, 64, k, x[rows])) < 1e-6
+
+
+def test_operands_are_validated_before_any_launch(tq):
+    """A tensor on another device, of another element type or with strides would make a kernel
+    read memory it must not: the host layer refuses it with a status instead."""
+    w = make_weight(oracle.Q4_K, 32, 256, 3)
+    mm = tq.QMatMul(tq.QTensor.new(w, tq.GgmlDType.Q4K, (32, 256)))
+    x = torch.zeros(2, 256, device="cuda")
+    with pytest.raises(tq.TurqError) as e:
+        mm.forward(x, bias=torch.zeros(32, device="cuda", dtype=torch.float16))
+    assert e.value.status == 3
+    with pytest.raises(tq.TurqError) as e:
+        mm.forward(x, bias=torch.zeros(32))                                   # bias on the host
+    assert e.value.status == 1
+    with pytest.raises(tq.TurqError) as e:
+        mm.forward(x, bias=torch.zeros(31, device="cuda"))
+    assert e.value.status == 2
+    with pytest.raises(tq.TurqError) as e:
+        mm.forward(x, out=torch.zeros(2, 64, device="cuda")[:, ::2])          # strided output
+    assert e.value.status == 1
+    with pytest.raises(tq.TurqError) as e:
+        mm.forward(x, out=torch.zeros(2, 32, device="cuda", dtype=torch.bfloat16))
+    assert e.value.status == 3
+    with pytest.raises(tq.TurqError) as e:
+        mm.forward(x, out=torch.zeros(2, 32))                                 # output on the host
+    assert e.value.status == 1
+    with pytest.raises(tq.TurqError) as e:
+        tq.QMatMul.forward_multi([mm, mm], x, outs=[torch.zeros(2, 32, device="cuda"), torch.zeros(2, 16, device="cuda")])
+    assert e.value.status == 2
+    with pytest.raises(tq.TurqError) as e:
+        mm.forward(torch.zeros(2, 256), out=torch.zeros(2, 32, device="cuda"))  # host x, device out
+    assert e.value.status == 1
+    assert torch.equal(mm.forward(x), torch.zeros(2, 32, device="cuda"))      # and the context still works
+
+
+@pytest.mark.parametrize("dt", TYPES, ids=ids)
+@pytest.mark.parametrize("pinned", [True, False], ids=["page_locked", "pageable"])
+def test_host_entries_for_several_weights_in_one_round_trip(tq, dt, pinned):
+    """turq_qmatmul_multi_host: q|k|v or gate|up from one host x. Page-locked buffers take the
+    copy-free route (x read and y written in place by the kernels), pageable ones are copied;
+    both must give the bits of the device-tensor call."""
+    k, shapes, m = 1024, [272, 64, 1000], 3
+    rng = np.random.default_rng(SEED + 321)
+    ws = [make_weight(dt, n, k, SEED + 800 + n) for n in shapes]
+    mms = [tq.QMatMul.from_arc(tq.QTensor.new(w, tq.GgmlDType(dt), (n, k))) for w, n in zip(ws, shapes)]
+    x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32))
+    if pinned:
+        x = x.pin_memory()
+    want = tq.QMatMul.forward_multi(mms, x.cuda(), mode=tq.Mode.INT8_ACT)
+    got = tq.QMatMul.forward_multi(mms, x, mode=tq.Mode.INT8_ACT)
+    for g, wnt, w, n in zip(got, want, ws, shapes):
+        assert not g.is_cuda and g.shape == (m, n)
+        assert torch.equal(g, wnt.cpu())
+        assert oracle.rel_fro(g.numpy(), oracle.qmatmul(dt, w, n, k, x.numpy())) < 1e-5
+    # with a bias (copied route) and through the single-weight entry
+    bias = torch.from_numpy(rng.standard_normal(shapes[1]).astype(np.float32))
+    got_b = tq.QMatMul.forward_multi(mms, x, biases=[None, bias, None], mode=tq.Mode.INT8_ACT)
+    assert torch.equal(got_b[1], want[1].cpu() + bias) and torch.equal(got_b[0], want[0].cpu())
+    assert torch.equal(mms[2].forward(x, mode=tq.Mode.INT8_ACT), want[2].cpu())
+    # repeated calls reuse the same buffers
+    for _ in range(3):
+        again = tq.QMatMul.forward_multi(mms, x, mode=tq.Mode.INT8_ACT)
+        assert all(torch.equal(a, b) for a, b in zip(again, got))
+    # other schemes go through the copied route and still agree with the device call
+    y_tc = mms[0].forward(x.repeat(8, 1), mode=tq.Mode.TENSOR_CORE)
+    assert torch.equal(y_tc, mms[0].forward(x.repeat(8, 1).cuda(), mode=tq.Mode.TENSOR_CORE).cpu())
+
+
+def test_auto_policy_pins_one_scheme_for_every_row_count_and_reserve_presizes(tq):
+    """tur requires a token's result not to depend on its batch or chunk
+    (tests/pipeline_integration.rs:275-369). AUTO switches scheme between 16 and 17 rows by
+    default; a context with a pinned policy does not."""
+    n, k = 256, 1024
+    w = make_weight(oracle.Q4_K, n, k, SEED + 61)
+    ctx = tq.new_context()
+    ctx.reserve(64, k, n)
+    mm = tq.QMatMul.from_arc(tq.QTensor.new(w, tq.GgmlDType.Q4K, (n, k), ctx=ctx))
+    x = torch.from_numpy(np.random.default_rng(SEED + 62).standard_normal((40, k)).astype(np.float32)).cuda()
+    y_auto = mm.forward(x, mode=tq.Mode.AUTO)
+    assert torch.equal(y_auto, mm.forward(x, mode=tq.Mode.TENSOR_CORE))
+    assert not torch.equal(y_auto[:8], mm.forward(x[:8], mode=tq.Mode.AUTO))        # default: scheme depends on M
+    for policy in (tq.Mode.INT8_ACT, tq.Mode.TENSOR_CORE, tq.Mode.EXACT_F32):
+        ctx.set_auto_policy(policy)
+        y40 = mm.forward(x, mode=tq.Mode.AUTO)
+        assert torch.equal(y40, mm.forward(x, mode=policy))
+        for rows in (slice(0, 1), slice(5, 13), slice(0, 17)):
+            assert torch.equal(mm.forward(x[rows], mode=tq.Mode.AUTO), y40[rows])
+    ctx.set_auto_policy(tq.Mode.AUTO)
+    assert torch.equal(mm.forward(x, mode=tq.Mode.AUTO), y_auto)
+    with pytest.raises(tq.TurqError):
+        ctx.reserve(0, k, n)
+    ctx.poll_status()
+
+
+@pytest.mark.parametrize("dt", TYPES, ids=ids)
+def test_tensor_core_mode_keeps_its_accuracy_for_tiny_and_huge_rows(tq, dt):
+    """Rows of 1e-6 magnitude would sink into f16 subnormals and rows of 1e+6 overflow without
+    the per-row power-of-two scaling in front of the f16 conversion."""
+    n, k, m = 256, 1024, 96
+    w = make_weight(dt, n, k, SEED + 71)
+    rng = np.random.default_rng(SEED + 72)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    x[::3] *= np.float32(1e-6)
+    x[1::3] *= np.float32(1e6)
+    x[5] *= np.float32(1e-30)
+    mm = tq.QMatMul.from_arc(tq.QTensor.new(w, tq.GgmlDType(dt), (n, k)))
+    y = mm.forward(torch.from_numpy(x).cuda(), mode=tq.Mode.TENSOR_CORE).cpu().numpy()
+    want = oracle.matmul_f64(dt, w, n, k, x)
+    for r in range(m):
+        assert oracle.rel_fro(y[r], want[r]) < TOL, r

@@ -124,3 +124,58 @@ def test_f16_conversions_exhaustive():
         ref = t.astype(np.float16).view(np.uint16)
     mine = np.array([lib.tqo_f32_to_f16(float(v)) for v in t], dtype=np.uint16)
     assert np.array_equal(ref, mine)
+
+
+def _tie_rows():
+    """Rows whose scaled values are exact .5 ties: block maximum +-1.0 -> |iscale| = 128 (or 127)."""
+    k = 256
+    j = np.arange(k - 1)
+    x = np.empty((2, k), np.float32)
+    x[0, :-1] = ((2 * j + 1) % 255) / np.float32(256.0) * np.where(j % 3 == 0, -1, 1)
+    x[0, -1] = 1.0
+    x[1, :-1] = ((2 * j + 1) % 253) / np.float32(254.0) * np.where(j % 2 == 0, -1, 1)   # ties for divisor 127
+    x[1, -1] = -1.0
+    return x
+
+
+def _q(blocks):
+    return blocks.reshape(-1, 292)[:, 4:260].view(np.int8).astype(np.int32), blocks.reshape(-1, 292)[:, :4].view(np.float32)
+
+
+def test_q8k_default_is_candles_published_quantizer_ties_away_from_zero():
+    assert oracle.q8k_variant() == 0x180          # divisor 128, negative-scale convention, ties away
+    x = _tie_rows()[:1]
+    q, d = _q(oracle.quantize(oracle.Q8_K, x))
+    v = np.float32(-128.0) * x[0]
+    want = np.where(v >= 0, np.floor(v + 0.5), -np.floor(-v + 0.5)).astype(np.int32)   # half away from zero
+    assert np.array_equal(q[0], np.minimum(want, 127))
+    assert q[0, -1] == -128 and d[0, 0] == np.float32(-1 / 128)
+    assert np.count_nonzero(np.abs(v - np.trunc(v)) == 0.5) > 100      # half of the row is exact ties
+
+
+@pytest.mark.parametrize("defs,check", [
+    ({"TQO_Q8K_ROUND_HALF_EVEN": 1}, "even"),
+    ({"TQO_Q8K_DIVISOR": 127}, "div127"),
+    ({"TQO_Q8K_NEG_SCALE": 0}, "pos"),
+    ({"TQO_Q8K_DIVISOR": 127, "TQO_Q8K_NEG_SCALE": 0, "TQO_Q8K_ROUND_HALF_EVEN": 1}, "ggml127"),
+], ids=["ties_to_even", "divisor_127", "positive_scale", "all_three"])
+def test_q8k_switches_each_change_exactly_their_choice(defs, check):
+    x = _tie_rows()
+    base_q, base_d = _q(oracle.quantize(oracle.Q8_K, x))
+    q, d = _q(oracle.quantize_q8k_variant(x, **defs))
+    if check == "even":
+        v = np.float32(-128.0) * x[0]
+        assert np.array_equal(q[0], np.minimum(np.rint(v).astype(np.int32), 127))     # numpy rint: ties to even
+        assert not np.array_equal(q[0], base_q[0]) and np.array_equal(d, base_d)
+    elif check == "div127":
+        assert d[0, 0] == np.float32(1.0) / (np.float32(-127.0) / np.float32(1.0)) and q[0, -1] == -127
+        assert d[1, 0] == np.float32(1.0) / (np.float32(-127.0) / np.float32(-1.0)) and q[1, -1] == -127
+    elif check == "pos":
+        assert np.all(d > 0) and q[0, -1] == 127 and q[1, -1] == -128      # +1.0 * 128 clamps, -1.0 * 128 fits
+        assert np.array_equal(q[1], base_q[1])                             # row 1's maximum is negative: same scale
+    else:
+        v = (np.float32(127.0) / np.float32(1.0)) * x[1]
+        assert np.array_equal(q[1], np.rint(v).astype(np.int32)) and d[1, 0] == np.float32(1.0) / np.float32(127.0)
+    # group sums always match the quants
+    b = oracle.quantize_q8k_variant(x, **defs).reshape(-1, 292)
+    assert np.array_equal(b[:, 260:].view(np.int16), q.reshape(2, 16, 16).sum(2).astype(np.int16))

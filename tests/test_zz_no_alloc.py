@@ -59,5 +59,34 @@ def test_static_entry_refuses_what_does_not_fit():
     x = torch.zeros((m, k), dtype=torch.float32, device="cuda")
     st, _ = _static_forward(lib, ctx, qt, x)
     assert st == 9 and b"static buffer" in lib.turq_last_error(ctx.handle)
-    st, y = _static_forward(lib, ctx, qt, x[:8])       # and the context is still usable
+    # 330 rows need 3.2 MB of planes: inside the 4 MiB array, but not beside its hand-over workspace
+    st, _ = _static_forward(lib, ctx, qt, x[:330])
+    assert st == 9 and b"hand-over workspace" in lib.turq_last_error(ctx.handle)
+    st, y = _static_forward(lib, ctx, qt, x[:8])       # a refused call leaves the context usable
     assert st == 0 and torch.equal(y, torch.zeros_like(y))
+    st, _ = _static_forward(lib, ctx, qt, x[:280])     # 2.7 MB of planes: fits
+    assert st == 0
+
+
+@pytest.mark.parametrize("n,k,m,why", [
+    (9600, 4096, 2, "601 row-tiles on 296 CTA slots: row-tiles are cut between CTAs, partial sums and "
+                    "ready flags go through the workspace at the tail of the static array"),
+    (304, 1024, 1, "one row of 1024 values: the CTAs quantize the activations themselves, the array is only "
+                   "used for its workspace"),
+    (304, 4096, 9, "planes staged through the array and bulk-copied into shared memory"),
+], ids=["cut_row_tiles", "in_kernel_quantization", "staged_planes"])
+def test_static_entry_on_each_route_of_the_matmul(n, k, m, why):
+    from tur_b200 import GgmlDType, Mode, QMatMul, QTensor, _lib, context
+    lib = _lib.load()
+    rng = np.random.default_rng(299792458 + n + m)
+    w = oracle.quantize(oracle.Q4_K, (rng.standard_normal((min(n, 608), k)) * 0.02).astype(np.float32))
+    w = np.ascontiguousarray(np.tile(w, (-(-n // w.shape[0]), 1))[:n])
+    qt = QTensor.new(w, GgmlDType.Q4K, (n, k))
+    ctx = context(qt.device())
+    mm = QMatMul.from_arc(qt)
+    for seed in (1, 2):                                # two calls in a row, different inputs
+        x = torch.from_numpy(np.random.default_rng(seed).standard_normal((m, k)).astype(np.float32)).cuda()
+        st, y = _static_forward(lib, ctx, qt, x)
+        assert st == 0, lib.turq_last_error(ctx.handle)
+        assert torch.equal(y, mm.forward(x, mode=Mode.INT8_ACT)), why
+    ctx.poll_status()

@@ -16,6 +16,7 @@ PP = ctypes.POINTER(c_vp)
 # name -> (restype, argtypes); kept in step with include/turq.h (a test checks it)
 SIGNATURES = {
     "turq_version": (c_i32, []),
+    "turq_q8k_variant": (c_i32, []),
     "turq_status_string": (ctypes.c_char_p, [c_i32]),
     "turq_block_elems": (c_i32, [c_i32]),
     "turq_block_bytes": (c_i32, [c_i32]),
@@ -25,6 +26,8 @@ SIGNATURES = {
     "turq_last_error": (ctypes.c_char_p, [c_vp]),
     "turq_ctx_launch_count": (c_i64, [c_vp]),
     "turq_ctx_poll_status": (c_i32, [c_vp, c_vp]),
+    "turq_ctx_reserve": (c_i32, [c_vp, c_i64, c_i64, c_i64]),
+    "turq_ctx_set_auto_policy": (c_i32, [c_vp, c_i32]),
     "turq_qtensor_from_host": (c_i32, [c_vp, c_i32, c_i64, c_i64, c_vp, c_sz, PP]),
     "turq_qtensor_from_device": (c_i32, [c_vp, c_i32, c_i64, c_i64, c_vp, c_sz, c_vp, PP]),
     "turq_qtensor_slice_rows": (c_i32, [c_vp, c_vp, c_i64, c_i64, PP]),
@@ -38,6 +41,7 @@ SIGNATURES = {
     "turq_qmatmul": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i64, c_vp, c_i32, c_vp, c_vp]),
     "turq_qmatmul_multi": (c_i32, [c_vp, c_i32, c_vp, c_vp, c_i32, c_i64, c_vp, c_i32, c_vp, c_vp]),
     "turq_qmatmul_host": (c_i32, [c_vp, c_vp, c_vp, c_i64, c_vp, c_i32, c_vp]),
+    "turq_qmatmul_multi_host": (c_i32, [c_vp, c_i32, c_vp, c_vp, c_i64, c_vp, c_i32, c_vp]),
     "turq_qmatmul_static": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i64, c_vp, c_vp, c_vp]),
 }
 

@@ -3,13 +3,16 @@
 // GGUF wire blocks (public entry, parity-tested bit-exact) and the plane layout the GEMV
 // kernels read (same integers and scales, produced by the same device code).
 //
-// Q8_K (GGML reference semantics): the element of largest magnitude (first one on ties)
-// maps to -128 before the clamp at 127, rounding is to nearest-even, d = 1/iscale.
+// Q8_K (defaults; the three choices are compile-time switches, see actquant.cuh): the element of
+// largest magnitude (first one on ties) maps to -128 before the clamp at 127, ties round away
+// from zero, d = 1/iscale.
 // Q8_0: d = amax/127 in f32, stored as f16; q = round-half-away(x * (1/d)).
 #include "actquant.cuh"
 #include "turq_internal.h"
 
 namespace turq {
+
+int q8k_variant() { return TURQ_Q8K_DIVISOR | (TURQ_Q8K_NEG_SCALE ? 0x100 : 0) | (TURQ_Q8K_ROUND_HALF_EVEN ? 0x200 : 0); }
 
 ActPackPlan plan_act_pack(int fmt, int64_t m, int64_t k) {
   auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
@@ -121,12 +124,12 @@ static cudaError_t launch_act(int fmt, const void* x, int x_dtype, int64_t m, in
   if (fmt == TQ_Q8_K) {
     int64_t warps = m * (k >> 8);
     int64_t blocks = (warps + 3) / 4;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > (int64_t)device_sm_count() * 16) blocks = (int64_t)device_sm_count() * 16;
     quant_q8k_kernel<<<(unsigned)blocks, threads, 0, s>>>(x, is_bf16, m, k, out);
   } else if (fmt == TQ_Q8_0) {
     int64_t warps = m * (((k >> 5) + 7) >> 3);
     int64_t blocks = (warps + 3) / 4;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > (int64_t)device_sm_count() * 16) blocks = (int64_t)device_sm_count() * 16;
     quant_q8_0_kernel<<<(unsigned)blocks, threads, 0, s>>>(x, is_bf16, m, k, out);
   } else {
     return cudaErrorInvalidValue;

@@ -4,7 +4,49 @@
 #pragma once
 #include "device_utils.cuh"
 
+// The Q8_K activation quantizer has three choices on which GGML revisions and candle differ.
+// They are compile-time switches here and (under the TQO_ prefix) in the CPU oracle, which
+// must be built with the same values; turq_q8k_variant() reports what a library was built with.
+//   TURQ_Q8K_DIVISOR          128 (default) or 127: magnitude the block maximum maps to
+//   TURQ_Q8K_NEG_SCALE        1 (default): iscale = -DIVISOR / (signed element of largest
+//                             magnitude, first one on ties), so that element maps to -DIVISOR
+//                             and d = 1/iscale carries its sign; 0: iscale = DIVISOR / amax
+//   TURQ_Q8K_ROUND_HALF_EVEN  0 (default): ties round away from zero (Rust's f32::round, which
+//                             candle-core's BlockQ8K::from_float applies); 1: ties to even
+//                             (GGML's nearest_int)
+// The defaults are candle-core's published behaviour; the result is then clamped at 127.
+#ifndef TURQ_Q8K_DIVISOR
+#define TURQ_Q8K_DIVISOR 128
+#endif
+#ifndef TURQ_Q8K_NEG_SCALE
+#define TURQ_Q8K_NEG_SCALE 1
+#endif
+#ifndef TURQ_Q8K_ROUND_HALF_EVEN
+#define TURQ_Q8K_ROUND_HALF_EVEN 0
+#endif
+#if TURQ_Q8K_DIVISOR != 127 && TURQ_Q8K_DIVISOR != 128
+#error "TURQ_Q8K_DIVISOR must be 127 or 128"
+#endif
+
 namespace turq {
+
+// mx = the element of largest magnitude (signed), amax = its magnitude (> 0)
+__device__ __forceinline__ float q8k_iscale(float mx, float amax) {
+#if TURQ_Q8K_NEG_SCALE
+  (void)amax;
+  return __fdiv_rn(-(float)TURQ_Q8K_DIVISOR, mx);
+#else
+  (void)mx;
+  return __fdiv_rn((float)TURQ_Q8K_DIVISOR, amax);
+#endif
+}
+__device__ __forceinline__ int q8k_round(float v) {
+#if TURQ_Q8K_ROUND_HALF_EVEN
+  return min(127, __float2int_rn(v));
+#else
+  return min(127, (int)roundf(v));
+#endif
+}
 
 __device__ __forceinline__ void load8(const void* x, int is_bf16, int64_t idx, float (&v)[8]) {
   if (is_bf16) {
@@ -28,8 +70,8 @@ __device__ __forceinline__ uint32_t pack4(const int* q) {
 }
 
 // Q8_K block of 256 values held 8 per lane (lane owns elements 8*lane .. 8*lane+7).
-// GGML reference semantics: the element of largest magnitude (first on ties) maps to -128
-// before the clamp at 127, round-to-nearest-even, d = 1/iscale. Returns the packed quants
+// Default semantics: the element of largest magnitude (first on ties) maps to -128 before the
+// clamp at 127, ties round away from zero, d = 1/iscale (switches above). Returns the packed quants
 // (w0, w1), the block scale d and the sums of this lane's aligned group of 16 and of 32.
 __device__ __forceinline__ void quant_block_q8k(const float (&v)[8], int lane, uint32_t& w0, uint32_t& w1, float& d,
                                                 int& s16, int& s32) {
@@ -54,9 +96,9 @@ __device__ __forceinline__ void quant_block_q8k(const float (&v)[8], int lane, u
 #pragma unroll
     for (int e = 0; e < 8; e++) q[e] = 0;
   } else {
-    float iscale = __fdiv_rn(-128.f, mx);
+    const float iscale = q8k_iscale(mx, amax);
 #pragma unroll
-    for (int e = 0; e < 8; e++) q[e] = min(127, __float2int_rn(__fmul_rn(iscale, v[e])));
+    for (int e = 0; e < 8; e++) q[e] = q8k_round(__fmul_rn(iscale, v[e]));
     d = __fdiv_rn(1.f, iscale);
   }
   int s8 = 0;
@@ -89,9 +131,9 @@ __device__ __forceinline__ void quant_block_q8k_half(const float (&v)[16], int l
 #pragma unroll
     for (int e = 0; e < 16; e++) q[e] = 0;
   } else {
-    const float iscale = __fdiv_rn(-128.f, mx);
+    const float iscale = q8k_iscale(mx, __uint_as_float(wmax));
 #pragma unroll
-    for (int e = 0; e < 16; e++) q[e] = min(127, __float2int_rn(__fmul_rn(iscale, v[e])));
+    for (int e = 0; e < 16; e++) q[e] = q8k_round(__fmul_rn(iscale, v[e]));
     d = __fdiv_rn(1.f, iscale);
   }
   s16 = 0;

@@ -11,6 +11,35 @@
 #include "handles.h"
 #include "turq_internal.h"
 
+namespace turq {
+
+namespace {
+struct DeviceFacts {
+  std::atomic<int> sms{0}, smem_optin{0};
+};
+DeviceFacts g_facts[64];
+
+int fact(int which) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+  std::atomic<int>& slot = which == 0 ? g_facts[dev].sms : g_facts[dev].smem_optin;
+  int v = slot.load(std::memory_order_acquire);
+  if (v > 0) return v;
+  if (cudaDeviceGetAttribute(&v, which == 0 ? cudaDevAttrMultiProcessorCount : cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) !=
+          cudaSuccess || v <= 0) {
+    cudaGetLastError();
+    v = which == 0 ? 1 : 48 * 1024;
+  }
+  slot.store(v, std::memory_order_release);
+  return v;
+}
+}  // namespace
+
+int device_sm_count() { return fact(0); }
+int device_smem_optin() { return fact(1); }
+
+}  // namespace turq
+
 namespace {
 
 int32_t fail(turq_ctx* ctx, int32_t st, const char* fmt, ...) {
@@ -38,6 +67,8 @@ int32_t cuda_fail(turq_ctx* ctx, cudaError_t e, const char* what) {
     if (e__ != cudaSuccess) return cuda_fail(ctx, e__, #call); \
   } while (0)
 
+// Grows a context-owned buffer. Growing synchronizes the device and reallocates, which is why
+// turq_ctx_reserve exists: a caller that reserves for its largest call never gets here again.
 int32_t ensure(turq_ctx* ctx, uint8_t** buf, size_t* have, size_t need) {
   if (need <= *have) return TURQ_OK;
   size_t want = need + need / 4;
@@ -93,6 +124,7 @@ int32_t new_qtensor(turq_ctx* ctx, int dtype, int64_t n_rows, int64_t n_cols, tu
 extern "C" {
 
 int32_t turq_version(void) { return TURQ_VERSION; }
+int32_t turq_q8k_variant(void) { return turq::q8k_variant(); }
 
 const char* turq_status_string(int32_t st) {
   switch (st) {
@@ -167,6 +199,38 @@ int32_t turq_ctx_destroy(turq_ctx* ctx) {
   if (ctx->gemv_ws) cudaFree(ctx->gemv_ws);
   if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
   delete ctx;
+  return TURQ_OK;
+}
+
+int32_t turq_ctx_reserve(turq_ctx* ctx, int64_t max_m, int64_t max_k, int64_t max_n) {
+  if (!ctx) return TURQ_E_INVALID_ARG;
+  if (max_m <= 0 || max_k <= 0 || max_n <= 0 || max_m > INT32_MAX / 2 || max_k > INT32_MAX || max_n > INT32_MAX)
+    return fail(ctx, TURQ_E_SHAPE, "reserve(%lld, %lld, %lld): sizes must be positive and fit 31 bits", (long long)max_m,
+                (long long)max_k, (long long)max_n);
+  TQ_CUDA(ctx, cudaSetDevice(ctx->device));
+  const int64_t k256 = (max_k + 255) / 256 * 256;
+  size_t need = turq::plan_act_pack(TQ_Q8_K, max_m, k256).total;
+  const size_t q80 = turq::plan_act_pack(TQ_Q8_0, max_m, k256).total;
+  if (q80 > need) need = q80;
+  // the tensor-core path's f16 operand and split-K partial sums (decode batches split the K loop)
+  for (int64_t mm : {max_m < 64 ? max_m : (int64_t)64, max_m}) {
+    const size_t tc = turq::gemm_tc_scratch_bytes(mm, k256, max_n, ctx->sm_count);
+    if (tc > need) need = tc;
+    // the widest split happens for weights of at most 128 rows
+    const size_t tc_small = turq::gemm_tc_scratch_bytes(mm, k256, max_n < 128 ? max_n : 128, ctx->sm_count);
+    if (tc_small > need) need = tc_small;
+  }
+  int32_t st = ensure(ctx, &ctx->scratch, &ctx->scratch_bytes, need);
+  if (st != TURQ_OK) return st;
+  auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+  return ensure(ctx, &ctx->io, &ctx->io_bytes,
+                up((size_t)max_m * max_k * 4) + 4 * up((size_t)max_m * max_n * 4) + 4 * up((size_t)max_n * 4));
+}
+
+int32_t turq_ctx_set_auto_policy(turq_ctx* ctx, int32_t mode) {
+  if (!ctx) return TURQ_E_INVALID_ARG;
+  if (mode < TURQ_MODE_AUTO || mode > TURQ_MODE_TENSOR_CORE) return fail(ctx, TURQ_E_INVALID_ARG, "unknown mode %d", mode);
+  ctx->auto_policy = mode;
   return TURQ_OK;
 }
 
@@ -355,9 +419,14 @@ int32_t turq_quantize_act(turq_ctx* ctx, int32_t fmt, const void* dev_x, int32_t
 // TURQ_MODE_AUTO: the integer GEMV up to 16 rows, the tcgen05 GEMM above (64-row activation
 // tiles with split-K for decode batches, 128/256-row tiles for prefill). Measured on B200 at 32
 // and 64 rows the GEMM is ahead for every weight shape of the benchmark configurations.
+// A context whose policy was pinned with turq_ctx_set_auto_policy uses that one scheme for every
+// row count, so a token's result does not depend on the batch or chunk it arrives in.
 static int32_t auto_mode(const turq_ctx* ctx, int64_t n_rows, int64_t n_cols, int64_t m) {
-  (void)ctx;
   (void)n_rows;
+  if (ctx->auto_policy != TURQ_MODE_AUTO) {
+    if (ctx->auto_policy == TURQ_MODE_TENSOR_CORE && n_cols % 64 != 0) return TURQ_MODE_INT8_ACT;
+    return ctx->auto_policy;
+  }
   return (m <= 16 || n_cols % 64 != 0) ? TURQ_MODE_INT8_ACT : TURQ_MODE_TENSOR_CORE;
 }
 
@@ -399,9 +468,9 @@ int32_t turq_qmatmul(turq_ctx* ctx, const turq_qtensor* qt, const void* dev_x, i
   return TURQ_OK;
 }
 
-int32_t turq_qmatmul_multi(turq_ctx* ctx, int32_t count, const turq_qtensor* const* qts, const void* dev_x,
-                           int32_t x_dtype, int64_t m, float* const* dev_ys, int32_t mode,
-                           const float* const* dev_biases, void* stream) {
+static int32_t qmatmul_multi_impl(turq_ctx* ctx, int32_t count, const turq_qtensor* const* qts, const void* dev_x,
+                                  int32_t x_dtype, int64_t m, float* const* dev_ys, int32_t mode,
+                                  const float* const* dev_biases, void* stream, bool x_remote) {
   if (!ctx || !qts || !dev_x || !dev_ys) return fail(ctx, TURQ_E_INVALID_ARG, "null argument");
   if (count < 1 || count > 4) return fail(ctx, TURQ_E_INVALID_ARG, "count %d outside 1..4", count);
   for (int i = 0; i < count; i++) {
@@ -418,7 +487,8 @@ int32_t turq_qmatmul_multi(turq_ctx* ctx, int32_t count, const turq_qtensor* con
     for (int i = 0; i < count; i++) rows_all += qts[i]->n_rows;
     eff = auto_mode(ctx, rows_all, qts[0]->n_cols, m);
   }
-  if (!same || eff != TURQ_MODE_INT8_ACT || count == 1) {
+  if (!same || eff != TURQ_MODE_INT8_ACT || (count == 1 && !x_remote)) {
+    if (x_remote) return fail(ctx, TURQ_E_INVALID_ARG, "host-mapped activations need the integer scheme and one activation format");
     for (int i = 0; i < count; i++) {
       int32_t st = turq_qmatmul(ctx, qts[i], dev_x, x_dtype, m, dev_ys[i], mode, dev_biases ? dev_biases[i] : nullptr, stream);
       if (st != TURQ_OK) return st;
@@ -440,31 +510,104 @@ int32_t turq_qmatmul_multi(turq_ctx* ctx, int32_t count, const turq_qtensor* con
     parts[i] = turq::GemvPart{qts[i]->tiles, qts[i]->n_rows, dev_ys[i], dev_biases ? dev_biases[i] : nullptr, qts[i]->dtype};
   int launches = 0;
   cudaError_t e = turq::launch_gemv_int8_multi(qts[0]->dtype, parts, count, k, dev_x, x_dtype, ctx->scratch, m, ctx->gemv_ws,
-                                               ctx->dev_status, ctx->sm_count, static_cast<cudaStream_t>(stream), &launches);
+                                               ctx->dev_status, ctx->sm_count, static_cast<cudaStream_t>(stream), &launches,
+                                               x_remote);
   ctx->launches += launches;
   if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_multi launch");
   return TURQ_OK;
 }
 
+int32_t turq_qmatmul_multi(turq_ctx* ctx, int32_t count, const turq_qtensor* const* qts, const void* dev_x,
+                           int32_t x_dtype, int64_t m, float* const* dev_ys, int32_t mode,
+                           const float* const* dev_biases, void* stream) {
+  return qmatmul_multi_impl(ctx, count, qts, dev_x, x_dtype, m, dev_ys, mode, dev_biases, stream, false);
+}
+
+// Device-side alias of a host pointer when the memory is page-locked and reachable from this
+// device (cudaHostAlloc / cudaHostRegister under unified addressing); nullptr otherwise.
+static void* mapped_alias(const void* host_ptr) {
+  cudaPointerAttributes at;
+  if (cudaPointerGetAttributes(&at, host_ptr) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  if (at.type != cudaMemoryTypeHost || !at.devicePointer) return nullptr;
+  return at.devicePointer;
+}
+
+int32_t turq_qmatmul_multi_host(turq_ctx* ctx, int32_t count, const turq_qtensor* const* qts, const float* host_x,
+                                int64_t m, float* const* host_ys, int32_t mode, const float* const* host_biases) {
+  if (!ctx || !qts || !host_x || !host_ys) return fail(ctx, TURQ_E_INVALID_ARG, "null argument");
+  if (count < 1 || count > 4) return fail(ctx, TURQ_E_INVALID_ARG, "count %d outside 1..4", count);
+  if (m <= 0 || m > INT32_MAX / 2) return fail(ctx, TURQ_E_SHAPE, "m=%lld out of range", (long long)m);
+  bool k_quant = false, q8_0 = false;
+  int64_t rows_all = 0, rows_max = 0;
+  for (int i = 0; i < count; i++) {
+    if (!qts[i] || !host_ys[i]) return fail(ctx, TURQ_E_INVALID_ARG, "null argument");
+    if (qts[i]->n_cols != qts[0]->n_cols) return fail(ctx, TURQ_E_SHAPE, "weights of one call must share the in-feature count");
+    (qts[i]->dtype == TURQ_Q8_0 ? q8_0 : k_quant) = true;
+    rows_all += qts[i]->n_rows;
+    if (qts[i]->n_rows > rows_max) rows_max = qts[i]->n_rows;
+  }
+  TQ_CUDA(ctx, cudaSetDevice(ctx->device));
+  cudaStream_t s = ctx->own_stream;
+  const int64_t k = qts[0]->n_cols;
+  const int32_t eff = mode == TURQ_MODE_AUTO ? auto_mode(ctx, rows_all, k, m) : mode;
+  auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+
+  // Decode-sized calls on page-locked buffers run without any copy: the quantization launch
+  // reads x from the caller's memory once, the GEMV writes y straight into it, and the one
+  // synchronize at the end is the only host wait. Needs the integer scheme, 16-byte aligned x
+  // and little enough output that posted writes over the bus do not hold the kernel up.
+  if (eff == TURQ_MODE_INT8_ACT && !(k_quant && q8_0) && (size_t)m * rows_max * 4 <= ((size_t)2 << 20)) {
+    bool any_bias = false;
+    for (int i = 0; host_biases && i < count; i++) any_bias = any_bias || host_biases[i] != nullptr;
+    void* mx = any_bias ? nullptr : mapped_alias(host_x);  // a bias would be read element-wise over the bus
+    float* mys[4] = {nullptr, nullptr, nullptr, nullptr};
+    bool ok = mx != nullptr && (uintptr_t)mx % 16 == 0;
+    for (int i = 0; ok && i < count; i++) {
+      mys[i] = static_cast<float*>(mapped_alias(host_ys[i]));
+      ok = mys[i] != nullptr;
+    }
+    if (ok) {
+      int32_t st = qmatmul_multi_impl(ctx, count, qts, mx, TURQ_F32, m, mys, TURQ_MODE_INT8_ACT, nullptr, s, true);
+      if (st != TURQ_OK) return st;
+      return turq_ctx_poll_status(ctx, s);
+    }
+  }
+
+  // General case: one copy of x in, one launch group, one copy per output back, one synchronize.
+  size_t need = up((size_t)m * k * 4);
+  for (int i = 0; i < count; i++) need += up((size_t)m * qts[i]->n_rows * 4) + up((size_t)qts[i]->n_rows * 4);
+  int32_t st = ensure(ctx, &ctx->io, &ctx->io_bytes, need);
+  if (st != TURQ_OK) return st;
+  uint8_t* p = ctx->io;
+  float* dx = reinterpret_cast<float*>(p);
+  p += up((size_t)m * k * 4);
+  float* dys[4];
+  const float* dbs[4];
+  TQ_CUDA(ctx, cudaMemcpyAsync(dx, host_x, (size_t)m * k * 4, cudaMemcpyHostToDevice, s));
+  for (int i = 0; i < count; i++) {
+    dys[i] = reinterpret_cast<float*>(p);
+    p += up((size_t)m * qts[i]->n_rows * 4);
+    dbs[i] = nullptr;
+    if (host_biases && host_biases[i]) {
+      TQ_CUDA(ctx, cudaMemcpyAsync(p, host_biases[i], (size_t)qts[i]->n_rows * 4, cudaMemcpyHostToDevice, s));
+      dbs[i] = reinterpret_cast<const float*>(p);
+    }
+    p += up((size_t)qts[i]->n_rows * 4);
+  }
+  st = qmatmul_multi_impl(ctx, count, qts, dx, TURQ_F32, m, dys, mode, dbs, s, false);
+  if (st != TURQ_OK) return st;
+  for (int i = 0; i < count; i++)
+    TQ_CUDA(ctx, cudaMemcpyAsync(host_ys[i], dys[i], (size_t)m * qts[i]->n_rows * 4, cudaMemcpyDeviceToHost, s));
+  return turq_ctx_poll_status(ctx, s);
+}
+
 int32_t turq_qmatmul_host(turq_ctx* ctx, const turq_qtensor* qt, const float* host_x, int64_t m, float* host_y,
                           int32_t mode, const float* host_bias) {
   if (!ctx || !qt || !host_x || !host_y) return fail(ctx, TURQ_E_INVALID_ARG, "null argument");
-  if (m <= 0) return fail(ctx, TURQ_E_SHAPE, "m=%lld must be positive", (long long)m);
-  TQ_CUDA(ctx, cudaSetDevice(ctx->device));
-  auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
-  const size_t xb = up((size_t)m * qt->n_cols * 4), yb = up((size_t)m * qt->n_rows * 4), bb = up((size_t)qt->n_rows * 4);
-  int32_t st = ensure(ctx, &ctx->io, &ctx->io_bytes, xb + yb + bb);
-  if (st != TURQ_OK) return st;
-  float* dx = reinterpret_cast<float*>(ctx->io);
-  float* dy = reinterpret_cast<float*>(ctx->io + xb);
-  float* db = host_bias ? reinterpret_cast<float*>(ctx->io + xb + yb) : nullptr;
-  cudaStream_t s = ctx->own_stream;
-  TQ_CUDA(ctx, cudaMemcpyAsync(dx, host_x, (size_t)m * qt->n_cols * 4, cudaMemcpyHostToDevice, s));
-  if (db) TQ_CUDA(ctx, cudaMemcpyAsync(db, host_bias, (size_t)qt->n_rows * 4, cudaMemcpyHostToDevice, s));
-  st = turq_qmatmul(ctx, qt, dx, TURQ_F32, m, dy, mode, db, s);
-  if (st != TURQ_OK) return st;
-  TQ_CUDA(ctx, cudaMemcpyAsync(host_y, dy, (size_t)m * qt->n_rows * 4, cudaMemcpyDeviceToHost, s));
-  return turq_ctx_poll_status(ctx, s);
+  return turq_qmatmul_multi_host(ctx, 1, &qt, host_x, m, &host_y, mode, host_bias ? &host_bias : nullptr);
 }
 
 }  // extern "C"

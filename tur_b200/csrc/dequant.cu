@@ -58,7 +58,7 @@ static cudaError_t launch_dt(const uint8_t* tiles, void* out, int out_dtype, int
   if (total == 0) return cudaSuccess;
   int threads = 256;
   int64_t blocks = (total + 7) / 8;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > (int64_t)device_sm_count() * 16) blocks = (int64_t)device_sm_count() * 16;
   switch (out_dtype) {
     case TQ_F32:
       dequant_kernel<DT, float><<<(unsigned)blocks, threads, 0, s>>>(tiles, (float*)out, n_rows, k, ktiles, total);
@@ -116,7 +116,7 @@ static cudaError_t launch_gather_dt(const uint8_t* tiles, const int32_t* ids, vo
   const int64_t total = n_ids * ktiles;
   if (total == 0) return cudaSuccess;
   int64_t blocks = (total + 7) / 8;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > (int64_t)device_sm_count() * 16) blocks = (int64_t)device_sm_count() * 16;
   switch (out_dtype) {
     case TQ_F32:
       gather_rows_kernel<DT, float><<<(unsigned)blocks, 256, 0, s>>>(tiles, ids, (float*)out, n_rows, n_ids, k, ktiles, status);

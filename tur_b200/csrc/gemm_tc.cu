@@ -2,8 +2,8 @@
 //
 //   y[m, n] = sum_k x[m, k] * W[n, k]      W quantized (device fragment tiles), x f32 or bf16
 //
-// Step 1 (prep kernel): x -> f16 [M, K], each row scaled by a power of two only when its
-// magnitude would overflow f16 (the scale is undone exactly in the epilogue).
+// Step 1 (prep kernel): x -> f16 [M, K], each row scaled by a power of two that puts its largest
+// magnitude just below the top of the f16 range (the scale is undone exactly in the epilogue).
 // Step 2 (this kernel, one CTA per 128 weight rows x BN = 256 or 64 activation rows):
 //   * warp 0        TMA producer: activation tiles (256 rows x 64 k, f16) into 128B-swizzled
 //                   shared memory (cp.async.bulk.tensor, no multicast);
@@ -462,8 +462,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
   }
 }
 
-// x [m, k] (f32 / bf16) -> f16 [m, k] with a per-row power-of-two scale that is 1 unless the
-// row would overflow f16; rscale[m] undoes it. One CTA per row.
+// x [m, k] (f32 / bf16) -> f16 [m, k] with a per-row power-of-two scale that brings the row's
+// largest magnitude into [8192, 16384): rows of large values do not overflow f16 and rows of
+// tiny values do not sink into its subnormals. rscale[m] undoes the scale exactly in the
+// epilogue. Rows that are all zero, or hold an infinity or NaN, are converted as they are.
+// One CTA per row.
 __global__ void __launch_bounds__(256) prep_act_kernel(const void* __restrict__ x, int is_bf16, int64_t k,
                                                         __half* __restrict__ xh, float* __restrict__ rscale) {
   __shared__ float wmax[8];
@@ -478,10 +481,12 @@ __global__ void __launch_bounds__(256) prep_act_kernel(const void* __restrict__ 
 #pragma unroll
   for (int w = 1; w < 8; w++) amax = fmaxf(amax, wmax[w]);
   float s = 1.f;
-  if (amax >= 16384.f && amax < 3.0e38f) {
+  if (amax > 0.f && amax < 3.0e38f) {  // also false for NaN
     int e;
     frexpf(amax, &e);           // amax = f * 2^e, f in [0.5, 1)
-    s = ldexpf(1.f, 14 - e);    // scaled row maximum lands in [8192, 16384)
+    int se = 14 - e;            // scaled row maximum lands in [8192, 16384)
+    if (se > 126) se = 126;     // keep the scale and its reciprocal normal numbers
+    s = ldexpf(1.f, se);
   }
   if (threadIdx.x == 0) rscale[row] = 1.f / s;
   for (int64_t i = threadIdx.x; i < k; i += blockDim.x)
@@ -535,13 +540,13 @@ template <int DT, int BN>
 cudaError_t launch_tc_bn(const CUtensorMap& map, const GemmArgs& a, cudaStream_t s) {
   constexpr int ST = stages_for_bn(BN);
   constexpr int SMEM = ST * (A_BYTES + BN * BK * 2) + (3 * ST + 1) * 8 + 16 + 1024;
-  static int configured_dev = -1;
+  static PerDeviceOnce configured;
   int dev = 0;
   cudaGetDevice(&dev);
-  if (configured_dev != dev) {
+  if (!configured.done(dev)) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<DT, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return e;
-    configured_dev = dev;
+    configured.set(dev);
   }
   dim3 grid((unsigned)((a.n_rows + BM - 1) / BM), (unsigned)((a.m + BN - 1) / BN), (unsigned)a.splits);
   gemm_tc_kernel<DT, BN><<<grid, TC_THREADS, SMEM, s>>>(map, a);
@@ -556,12 +561,12 @@ cudaError_t launch_tc_dt(const CUtensorMap& map, const GemmArgs& a, int bn, cuda
 }  // namespace
 
 static int pick_bn(int64_t n_rows, int64_t m, int sm_count) {
-  static const int bn_env = getenv("TURQ_GEMM_BN") ? atoi(getenv("TURQ_GEMM_BN")) : 0;
+  static const int bn_env = tuning_env("TURQ_GEMM_BN", 0);
   return plan_gemm_bn(n_rows, m, sm_count, bn_env);
 }
 
 static int pick_splits(int64_t n_rows, int64_t m, int64_t k, int sm_count) {
-  static const int env = getenv("TURQ_GEMM_SPLITK") ? atoi(getenv("TURQ_GEMM_SPLITK")) : -1;
+  static const int env = tuning_env("TURQ_GEMM_SPLITK", -1);
   return plan_gemm_splits(n_rows, m, k, sm_count, env);
 }
 

@@ -547,17 +547,7 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
 
 // ------------------------------------------------------------------ host side
 
-static int g_smem_optin = -1;
-
-static int smem_budget() {
-  if (g_smem_optin < 0) {
-    int dev = 0, v = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
-    g_smem_optin = v > 0 ? v : 48 * 1024;
-  }
-  return g_smem_optin;
-}
+static int smem_budget() { return device_smem_optin(); }
 
 // In-kernel quantization is redundant work in every CTA and every CTA reads the same few
 // cache lines of x: one pass (16 Q8_K blocks, or 64 Q8_0 blocks, per CTA) costs about as much
@@ -567,25 +557,28 @@ static int smem_budget() {
 // launch of their own and bulk-copied; Q6_K 4096x12288, three passes, 15.0 against 12.4 us).
 bool gemv_int8_fuses_act(int dtype, int64_t m, int64_t k) {
   (void)dtype;
-  static const int max_elems = getenv("TURQ_GEMV_FUSE_ELEMS") ? atoi(getenv("TURQ_GEMV_FUSE_ELEMS")) : 4096;
+  static const int max_elems = tuning_env("TURQ_GEMV_FUSE_ELEMS", 4096);
   return m <= 8 && m * k <= max_elems;
 }
 
 // partial sums [up to 4 CTAs per SM][4 groups of 8 rows][128] + one flag per CTA
 size_t gemv_workspace_bytes(int sms) { return (size_t)sms * 4 * 4 * 128 * 4 + (size_t)sms * 4 * 4 + 256; }
+// where in the workspace the ready flags live (the only part that must read zero at launch)
+size_t gemv_workspace_flags_offset(int sms) { return (size_t)sms * 4 * 4 * 128 * 4; }
+size_t gemv_workspace_flags_bytes(int sms) { return (size_t)sms * 4 * 4; }
 
 // Launches with the programmatic-stream-serialization attribute (the kernel orders itself
 // against its predecessor with griddepcontrol.wait).
 template <int DT, int MG, int ACT, int DT2 = DT>
 static cudaError_t launch_one(StreamArgs a, int grid, int smem_bytes, cudaStream_t s, bool after_quant = false) {
-  static int configured_dev = -1;  // per instantiation; the attribute is per device function
+  static PerDeviceOnce configured;  // per instantiation; the attribute is per device function
   int dev = 0;
   cudaGetDevice(&dev);
-  if (configured_dev != dev) {
+  if (!configured.done(dev)) {
     cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<DT, MG, ACT, DT2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          smem_budget());
     if (e != cudaSuccess) return e;
-    configured_dev = dev;
+    configured.set(dev);
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
@@ -598,8 +591,8 @@ static cudaError_t launch_one(StreamArgs a, int grid, int smem_bytes, cudaStream
   cfg.attrs = attr;
   // Always-on variant for testing (TURQ_GEMV_PDL=1); by default only the launch that follows
   // its own quantization launch overlaps with it (TURQ_GEMV_PDL_PAIR=0 turns that off).
-  static const int pdl = getenv("TURQ_GEMV_PDL") ? atoi(getenv("TURQ_GEMV_PDL")) : 0;
-  static const int pdl_pair = getenv("TURQ_GEMV_PDL_PAIR") ? atoi(getenv("TURQ_GEMV_PDL_PAIR")) : 1;
+  static const int pdl = tuning_env("TURQ_GEMV_PDL", 0);
+  static const int pdl_pair = tuning_env("TURQ_GEMV_PDL_PAIR", 1);
   cfg.numAttrs = (pdl || (after_quant && pdl_pair)) ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<DT, MG, ACT, DT2>, a);
 }
@@ -610,7 +603,7 @@ static cudaError_t launch_one(StreamArgs a, int grid, int smem_bytes, cudaStream
 template <int DT, int DT2 = DT>
 static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const void* x, int x_dtype,
                              uint8_t* act_scratch, int64_t m, uint8_t* workspace, int* status, int sm_count,
-                             cudaStream_t s, int* launches) {
+                             cudaStream_t s, int* launches, bool x_remote) {
   constexpr bool MIXED = DT2 != DT;
   constexpr int GROUP = TileGeom<DT>::GROUP;
   constexpr int UNIT_BYTES = (TileGeom<DT2>::BYTES > TileGeom<DT>::BYTES ? TileGeom<DT2>::BYTES : TileGeom<DT>::BYTES) * GROUP;
@@ -623,10 +616,10 @@ static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const
   const int64_t T = (int64_t)rt_begin[nparts] * KU;
   if (T > (int64_t)1 << 30) return cudaErrorInvalidValue;
   // The tile split (hence the summation order) must not depend on M: always two CTAs per SM.
-  static const int cps_env = getenv("TURQ_GEMV_CPS") ? atoi(getenv("TURQ_GEMV_CPS")) : 0;
+  static const int cps_env = tuning_env("TURQ_GEMV_CPS", 0);
   const int ctas_per_sm = cps_env > 0 ? cps_env : 2;
   // Each CTA may use half of the SM's shared memory.
-  static const int share_env = getenv("TURQ_GEMV_SHARE") ? atoi(getenv("TURQ_GEMV_SHARE")) : 0;
+  static const int share_env = tuning_env("TURQ_GEMV_SHARE", 0);
   const int share_div = share_env > 0 ? share_env : 2;
   const int fmt = DT == TQ_Q8_0 ? TQ_Q8_0 : TQ_Q8_K;
   const int stage_bytes = NW * UNIT_BYTES;
@@ -635,7 +628,7 @@ static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const
   auto stages_for = [&](bool planes_in_smem, int cps, int rows, int mg) {
     if (cps < share_div) cps = share_div;
     const int share = (smem_budget() + 1024) / cps - 1024;  // 1 KB per CTA is reserved by the system
-    static const int gmax = getenv("TURQ_GEMV_GSTAGES") ? atoi(getenv("TURQ_GEMV_GSTAGES")) : MAX_STAGES;
+    static const int gmax = tuning_env("TURQ_GEMV_GSTAGES", MAX_STAGES);
     int st = planes_in_smem ? MAX_STAGES : (gmax < MAX_STAGES ? (gmax < 2 ? 2 : gmax) : MAX_STAGES);
     for (; st >= 2; st--)
       if (plan_smem(DT, mg, planes_in_smem, rows, (int)k, st, stage_bytes, DT2).total <= share) break;
@@ -644,11 +637,13 @@ static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const
   // Activation planes: quantized in the kernel (few rows), else quantized once by a launch of
   // their own and then either bulk-copied into every CTA's shared memory (up to 16 rows, when
   // they fit beside a two-stage ring) or read from global memory by the MMA loop.
-  int act_mode = gemv_int8_fuses_act(DT, m, k) ? ACT_FUSED : ACT_GLOBAL;
+  // x_remote: x lives in mapped host memory - every CTA reading it over the bus would cost far
+  // more than the one pass of the quantization launch, so the planes are always staged.
+  int act_mode = (gemv_int8_fuses_act(DT, m, k) && !x_remote) ? ACT_FUSED : ACT_GLOBAL;
   {
     const int rows0 = (int)(m < 32 ? m : 32), mg0 = rows0 <= 8 ? 1 : rows0 <= 16 ? 2 : 4;
     if (act_mode == ACT_FUSED && stages_for(true, ctas_per_sm, rows0, mg0) < 2) act_mode = ACT_GLOBAL;
-    static const int stage_env = getenv("TURQ_GEMV_STAGED") ? atoi(getenv("TURQ_GEMV_STAGED")) : 1;
+    static const int stage_env = tuning_env("TURQ_GEMV_STAGED", 1);
     if (act_mode == ACT_GLOBAL && m <= 16 && stage_env && stages_for(true, ctas_per_sm, rows0, mg0) >= 2) act_mode = ACT_STAGED;
   }
   const bool fused = act_mode == ACT_FUSED, planes_in_smem = act_mode != ACT_GLOBAL;
@@ -658,7 +653,7 @@ static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const
   // in tiles, with the hand-over of split row-tiles. Depends on the shape only, never on M.
   const int slots = sm_count * ctas_per_sm;
   const int row_tiles_all = rt_begin[nparts];
-  static const int split_env = getenv("TURQ_GEMV_SPLIT") ? atoi(getenv("TURQ_GEMV_SPLIT")) : -1;
+  static const int split_env = tuning_env("TURQ_GEMV_SPLIT", -1);
   const GemvSplit split = plan_gemv_split(row_tiles_all, KU, slots, split_env);
   const int grid = split.grid, split_q = split.split_q, split_r = split.split_r;
   const size_t x_es = x_dtype == TQ_BF16 ? 2 : 4;
@@ -699,7 +694,7 @@ static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const
     }
     a.rows = rows;
     a.partial = reinterpret_cast<float*>(workspace);
-    a.flags = reinterpret_cast<int*>(workspace + (size_t)sm_count * 4 * 4 * 128 * 4);
+    a.flags = reinterpret_cast<int*>(workspace + gemv_workspace_flags_offset(sm_count));
     a.status = status;
     const int stages = stages_for(planes_in_smem, ctas_per_sm, rows, mg);
     if (stages < 2) return cudaErrorInvalidConfiguration;
@@ -728,11 +723,11 @@ static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const
   return cudaSuccess;
 }
 
-#define TQ_LAUNCH_ARGS k, x, x_dtype, act_scratch, m, workspace, status, sm_count, s, launches
+#define TQ_LAUNCH_ARGS k, x, x_dtype, act_scratch, m, workspace, status, sm_count, s, launches, x_remote
 
 static cudaError_t launch_one_type(int dtype, const GemvPart* parts, int nparts, int64_t k, const void* x, int x_dtype,
                                    uint8_t* act_scratch, int64_t m, uint8_t* workspace, int* status, int sm_count,
-                                   cudaStream_t s, int* launches) {
+                                   cudaStream_t s, int* launches, bool x_remote) {
   switch (dtype) {
     case TQ_Q8_0: return launch_dt<TQ_Q8_0>(parts, nparts, TQ_LAUNCH_ARGS);
     case TQ_Q4_K: return launch_dt<TQ_Q4_K>(parts, nparts, TQ_LAUNCH_ARGS);
@@ -746,7 +741,7 @@ static cudaError_t launch_one_type(int dtype, const GemvPart* parts, int nparts,
 // together with Q6_K parts too, where the mixed kernel exists; anything else one launch per type.
 cudaError_t launch_gemv_int8_multi(int dtype, const GemvPart* parts, int nparts, int64_t k, const void* x, int x_dtype,
                                    uint8_t* act_scratch, int64_t m, uint8_t* workspace, int* status, int sm_count,
-                                   cudaStream_t s, int* launches) {
+                                   cudaStream_t s, int* launches, bool x_remote) {
   if (nparts < 1 || nparts > MAX_PARTS) return cudaErrorInvalidValue;
   GemvPart p[MAX_PARTS];
   int types[MAX_PARTS], ntypes = 0;
@@ -758,7 +753,7 @@ cudaError_t launch_gemv_int8_multi(int dtype, const GemvPart* parts, int nparts,
     if (!seen) types[ntypes++] = p[i].dtype;
   }
   if (ntypes == 1) return launch_one_type(types[0], p, nparts, TQ_LAUNCH_ARGS);
-  static const int mixed_env = getenv("TURQ_GEMV_MIXED") ? atoi(getenv("TURQ_GEMV_MIXED")) : 1;
+  static const int mixed_env = tuning_env("TURQ_GEMV_MIXED", 1);
   if (ntypes == 2 && mixed_env) {
     const int other = types[0] == TQ_Q6_K ? types[1] : types[0];
     if ((types[0] == TQ_Q6_K || types[1] == TQ_Q6_K) && (other == TQ_Q4_K || other == TQ_Q5_K)) {
@@ -783,7 +778,7 @@ cudaError_t launch_gemv_int8(int dtype, const uint8_t* tiles, int64_t n_rows, in
                              uint8_t* act_scratch, int64_t m, float* y, const float* bias, uint8_t* workspace,
                              int* status, int sm_count, cudaStream_t s, int* launches) {
   GemvPart part{tiles, n_rows, y, bias, dtype};
-  return launch_gemv_int8_multi(dtype, &part, 1, k, x, x_dtype, act_scratch, m, workspace, status, sm_count, s, launches);
+  return launch_gemv_int8_multi(dtype, &part, 1, k, x, x_dtype, act_scratch, m, workspace, status, sm_count, s, launches, false);
 }
 
 }  // namespace turq

@@ -17,6 +17,7 @@ struct turq_ctx {
   int* dev_status = nullptr;   // the same word's device address
   uint8_t* gemv_ws = nullptr;  // split row-tile workspace of the streaming GEMV (zeroed once)
   cudaStream_t own_stream = nullptr;
+  int auto_policy = 0;  // what TURQ_MODE_AUTO resolves to: 0 = by row count, else a fixed turq_mode
   int64_t launches = 0;
   std::string err;
 };

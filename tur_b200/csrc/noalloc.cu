@@ -9,8 +9,10 @@
 // call itself touches no allocator at all.
 //
 // The price: the array has a fixed size (TURQ_STATIC_SCRATCH_BYTES, resident on every GPU
-// that loads the library until the process exits), larger requests are refused with
-// TURQ_E_LIMIT, and all calls on one GPU share it - two calls whose kernels may overlap on
+// that loads the library until the process exits). Its tail holds the GEMV's hand-over
+// workspace for row-tiles cut between CTAs (about 1.2 MB on a 148-SM part), the rest - about
+// 2.8 MiB there - is what the activation planes of one call may use (roughly m * k * 1.2
+// bytes); larger requests are refused with TURQ_E_LIMIT. All calls on one GPU share it - two calls whose kernels may overlap on
 // the GPU (different streams) race on it and must be serialised by the caller.
 #include <cstdio>
 #include <mutex>
@@ -23,8 +25,8 @@ namespace {
 
 // Quantized activation planes of the call in flight, followed by the GEMV's workspace for
 // row-tiles split between CTAs. The planes need no clearing (every element read is written
-// first by the same call); the workspace's ready flags must start at zero and are cleared by
-// each call before its kernels run.
+// first by the same call), nor do the workspace's partial sums; its ready flags must start at
+// zero and are cleared by each call before its kernels run.
 static __device__ __align__(256) uint8_t g_static_scratch[TURQ_STATIC_SCRATCH_BYTES];
 
 constexpr int kMaxDevices = 64;
@@ -64,6 +66,7 @@ extern "C" int32_t turq_qmatmul_static(turq_ctx* ctx, const turq_qtensor* qt, co
   if (!ctx || !qt || !dev_x || !dev_y) return fail(ctx, TURQ_E_INVALID_ARG, "null argument");
   if (x_dtype != TURQ_F32 && x_dtype != TURQ_BF16) return fail(ctx, TURQ_E_DTYPE, "activations must be F32 or BF16");
   if (m <= 0) return fail(ctx, TURQ_E_SHAPE, "m must be positive");
+  if (m > INT32_MAX / 2) return fail(ctx, TURQ_E_SHAPE, "m is too large");
   if (qt->device != ctx->device || ctx->device < 0 || ctx->device >= kMaxDevices)
     return fail(ctx, TURQ_E_INVALID_ARG, "tensor and context must live on the same device");
   if ((uintptr_t)dev_x % 16 != 0 || (uintptr_t)dev_y % 4 != 0) return fail(ctx, TURQ_E_ALIGN, "dev_x must be 16-byte aligned");
@@ -72,10 +75,14 @@ extern "C" int32_t turq_qmatmul_static(turq_ctx* ctx, const turq_qtensor* qt, co
   const turq::ActPackPlan plan = turq::plan_act_pack(fmt, m, k);
   // the tail of the array is the GEMV's split row-tile workspace (partial sums + ready flags)
   const size_t ws_bytes = (turq::gemv_workspace_bytes(ctx->sm_count) + 255) & ~(size_t)255;
-  if (plan.total + ws_bytes > (size_t)TURQ_STATIC_SCRATCH_BYTES) {
-    char buf[200];
-    snprintf(buf, sizeof(buf), "m=%lld x k=%lld needs %zu bytes of activation planes, the static buffer holds %d",
-             (long long)m, (long long)k, plan.total, (int)TURQ_STATIC_SCRATCH_BYTES);
+  if (ws_bytes >= (size_t)TURQ_STATIC_SCRATCH_BYTES) return fail(ctx, TURQ_E_LIMIT, "this GPU's hand-over workspace alone exceeds the static buffer");
+  const size_t capacity = (size_t)TURQ_STATIC_SCRATCH_BYTES - ws_bytes;
+  if (plan.total > capacity) {
+    char buf[240];
+    snprintf(buf, sizeof(buf),
+             "m=%lld x k=%lld needs %zu bytes of activation planes, the static buffer has room for %zu (%d bytes minus "
+             "the %zu-byte hand-over workspace)",
+             (long long)m, (long long)k, plan.total, capacity, (int)TURQ_STATIC_SCRATCH_BYTES, ws_bytes);
     return fail(ctx, TURQ_E_LIMIT, buf);
   }
   uint8_t* scratch = nullptr;
@@ -86,7 +93,8 @@ extern "C" int32_t turq_qmatmul_static(turq_ctx* ctx, const turq_qtensor* qt, co
   uint8_t* ws = scratch + TURQ_STATIC_SCRATCH_BYTES - ws_bytes;
   // The ready flags must read zero at kernel start. A completed call leaves them zero, but the
   // array is shared and outlives failed calls, so they are cleared every time (stream-ordered).
-  if (e == cudaSuccess) e = cudaMemsetAsync(ws, 0, ws_bytes, s);
+  if (e == cudaSuccess)
+    e = cudaMemsetAsync(ws + turq::gemv_workspace_flags_offset(ctx->sm_count), 0, turq::gemv_workspace_flags_bytes(ctx->sm_count), s);
   if (e == cudaSuccess)
     e = turq::launch_gemv_int8(qt->dtype, qt->tiles, qt->n_rows, k, dev_x, x_dtype, scratch, m, dev_y, dev_bias, ws,
                                ctx->dev_status, ctx->sm_count, s, &launches);

@@ -30,7 +30,7 @@ cudaError_t launch_repack(int dtype, const uint8_t* dev_wire, uint8_t* dev_tiles
   if (total_words == 0) return cudaSuccess;
   int threads = 256;
   int64_t blocks = (total_words + threads - 1) / threads;
-  if (blocks > 148 * 64) blocks = 148 * 64;
+  if (blocks > (int64_t)device_sm_count() * 64) blocks = (int64_t)device_sm_count() * 64;
   repack_kernel<<<(unsigned)blocks, threads, 0, s>>>(dtype, dev_wire, reinterpret_cast<uint32_t*>(dev_tiles),
                                                       n_rows, ktiles, total_words);
   return cudaGetLastError();
@@ -55,7 +55,7 @@ cudaError_t launch_slice_cols(int dtype, const uint8_t* src_tiles, uint8_t* dst_
   if (total == 0) return cudaSuccess;
   int threads = 256;
   int64_t blocks = (total + threads - 1) / threads;
-  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (blocks > (int64_t)device_sm_count() * 32) blocks = (int64_t)device_sm_count() * 32;
   slice_cols_kernel<<<(unsigned)blocks, threads, 0, s>>>(reinterpret_cast<const uint4*>(src_tiles),
                                                           reinterpret_cast<uint4*>(dst_tiles), row_tiles,
                                                           src_ktiles, kt0, nkt, vec_per_tile);

@@ -5,7 +5,36 @@
 
 #include "layout.h"
 
+#include <atomic>
+#include <cstdlib>
+
 namespace turq {
+
+// Facts about the current CUDA device, looked up once per device (safe from any thread).
+int device_sm_count();
+int device_smem_optin();
+// Q8_K quantizer switches of this build: divisor | 0x100 (negative scale) | 0x200 (ties to even)
+int q8k_variant();
+
+// Tuning knobs read from the environment exist only in -DTURQ_TUNING builds: several of them
+// change how a sum is split (hence its last bits), which a shipped library must not allow.
+inline int tuning_env(const char* name, int dflt) {
+#ifdef TURQ_TUNING
+  const char* v = getenv(name);
+  return v ? atoi(v) : dflt;
+#else
+  (void)name;
+  return dflt;
+#endif
+}
+
+// "cudaFuncSetAttribute was applied on device d" for one kernel instantiation: a bit per
+// device, set after the call succeeded (the call is idempotent, so a race only repeats it).
+struct PerDeviceOnce {
+  std::atomic<unsigned long long> mask{0};
+  bool done(int dev) const { return dev >= 0 && dev < 64 && ((mask.load(std::memory_order_acquire) >> dev) & 1ull); }
+  void set(int dev) { if (dev >= 0 && dev < 64) mask.fetch_or(1ull << dev, std::memory_order_release); }
+};
 
 struct ActPackPlan {
   size_t off_qs, off_dsc, off_bs16, off_bs32, total;
@@ -39,13 +68,16 @@ cudaError_t launch_quantize_act_pack(int fmt, const void* x, int x_dtype, int64_
 // plan_act_pack(fmt, m, k).total bytes) with a preceding launch. `workspace` holds
 // gemv_workspace_bytes(sm_count) bytes, zero-initialised once; `status` is a device int.
 size_t gemv_workspace_bytes(int sms);
+size_t gemv_workspace_flags_offset(int sms);  // the ready flags inside the workspace: the only
+size_t gemv_workspace_flags_bytes(int sms);   // part that has to read zero when a launch starts
 bool gemv_int8_fuses_act(int dtype, int64_t m, int64_t k);
 cudaError_t launch_gemv_int8(int dtype, const uint8_t* tiles, int64_t n_rows, int64_t k, const void* x,
                              int x_dtype, uint8_t* act_scratch, int64_t m, float* y, const float* bias,
                              uint8_t* workspace, int* status, int sm_count, cudaStream_t s, int* launches);
 // The same for several weights of one in-feature count that share x: one launch over the
 // concatenated rows (q|k|v, gate|up) per weight type - and a single one for Q4_K or Q5_K parts
-// beside Q6_K parts at up to 8 rows - each part with its own output and bias.
+// beside Q6_K parts at up to 8 rows - each part with its own output and bias. x_remote: x is
+// mapped host memory; it is then read exactly once, by the quantization launch.
 struct GemvPart {
   const uint8_t* tiles;
   int64_t n_rows;
@@ -55,7 +87,7 @@ struct GemvPart {
 };
 cudaError_t launch_gemv_int8_multi(int dtype, const GemvPart* parts, int nparts, int64_t k, const void* x,
                                    int x_dtype, uint8_t* act_scratch, int64_t m, uint8_t* workspace, int* status,
-                                   int sm_count, cudaStream_t s, int* launches);
+                                   int sm_count, cudaStream_t s, int* launches, bool x_remote = false);
 // y[m, n] = x . dequant(W)^T with f32 FMAs on exact f32 weights.
 cudaError_t launch_gemv_f32(int dtype, const uint8_t* tiles, int64_t n_rows, int64_t k,
                             const void* x, int x_dtype, int64_t m, float* y, const float* bias,

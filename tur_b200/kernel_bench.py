@@ -17,25 +17,9 @@ import numpy as np
 import torch
 
 from . import GgmlDType, Mode, QMatMul, QTensor, context
-from .workloads import BLOCK, SEED
+from .workloads import BLOCK, SEED, random_blocks
 
 NAMES = {"Q8_0": 8, "Q4_K": 12, "Q5_K": 13, "Q6_K": 14}
-
-
-def random_blocks(dtype: int, n: int, k: int, seed: int, device) -> torch.Tensor:
-    """Valid wire blocks with plausible scales, generated on the GPU (timing input only)."""
-    be, bb = BLOCK[dtype]
-    g = torch.Generator(device=device).manual_seed(seed)
-    nb = n * (k // be)
-    raw = torch.randint(0, 256, (nb, bb), dtype=torch.uint8, device=device, generator=g)
-    scale = (torch.rand((nb,), device=device, generator=g) * 0.004 + 0.0005).to(torch.float16).view(torch.uint8).reshape(nb, 2)
-    if dtype == 14:
-        raw[:, 208:210] = scale
-    else:
-        raw[:, 0:2] = scale
-        if dtype in (12, 13):
-            raw[:, 2:4] = scale
-    return raw.reshape(-1)
 
 
 def main() -> None:

@@ -78,6 +78,15 @@ class _Context:
     def launch_count(self) -> int:
         return int(_lib.load().turq_ctx_launch_count(self.handle))
 
+    def reserve(self, max_m: int, max_k: int, max_n: int) -> None:
+        """Sizes the context's scratch for its largest call, so that no later call allocates
+        (required before capturing calls into a CUDA graph)."""
+        self.check(_lib.load().turq_ctx_reserve(self.handle, max_m, max_k, max_n))
+
+    def set_auto_policy(self, mode: "Mode") -> None:
+        """Pins what Mode.AUTO means on this context to one scheme for every row count."""
+        self.check(_lib.load().turq_ctx_set_auto_policy(self.handle, int(mode)))
+
 
 _contexts: dict[int, _Context] = {}
 
@@ -106,6 +115,17 @@ def new_context(device: int | torch.device | None = None) -> _Context:
 
 def _stream_ptr(device: int) -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _check_operand(t: torch.Tensor, what: str, device: int, dtypes: Sequence[torch.dtype]) -> None:
+    """The kernels dereference raw pointers on the weight's device: refuse, before any launch,
+    a tensor that lives elsewhere, has another element type or is not dense."""
+    if not t.is_cuda or t.device.index != device:
+        raise TurqError(1, f"{what} lives on {t.device}, the weight on cuda:{device}")
+    if t.dtype not in dtypes:
+        raise TurqError(3, f"{what} has dtype {t.dtype}, expected one of {[str(d) for d in dtypes]}")
+    if not t.is_contiguous():
+        raise TurqError(1, f"{what} must be contiguous")
 
 
 class QTensor:
@@ -236,6 +256,9 @@ class QMatMul:
         ctx = qt._ctx
         if not x.is_cuda:
             x2 = x.reshape(-1, k).to(torch.float32).contiguous()
+            if out is not None and (out.is_cuda or out.dtype != torch.float32 or not out.is_contiguous()
+                                    or out.numel() != x2.shape[0] * n):
+                raise TurqError(1, "out must be a contiguous f32 host tensor of m x n elements when x is a host tensor")
             y = out if out is not None else torch.empty((x2.shape[0], n), dtype=torch.float32, pin_memory=x2.is_pinned())
             b = bias.to(torch.float32).contiguous() if bias is not None else None
             ctx.check(lib.turq_qmatmul_host(ctx.handle, qt._h, ctypes.c_void_p(x2.data_ptr()), x2.shape[0],
@@ -246,7 +269,16 @@ class QMatMul:
             x = x.to(torch.float32)
         x2 = x.reshape(-1, k).contiguous()
         m = x2.shape[0]
-        y = out if out is not None else torch.empty((m, n), dtype=torch.float32, device=x.device)
+        _check_operand(x2, "x", ctx.device, (torch.float32, torch.bfloat16))
+        if bias is not None:
+            _check_operand(bias, "bias", ctx.device, (torch.float32,))
+            if bias.numel() != n:
+                raise TurqError(2, f"bias has {bias.numel()} elements, the weight {n} rows")
+        if out is not None:
+            _check_operand(out, "out", ctx.device, (torch.float32,))
+            if out.numel() != m * n:
+                raise TurqError(2, f"out has {out.numel()} elements, expected {m} x {n}")
+        y = out if out is not None else torch.empty((m, n), dtype=torch.float32, device=qt.device())
         ctx.check(lib.turq_qmatmul(ctx.handle, qt._h, ctypes.c_void_p(x2.data_ptr()), int(_TORCH_TO_GGML[x2.dtype]), m,
                                    ctypes.c_void_p(y.data_ptr()), int(mode),
                                    ctypes.c_void_p(bias.data_ptr()) if bias is not None else None,
@@ -259,26 +291,51 @@ class QMatMul:
     def forward_multi(mms: Sequence["QMatMul"], x: torch.Tensor, biases: Optional[Sequence[Optional[torch.Tensor]]] = None,
                       mode: Mode = Mode.AUTO, outs: Optional[Sequence[torch.Tensor]] = None) -> list[torch.Tensor]:
         """Linears that read the same x (q|k|v, gate|up) in one call: weights of one type run
-        as a single kernel launch over their concatenated rows. x is a CUDA tensor [..., k]."""
+        as a single kernel launch over their concatenated rows. x [..., k] is a CUDA tensor, or a
+        host tensor (then the call makes one round trip for all the weights)."""
         lib = _lib.load()
         n = len(mms)
         ctx = mms[0].qtensor._ctx
         k = mms[0].qtensor.shape()[1]
+        arr = ctypes.c_void_p * n
+        qts = arr(*[mm.qtensor._h for mm in mms])
+        lead = tuple(x.shape[:-1])
         if not x.is_cuda:
-            raise TurqError(8, "forward_multi needs a CUDA tensor")
+            # host tensors: one round trip for all the weights (turq_qmatmul_multi_host)
+            x2 = x.reshape(-1, k).to(torch.float32).contiguous()
+            m = x2.shape[0]
+            if outs is None:
+                outs = [torch.empty((m, mm.qtensor.shape()[0]), dtype=torch.float32, pin_memory=x2.is_pinned()) for mm in mms]
+            for o, mm in zip(outs, mms):
+                if o.is_cuda or o.dtype != torch.float32 or not o.is_contiguous() or o.numel() != m * mm.qtensor.shape()[0]:
+                    raise TurqError(1, "outs must be contiguous f32 host tensors of m x n elements when x is a host tensor")
+            ys = arr(*[ctypes.c_void_p(o.data_ptr()) for o in outs])
+            bs, keep = None, []
+            if biases is not None:
+                keep = [b.to(torch.float32).contiguous() if b is not None else None for b in biases]
+                bs = arr(*[ctypes.c_void_p(b.data_ptr()) if b is not None else None for b in keep])
+            ctx.check(lib.turq_qmatmul_multi_host(ctx.handle, n, qts, ctypes.c_void_p(x2.data_ptr()), m, ys, int(mode), bs))
+            return [o.reshape(*lead, o.shape[-1]) for o in outs]
         if x.dtype not in (torch.float32, torch.bfloat16):
             x = x.to(torch.float32)
         x2 = x.reshape(-1, k).contiguous()
         m = x2.shape[0]
+        _check_operand(x2, "x", ctx.device, (torch.float32, torch.bfloat16))
         if outs is None:
-            outs = [torch.empty((m, mm.qtensor.shape()[0]), dtype=torch.float32, device=x.device) for mm in mms]
-        arr = ctypes.c_void_p * n
-        qts = arr(*[mm.qtensor._h for mm in mms])
+            outs = [torch.empty((m, mm.qtensor.shape()[0]), dtype=torch.float32, device=ctx.device) for mm in mms]
+        for i, (o, mm) in enumerate(zip(outs, mms)):
+            _check_operand(o, f"outs[{i}]", ctx.device, (torch.float32,))
+            if o.numel() != m * mm.qtensor.shape()[0]:
+                raise TurqError(2, f"outs[{i}] has {o.numel()} elements, expected {m} x {mm.qtensor.shape()[0]}")
         ys = arr(*[ctypes.c_void_p(o.data_ptr()) for o in outs])
         bs = None
         if biases is not None:
+            for i, (b, mm) in enumerate(zip(biases, mms)):
+                if b is not None:
+                    _check_operand(b, f"biases[{i}]", ctx.device, (torch.float32,))
+                    if b.numel() != mm.qtensor.shape()[0]:
+                        raise TurqError(2, f"biases[{i}] has {b.numel()} elements, the weight {mm.qtensor.shape()[0]} rows")
             bs = arr(*[ctypes.c_void_p(b.data_ptr()) if b is not None else None for b in biases])
         ctx.check(lib.turq_qmatmul_multi(ctx.handle, n, qts, ctypes.c_void_p(x2.data_ptr()), int(_TORCH_TO_GGML[x2.dtype]), m,
                                          ys, int(mode), bs, _stream_ptr(ctx.device)))
-        lead = tuple(x.shape[:-1])
         return [o.reshape(*lead, o.shape[-1]) for o in outs]

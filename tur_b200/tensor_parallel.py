@@ -41,6 +41,7 @@ class Shard:
     rows: tuple[int, int]   # (row0, count)
     cols: tuple[int, int]   # (col0, count)
     parallel: str           # "column" | "row"
+    unit: int = 16          # granule the split was made in (rows for "column", columns for "row")
 
     @property
     def shape(self) -> tuple[int, int]:
@@ -55,13 +56,13 @@ def shard_of(w: Weight, tp: int, rank: int, row_unit: int = 16) -> Shard:
         if w.n % row_unit:
             raise ValueError(f"{w.name}: {w.n} rows are not a multiple of the split unit {row_unit}")
         s, c = split_units(w.n // row_unit, tp)[rank]
-        return Shard((s * row_unit, c * row_unit), (0, w.k), "column")
+        return Shard((s * row_unit, c * row_unit), (0, w.k), "column", row_unit)
     be = BLOCK[w.dtype][0]
     unit = max(be, row_unit if row_unit % be == 0 else be)
     if w.k % unit:
         raise ValueError(f"{w.name}: {w.k} columns are not a multiple of the split unit {unit}")
     s, c = split_units(w.k // unit, tp)[rank]
-    return Shard((0, w.n), (s * unit, c * unit), "row")
+    return Shard((0, w.n), (s * unit, c * unit), "row", unit)
 
 
 def shard_blocks(blocks, w: Weight, sh: Shard):
@@ -96,10 +97,9 @@ class TPLinear:
                 dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
             return y
         if self.gather_output and dist.is_initialized() and dist.get_world_size(self.group) > 1:
-            return gather_columns(y, self.w.n, dist.get_world_size(self.group), self.shard_unit, self.group)
+            return gather_columns(y, self.w.n, dist.get_world_size(self.group), self.shard.unit, self.group)
         return y
 
-    shard_unit = 16
     __call__ = forward
 
 

@@ -75,3 +75,21 @@ WORKLOADS = {
     "cfg4-q8": _mk("cfg4-q8", "3B dense decoder linear stack, Q8_0", 2560, 2560, 640, 8192, 40, Q8_0, Q8_0),
     "cfg5": _mk("cfg5", "Qwen3-32B linear stack, Q4_K_M (+ Q6_K lm_head)", 5120, 8192, 1024, 25600, 64, Q4_K, Q6_K, 151936),
 }
+
+
+def random_blocks(dtype: int, n: int, k: int, seed: int, device):
+    """Valid wire blocks with plausible scales, generated on the GPU as a flat uint8 tensor.
+    Timing input only: the quantized values are uniform bytes, not a quantized Gaussian."""
+    import torch
+    be, bb = BLOCK[dtype]
+    g = torch.Generator(device=device).manual_seed(seed)
+    nb = n * (k // be)
+    raw = torch.randint(0, 256, (nb, bb), dtype=torch.uint8, device=device, generator=g)
+    scale = (torch.rand((nb,), device=device, generator=g) * 0.004 + 0.0005).to(torch.float16).view(torch.uint8).reshape(nb, 2)
+    if dtype == Q6_K:
+        raw[:, 208:210] = scale
+    else:
+        raw[:, 0:2] = scale
+        if dtype in (Q4_K, Q5_K):
+            raw[:, 2:4] = scale
+    return raw.reshape(-1)
