@@ -455,6 +455,17 @@ def run_gpu(args):
     if rank == 0 and args.workload == "cfg2" and m == 1 and not args.no_extras:
         extras = run_extras(stack, dev, ctx, peak, tpeak, local)
 
+    pass_bytes, pass_flops = stack.pass_bytes(), stack.pass_flops(m)
+    head_w = stack.head[0] if stack.head else None
+
+    # ---- the sharded workload (cfg5) at this rank count: every rank takes part
+    tp_obj = None
+    if world > 1 and args.workload == "cfg2" and m == 1 and not args.no_extras:
+        del graph, dg
+        stack.layers, stack.head = [], None
+        torch.cuda.empty_cache()
+        tp_obj = tp_measure(WORKLOADS["cfg5"], dev, ctx, rank, world, [(1, "INT8_ACT", "f32"), (64, "AUTO", "f32")], steps=10)
+
     # ---- reduce over ranks
     if world > 1:
         t = torch.tensor([ms, e2e_ms or 0.0], device=dev)
@@ -465,15 +476,13 @@ def run_gpu(args):
             dist.destroy_process_group()
         return
 
-    pass_bytes = stack.pass_bytes()
-    pass_flops = stack.pass_flops(m)
     total_bytes = pass_bytes * world
     value = total_bytes * args.steps / (ms * 1e-3) / 1e9
     achieved = alg_bytes / (dom_us * 1e-6) / 1e9
     traffic = NCU_TRAFFIC_BYTES.get((tuple(w.name for w in dom_ws), wl.name, m))
     grp_x = [max(w.k for w in wl.per_layer if w.name in g) for g in GROUPS]
-    h2d = m * 4 * (sum(grp_x) * wl.layers + (stack.head[0].k if stack.head else 0))
-    d2h = sum(m * w.n * 4 for w in wl.per_layer) * wl.layers + (m * stack.head[0].n * 4 if stack.head else 0)
+    h2d = m * 4 * (sum(grp_x) * wl.layers + (head_w.k if head_w else 0))
+    d2h = sum(m * w.n * 4 for w in wl.per_layer) * wl.layers + (m * head_w.n * 4 if head_w else 0)
     members = " | ".join(f"{w.name} {TYPE_NAMES[w.dtype]} {w.n}x{w.k}" for w in dom_ws)
     if tensor_path and m > 64:
         # prefill runs the tcgen05 GEMM: bound by the tensor cores (decode batches of up to 64 rows
@@ -497,7 +506,7 @@ def run_gpu(args):
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": ("f16" if tensor_path else "int8" if mode in (Mode.INT8_ACT, Mode.AUTO) else "f32"), "data": "synthetic",
         "config": {
-            "workload": workload_text(wl, m, stack.head is not None),
+            "workload": workload_text(wl, m, head_w is not None),
             "mode": mode.name, "x_dtype": args.xdtype, "weight_bytes_per_step_per_gpu": pass_bytes,
             "tflops": pass_flops * world * args.steps / (ms * 1e-3) / 1e12, "parallelism": f"replicas x{world}",
             "l2": "weights per pass exceed L2 (distinct buffers per layer); CUDA-graph replay per step",
@@ -517,6 +526,8 @@ def run_gpu(args):
     if parity is not None:
         line["parity"] = parity
     line.update(extras)
+    if tp_obj is not None:
+        line["tp"] = tp_obj
     if not args.no_cpu and world == 1:
         gbs, cores, sample, _, _ = cpu_scheme_timing(wl, m, steps=args.cpu_steps)
         line["cpu_baseline"] = {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
@@ -583,14 +594,206 @@ def run_extras(stack, dev, ctx, peak, tpeak, local):
     return out
 
 
-def run_gpu_tp(args):
-    """Tensor-parallel pass of a sharded workload (cfg5): q/k/v/gate/up and the head split by
-    rows, o/down by columns with an NCCL all-reduce after each, all-gather of the logits.
-    Strong scaling: the model is fixed, every rank streams 1/N of it."""
+class TPStack:
+    """A workload's linears sharded Megatron-style over `world` ranks (this rank's shards only):
+    attn_q|k|v by whole heads, ffn_gate|up in 256-row units and the head in 16-row units (rows:
+    contiguous bytes), attn_output / ffn_down by whole blocks of columns. Weights are valid random
+    blocks generated on the GPU, the same on every rank, sharded as bytes."""
+
+    def __init__(self, wl, dev, rank, world, head=True, head_dim=128, layers=None):
+        import torch
+        from tur_b200 import GgmlDType, QMatMul, QTensor
+        from tur_b200.tensor_parallel import row_unit_for, shard_blocks, shard_of, split_units
+        from tur_b200.workloads import random_blocks
+        self.wl, self.dev, self.rank, self.world = wl, dev, rank, world
+        self.n_layers = layers or wl.layers
+
+        def make(w, seed):
+            sh = shard_of(w, world, rank, row_unit_for(w, head_dim))
+            return sh, shard_blocks(random_blocks(w.dtype, w.n, w.k, seed, dev), w, sh).reshape(-1)
+
+        protos = [(w,) + make(w, SEED + i) for i, w in enumerate(wl.per_layer)]
+        self.layers = [[(w, sh, QMatMul.from_arc(QTensor.new(b, GgmlDType(w.dtype), sh.shape))) for w, sh, b in protos]
+                       for _ in range(self.n_layers)]
+        self.head = None
+        if wl.head is not None and head:
+            sh, b = make(wl.head, SEED + 999)
+            self.head = (wl.head, sh, QMatMul.from_arc(QTensor.new(b, GgmlDType(wl.head.dtype), sh.shape)))
+            self.head_widths = [c * 16 for _, c in split_units(wl.head.n // 16, world)]
+        del protos
+        torch.cuda.synchronize()
+
+    def exchange_bytes(self, m):
+        """Largest tensor any exchange of a pass moves (per rank for the gather)."""
+        big = max(m * w.n * 4 for w, sh, _ in self.layers[0] if sh.parallel == "row")
+        if self.head:
+            big = max(big, m * max(self.head_widths) * 4)
+        return big
+
+    def buffers(self, m, xdtype="f32"):
+        import torch
+        xs, ys = {}, {}
+        for w, sh, _ in self.layers[0]:
+            kloc = sh.shape[1]
+            if (w.source, kloc) not in xs:
+                x = torch.from_numpy(gen_activations(m, kloc, SEED + 10**6 + m + len(xs))).to(self.dev)
+                xs[(w.source, kloc)] = x.to(torch.bfloat16) if xdtype == "bf16" else x
+            # row-parallel outputs are full width (summed over the ranks), column-parallel ones this rank's share
+            ys[w.name] = torch.empty((m, sh.shape[0]), dtype=torch.float32, device=self.dev)
+        if self.head:
+            ys["output_local"] = torch.empty((m, self.head[1].shape[0]), dtype=torch.float32, device=self.dev)
+            ys["output"] = torch.empty((m, self.wl.head.n), dtype=torch.float32, device=self.dev)
+        return xs, ys
+
+    def make_pass(self, xs, ys, mode, group=None):
+        """group = a TPGroup: exchanges by the library's own kernels (graph-capturable);
+        None: NCCL all-reduce / all-gather through torch.distributed (eager only)."""
+        import torch.distributed as dist
+        from tur_b200 import QMatMul
+        from tur_b200.tensor_parallel import gather_columns
+        world, wl = self.world, self.wl
+
+        def run():
+            for layer in self.layers:
+                by_name = {w.name: (w, sh, mm) for w, sh, mm in layer}
+                for grp in GROUPS:
+                    same = [by_name[n] for n in grp]
+                    w0, sh0, mm0 = same[0]
+                    x = xs[(w0.source, sh0.shape[1])]
+                    if len(same) > 1:
+                        QMatMul.forward_multi([mm for _, _, mm in same], x, mode=mode, outs=[ys[w.name] for w, _, _ in same])
+                    elif sh0.parallel == "row" and world > 1 and group is not None:
+                        group.qmatmul_rowparallel(mm0, x, mode=mode, out=ys[w0.name])
+                    else:
+                        y = mm0.forward(x, mode=mode, out=ys[w0.name])
+                        if sh0.parallel == "row" and world > 1:
+                            dist.all_reduce(y)
+            if self.head:
+                y = self.head[2].forward(xs[("hidden", wl.hidden)], mode=mode, out=ys["output_local"])
+                if world > 1 and group is not None:
+                    group.allgather(y, self.head_widths, out=ys["output"])
+                elif world > 1:
+                    gather_columns(y, wl.head.n, world, 16)
+        return run
+
+    def collectives_per_pass(self):
+        return sum(1 for w, sh, _ in self.layers[0] if sh.parallel == "row") * self.n_layers + (1 if self.head else 0)
+
+
+def timed_max_over_ranks(fn, steps, dev, world):
+    """`steps` calls of fn between barriers, device-timed, maximum over the ranks (ms per call)."""
     import torch
     import torch.distributed as dist
-    from tur_b200 import GgmlDType, Mode, QMatMul, QTensor, context
-    from tur_b200.tensor_parallel import TPLinear, gather_columns, row_unit_for, shard_blocks, shard_of
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.barrier()
+    return float(t[0])
+
+
+def tp_parity(stack, group, dev, ctx, m=4):
+    """Sharded against unsharded on real ranks, layer 0's ffn_gate (column-parallel: gathered
+    shares must equal the unsharded product bit for bit) and ffn_down (row-parallel: summed
+    partial products within f32 reassociation)."""
+    import torch
+    from tur_b200 import GgmlDType, Mode, QMatMul, QTensor
+    from tur_b200.tensor_parallel import split_units
+    from tur_b200.workloads import random_blocks
+    out = {}
+    for i, (w, sh, mm) in enumerate(stack.layers[0]):
+        if w.name not in ("ffn_gate", "ffn_down"):
+            continue
+        full = QMatMul.from_arc(QTensor.new(random_blocks(w.dtype, w.n, w.k, SEED + i, dev), GgmlDType(w.dtype), (w.n, w.k)))
+        x = torch.from_numpy(gen_activations(m, w.k, SEED + 31 + i)).to(dev)
+        ref = full.forward(x, mode=Mode.INT8_ACT)
+        if sh.parallel == "column":
+            widths = [c * sh.unit for _, c in split_units(w.n // sh.unit, stack.world)]
+            got = group.allgather(mm.forward(x, mode=Mode.INT8_ACT), widths)
+            out["column_parallel_bit_exact"] = bool(torch.equal(got, ref))
+        else:
+            xl = x[:, sh.cols[0]: sh.cols[0] + sh.cols[1]].contiguous()
+            got = group.qmatmul_rowparallel(mm, xl, mode=Mode.INT8_ACT)
+            out["row_parallel_rel_fro"] = float((got - ref).norm() / ref.norm())
+        del full
+    ctx.poll_status()
+    torch.cuda.empty_cache()
+    return out
+
+
+def tp_measure(wl, dev, ctx, rank, world, rows_modes, steps, head=True, own=True, one_gpu=True):
+    """Strong scaling of one sharded pass: ms per pass at `world` ranks (CUDA-graph replay with the
+    library's own exchange kernels when own=True, eager launches with NCCL collectives otherwise)
+    and, measured by rank 0 alone in the same run, the unsharded pass on one GPU."""
+    import torch
+    import torch.distributed as dist
+    from tur_b200 import Mode
+    from tur_b200.tensor_parallel import TPGroup
+    stack = TPStack(wl, dev, rank, world, head=head)
+    group = None
+    points, parity = [], None
+    if own and world > 1:
+        group = TPGroup(rank, world, max(stack.exchange_bytes(max(r for r, _, _ in rows_modes)), 4 * 25600 * 4), ctx=ctx)
+        parity = tp_parity(stack, group, dev, ctx)
+    for rows, mode_name, xdtype in rows_modes:
+        mode = Mode[mode_name]
+        xs, ys = stack.buffers(rows, xdtype)
+        fn = stack.make_pass(xs, ys, mode, group)
+        launches = None
+        if own or world == 1:
+            g, launches = graph_of(fn, dev, ctx)
+            runner = g.replay
+        else:
+            for _ in range(3):
+                fn()
+            runner = fn
+        ms = timed_max_over_ranks(runner, steps, dev, world)
+        ctx.poll_status()
+        points.append({"rows": rows, "mode": mode_name, "x_dtype": xdtype, "ms_per_step": ms, "launches_per_pass": launches,
+                       "cuda_graph": bool(own or world == 1)})
+        del xs, ys, fn, runner
+    total_bytes = wl.layers * wl.layer_bytes() + (wl.head.nbytes if stack.head else 0)
+    collectives = stack.collectives_per_pass()
+    del stack
+    torch.cuda.empty_cache()
+    if one_gpu and world > 1:
+        # the same pass, unsharded, on rank 0's GPU while the other ranks wait at the barrier
+        if rank == 0:
+            solo = TPStack(wl, dev, 0, 1, head=head)
+            for pt, (rows, mode_name, xdtype) in zip(points, rows_modes):
+                xs, ys = solo.buffers(rows, xdtype)
+                g, _ = graph_of(solo.make_pass(xs, ys, Mode[mode_name], None), dev, ctx)
+                pt["ms_per_step_1gpu"] = time_replays(g, max(3, steps // 2))
+                pt["speedup_vs_1gpu"] = pt["ms_per_step_1gpu"] / pt["ms_per_step"]
+                pt["strong_scaling_efficiency"] = pt["speedup_vs_1gpu"] / world
+                del g, xs, ys
+            del solo
+            torch.cuda.empty_cache()
+        dist.barrier()
+    for pt in points:
+        pt["weight_gbs_aggregate"] = total_bytes / (pt["ms_per_step"] * 1e-3) / 1e9
+    return {"workload": f"{wl.name}: {wl.description}, tensor-parallel x{world}" + (" + lm_head" if head else ""),
+            "weights": "valid random blocks generated on the GPU, sharded as bytes",
+            "exchange": ("own kernels over peer memory (turq_tp_*): all-reduce fused behind attn_output and ffn_down, "
+                         "all-gather behind the head; no NCCL call inside the pass") if own else
+                        "NCCL all-reduce after attn_output and ffn_down, all-gather after the head (eager launches)",
+            "collectives_per_pass": collectives, "weight_bytes_total": total_bytes, "parity": parity, "points": points}
+
+
+def run_gpu_tp(args):
+    """Tensor-parallel pass of a sharded workload (cfg5) as the whole job: strong scaling, the
+    model is fixed and every rank streams 1/N of it."""
+    import torch
+    import torch.distributed as dist
+    from tur_b200 import Mode, context
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -603,128 +806,32 @@ def run_gpu_tp(args):
     m = args.m
     mode = Mode[args.mode]
     ctx = context(local)
-    head_dim = 128
-
-    from tur_b200.workloads import random_blocks
-
-    def make(w, seed):
-        # random valid blocks generated on the GPU (same on every rank), sharded as bytes:
-        # the host quantizer would take minutes for these shapes and the timing only sees bytes
-        sh = shard_of(w, world, rank, row_unit_for(w, head_dim))
-        return sh, shard_blocks(random_blocks(w.dtype, w.n, w.k, seed, dev), w, sh).reshape(-1)
-
-    protos = [(w,) + make(w, SEED + i) for i, w in enumerate(wl.per_layer)]
-    layers = []
-    for _ in range(wl.layers):
-        layer = []
-        for w, sh, b in protos:
-            mm = QMatMul.from_arc(QTensor.new(b, GgmlDType(w.dtype), sh.shape))
-            layer.append((w, sh, TPLinear(w, sh, mm)))
-        layers.append(layer)
-    head = None
-    if wl.head is not None and not args.no_head:
-        sh, b = make(wl.head, SEED + 999)
-        head = (wl.head, sh, QMatMul.from_arc(QTensor.new(b, GgmlDType(wl.head.dtype), sh.shape)))
-    del protos
-    torch.cuda.synchronize()
-
-    # synthetic activations: full hidden state (replicated), this rank's slice of the
-    # attention output / MLP intermediate (they come from sharded heads / gate*up)
-    xs, ys = {}, {}
-    for w, sh, _ in layers[0]:
-        kloc = sh.shape[1]
-        if (w.source, kloc) not in xs:
-            x = torch.from_numpy(gen_activations(m, kloc, SEED + 10**6 + m + len(xs))).to(dev)
-            xs[(w.source, kloc)] = x.to(torch.bfloat16) if args.xdtype == "bf16" else x
-        ys[w.name] = torch.empty((m, sh.shape[0]), dtype=torch.float32, device=dev)
-    if head:
-        ys["output"] = torch.empty((m, head[1].shape[0]), dtype=torch.float32, device=dev)
-
-    groups = [["attn_q", "attn_k", "attn_v"], ["attn_output"], ["ffn_gate", "ffn_up"], ["ffn_down"]]
-
-    def one_pass():
-        for layer in layers:
-            by_name = {w.name: (w, sh, lin) for w, sh, lin in layer}
-            for grp in groups:
-                same = [by_name[n] for n in grp]
-                w0, sh0, _ = same[0]
-                if len(same) > 1:
-                    QMatMul.forward_multi([lin.matmul for _, _, lin in same], xs[(w0.source, sh0.shape[1])], mode=mode,
-                                          outs=[ys[w.name] for w, _, _ in same])
-                else:
-                    y = same[0][2].matmul.forward(xs[(w0.source, sh0.shape[1])], mode=mode, out=ys[w0.name])
-                    if sh0.parallel == "row" and world > 1:
-                        dist.all_reduce(y)
-        if head:
-            y = head[2].forward(xs[("hidden", wl.hidden)], mode=mode, out=ys["output"])
-            if world > 1:
-                gather_columns(y, wl.head.n, world, 16)
-
-    for _ in range(max(3, args.warmup)):
-        one_pass()
-    torch.cuda.synchronize()
-    l0 = ctx.launch_count()
-    runner, graphed = one_pass, False
-    try:
-        # NCCL collectives are never captured into the graph: beyond one rank the pass is
-        # launched eagerly
-        if args.no_graph or world > 1:
-            raise RuntimeError("graph capture disabled")
-        graph = torch.cuda.CUDAGraph()
-        side = torch.cuda.Stream(dev)
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side), torch.cuda.graph(graph, stream=side):
-            one_pass()
-        runner, graphed = graph.replay, True
-    except Exception:
-        torch.cuda.synchronize()
-    launches_per_step = (ctx.launch_count() - l0) if graphed else None
-    if not graphed:
-        l0 = ctx.launch_count()
-        one_pass()
-        launches_per_step = ctx.launch_count() - l0
-    for _ in range(3):
-        runner()
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
     sampler = ClockSampler(local)
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with sampler:
-        e0.record()
-        for _ in range(args.steps):
-            runner()
-        e1.record()
-        torch.cuda.synchronize()
-    barrier()
-    ms = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t[0])
+        obj = tp_measure(wl, dev, ctx, rank, world, [(m, args.mode, args.xdtype)], args.steps, head=not args.no_head,
+                         own=not args.nccl, one_gpu=not args.no_extras)
     if rank == 0:
-        total_bytes = wl.layers * wl.layer_bytes() + (wl.head.nbytes if head else 0)
-        pass_flops = m * (wl.layers * sum(2 * w.n * w.k for w in wl.per_layer) + (2 * wl.head.n * wl.head.k if head else 0))
+        pt = obj["points"][0]
+        ms = pt["ms_per_step"]
+        total_bytes = obj["weight_bytes_total"]
+        pass_flops = m * (wl.layers * sum(2 * w.n * w.k for w in wl.per_layer) + (0 if args.no_head else 2 * wl.head.n * wl.head.k))
         peak, peak_kind = measured_peaks()
-        value = total_bytes * args.steps / (ms * 1e-3) / 1e9
+        value = total_bytes / (ms * 1e-3) / 1e9
+        tensor_path = mode == Mode.TENSOR_CORE or (mode == Mode.AUTO and m > 16)
         print(json.dumps({
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "int8" if mode in (Mode.INT8_ACT, Mode.AUTO) else "f16", "data": "synthetic",
-            "config": {"workload": f"{wl.name}: {wl.description}, M={m}, tensor-parallel x{world}", "mode": mode.name,
-                       "x_dtype": args.xdtype, "lm_head": bool(head), "tflops": pass_flops * args.steps / (ms * 1e-3) / 1e12,
-                       "parallelism": f"tp{world}", "cuda_graph": graphed,
-                       "collectives": "NCCL all-reduce after attn_output and ffn_down, all-gather after the head",
-                       "weights": "random valid blocks generated on the GPU, sharded as bytes",
-                       "weight_bytes_total": total_bytes, "tokens_per_s": m * args.steps / (ms * 1e-3)},
-            "e2e": None, "gpu_launches": launches_per_step * args.steps, "clocks": sampler.summary(),
+            "warmup": 3, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16" if tensor_path else "int8", "data": "synthetic",
+            "config": {"workload": obj["workload"] + f", M={m}", "mode": mode.name,
+                       "x_dtype": args.xdtype, "tflops": pass_flops / (ms * 1e-3) / 1e12,
+                       "parallelism": f"tp{world}", "cuda_graph": pt["cuda_graph"], "exchange": obj["exchange"],
+                       "collectives_per_pass": obj["collectives_per_pass"], "weights": obj["weights"],
+                       "weight_bytes_total": total_bytes, "tokens_per_s": m / (ms * 1e-3)},
+            "e2e": None, "gpu_launches": (pt["launches_per_pass"] or 0) * args.steps, "clocks": sampler.summary(),
+            "tp": obj,
             "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                          "frac": value / world / peak, "traffic": None,
-                         "kernel": "whole sharded pass per GPU (GEMV kernels + NCCL collectives)"},
+                         "kernel": "whole sharded pass per GPU (GEMV / GEMM kernels + exchanges)"},
         }))
     if world > 1:
         dist.destroy_process_group()
@@ -745,7 +852,8 @@ def main():
     ap.add_argument("--no-multi", action="store_true", help="one launch per weight (no q|k, gate|up multi-weight launches)")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of the timed pass's outputs")
     ap.add_argument("--no-extras", action="store_true", help="skip the sweep / prefill / other-config objects of the default run")
-    ap.add_argument("--no-graph", action="store_true", help="tensor-parallel arm: launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--nccl", action="store_true", help="tensor-parallel arm: NCCL collectives and eager launches instead of the "
+                                                      "library's own exchange kernels in a CUDA graph (prefill-sized exchanges)")
     ap.add_argument("--xdtype", default="f32", choices=["f32", "bf16"], help="activation dtype on the device (prefill configs use bf16)")
     ap.add_argument("--no-head", action="store_true", help="leave the lm_head out of the pass (prefill evaluates it for one token only)")
     ap.add_argument("--no-e2e", action="store_true")

@@ -200,6 +200,53 @@ int32_t turq_qmatmul_static(turq_ctx* ctx, const turq_qtensor* qt, const void* d
                             int32_t x_dtype, int64_t m, float* dev_y, const float* dev_bias,
                             void* stream);
 
+/* ---- Tensor parallelism inside one node (no counterpart in the reference, which is
+ * single-device: src/models/layers/norm.rs:50 passes Shard::default() everywhere).
+ *
+ * One process per GPU. Every rank creates a group handle, exports an opaque blob, the host
+ * exchanges the blobs by whatever channel it has (the ranks' process group, a pipe, a file) and
+ * hands all of them, in rank order, to turq_tp_connect. After that the row-parallel linears
+ * (attn_output, ffn_down: each rank holds a range of input columns) and the gathers behind
+ * column-parallel ones (the vocabulary-sharded head) exchange their data with kernels of this
+ * library over peer memory (NVLink): plain peer loads in rank order, so sums are deterministic,
+ * and no NCCL call, so a whole sharded decode pass can be captured in one CUDA graph.
+ *
+ * All ranks must issue the same sequence of group calls with the same sizes. A peer that does
+ * not arrive within the wait limit makes the kernel give up: the exchange is skipped, the
+ * context's status word becomes TURQ_E_TIMEOUT (turq_ctx_poll_status) and the group is out of
+ * step until every rank has called turq_tp_reset. max_bytes is the largest m * n * 4 of any
+ * exchanged tensor (per rank for gathers); the group holds twice that on the device. */
+typedef struct turq_tp turq_tp;
+#define TURQ_TP_HANDLE_BYTES 64
+int32_t turq_tp_create(turq_ctx* ctx, int32_t rank, int32_t world, size_t max_bytes, turq_tp** out);
+int32_t turq_tp_export(const turq_tp* tp, void* handle_out /* TURQ_TP_HANDLE_BYTES */);
+int32_t turq_tp_connect(turq_tp* tp, const void* handles /* world * TURQ_TP_HANDLE_BYTES, rank order */);
+int32_t turq_tp_destroy(turq_tp* tp);
+/* Upper bound of every device-side wait for a peer, in SM clock cycles (default 2e9, about 1 s). */
+int32_t turq_tp_set_wait_limit(turq_tp* tp, int64_t cycles);
+/* Clears this rank's flags and call counter. Collective in effect: call it on every rank, with
+ * no group call in flight (the host synchronizes the ranks around it). */
+int32_t turq_tp_reset(turq_tp* tp);
+/* dev_out[i] = sum over ranks of dev_in[i], i < count, added in rank order on every rank. */
+int32_t turq_tp_allreduce(turq_tp* tp, const float* dev_in, float* dev_out, int64_t count, void* stream);
+/* dev_out[r, col0(p) + j] = rank p's dev_in[r, j]: rank p contributes [m, widths[p]], the result
+ * is [m, sum(widths)] on every rank. */
+int32_t turq_tp_allgather(turq_tp* tp, const float* dev_in, int64_t m, const int64_t* widths, float* dev_out,
+                          void* stream);
+/* Row-parallel LinearX::forward: qt holds this rank's range of input columns, dev_x the matching
+ * activation columns [m, n_cols of the shard]; dev_y [m, n_rows] receives the sum over the ranks
+ * (+ bias) on every rank. In the integer scheme the GEMV's epilogue writes its partial result
+ * straight into the exchange memory; one small kernel then signals, waits and adds. */
+int32_t turq_qmatmul_rowparallel(turq_tp* tp, const turq_qtensor* qt, const void* dev_x, int32_t x_dtype,
+                                 int64_t m, float* dev_y, int32_t mode, const float* dev_bias, void* stream);
+/* Test support on a single GPU: connects the group to local stand-ins for the other ranks, which
+ * never signal by themselves (a call then runs into its wait limit), and lets the host play a
+ * peer's part for the next call: its data (count floats, may be NULL / 0) and, with signal != 0,
+ * its "ready" flags. */
+int32_t turq_tp_connect_loopback(turq_tp* tp);
+int32_t turq_tp_loopback_fill(turq_tp* tp, int32_t peer, const float* dev_src, int64_t count, int32_t signal,
+                              void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,110 @@
+"""The library's own tensor-parallel exchange (turq_tp_*) on ONE GPU: the other ranks are local
+stand-ins whose part the host plays between calls, so no kernel ever waits for another kernel.
+Checks the arithmetic and order of the reduction, the slot alternation over consecutive calls,
+the fused row-parallel GEMV, graph replay, and that a peer that never arrives ends the wait with
+TURQ_E_TIMEOUT while the context stays usable. Real multi-GPU runs are in test_tp_multi_gpu.py."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+SEED = 299792458
+
+
+@pytest.fixture(scope="module")
+def tq():
+    from tur_b200 import quantized
+    assert torch.cuda.is_available()
+    return quantized
+
+
+def test_single_rank_group_is_the_plain_matmul_and_replays_in_a_graph(tq):
+    from tur_b200.tensor_parallel import TPGroup
+    n, k, m = 320, 1024, 3
+    rng = np.random.default_rng(SEED)
+    w = oracle.quantize(oracle.Q4_K, (rng.standard_normal((n, k)) * 0.02).astype(np.float32))
+    mm = tq.QMatMul.from_arc(tq.QTensor.new(w, tq.GgmlDType.Q4K, (n, k)))
+    x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).cuda()
+    bias = torch.from_numpy(rng.standard_normal(n).astype(np.float32)).cuda()
+    g = TPGroup(0, 1, m * n * 4)
+    want = mm.forward(x, bias=bias, mode=tq.Mode.INT8_ACT)
+    for _ in range(3):                                       # consecutive calls alternate the exchange slot
+        assert torch.equal(g.qmatmul_rowparallel(mm, x, bias=bias, mode=tq.Mode.INT8_ACT), want)
+    assert torch.equal(g.allreduce(x), x)
+    assert torch.equal(g.allgather(x, [k]), x)
+    # tensor-core scheme goes through the staging copy
+    x64 = torch.from_numpy(rng.standard_normal((40, k)).astype(np.float32)).cuda()
+    g2 = TPGroup(0, 1, 40 * n * 4)
+    assert torch.equal(g2.qmatmul_rowparallel(mm, x64, mode=tq.Mode.TENSOR_CORE), mm.forward(x64, mode=tq.Mode.TENSOR_CORE))
+    # a captured graph replays the same launches: the call number lives on the device
+    out = torch.empty((m, n), device="cuda")
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side), torch.cuda.graph(graph, stream=side):
+        g.qmatmul_rowparallel(mm, x, bias=bias, mode=tq.Mode.INT8_ACT, out=out)
+        g.qmatmul_rowparallel(mm, x, bias=bias, mode=tq.Mode.INT8_ACT, out=out)
+        g.qmatmul_rowparallel(mm, x, bias=bias, mode=tq.Mode.INT8_ACT, out=out)   # odd count: replays start on alternating slots
+    for _ in range(4):
+        out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, want)
+    tq.context().poll_status()
+    with pytest.raises(tq.TurqError) as e:
+        g.allreduce(torch.zeros(m * n + 4, device="cuda"))   # more than the slot holds
+    assert e.value.status == 9
+
+
+@pytest.mark.parametrize("world,rank", [(2, 0), (4, 2), (8, 7)])
+def test_reduction_adds_the_ranks_in_rank_order(tq, world, rank):
+    from tur_b200.tensor_parallel import TPGroup
+    n, k, m = 528, 512, 5
+    rng = np.random.default_rng(SEED + world)
+    w = oracle.quantize(oracle.Q6_K, (rng.standard_normal((n, k)) * 0.02).astype(np.float32))
+    mm = tq.QMatMul.from_arc(tq.QTensor.new(w, tq.GgmlDType.Q6K, (n, k)))
+    g = TPGroup(rank, world, m * n * 4, loopback=True)
+    bias = torch.from_numpy(rng.standard_normal(n).astype(np.float32)).cuda()
+    for call in range(3):
+        x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).cuda()
+        own = mm.forward(x, mode=tq.Mode.INT8_ACT)
+        parts = [torch.from_numpy(rng.standard_normal((m, n)).astype(np.float32)).cuda() for _ in range(world)]
+        parts[rank] = own
+        for p in range(world):
+            if p != rank:
+                g.loopback_fill(p, parts[p], signal=True)     # the stand-in "peer" has written its slot and signalled
+        y = g.qmatmul_rowparallel(mm, x, bias=bias, mode=tq.Mode.INT8_ACT)
+        want = parts[0].clone()
+        for p in range(1, world):
+            want += parts[p]                                  # rank order, one rounding per addition
+        want += bias
+        assert torch.equal(y, want), call
+    # all-gather with uneven widths
+    widths = [16 * (3 + (p % 3)) for p in range(world)]
+    shares = [torch.from_numpy(rng.standard_normal((m, wd)).astype(np.float32)).cuda() for wd in widths]
+    for p in range(world):
+        if p != rank:
+            g.loopback_fill(p, shares[p], signal=True)
+    assert torch.equal(g.allgather(shares[rank], widths), torch.cat(shares, dim=1))
+    tq.context().poll_status()
+
+
+def test_a_peer_that_never_arrives_ends_the_wait_with_a_status(tq):
+    from tur_b200.tensor_parallel import TPGroup
+    ctx = tq.new_context()
+    g = TPGroup(0, 2, 4096, ctx=ctx, loopback=True)
+    g.set_wait_limit(2_000_000)                               # about a millisecond of SM clock
+    x = torch.ones(1024, device="cuda")
+    out = torch.full_like(x, -1.0)
+    g.allreduce(x, out=out)                                   # rank 1 never signals
+    with pytest.raises(tq.TurqError) as e:
+        ctx.poll_status()
+    assert e.value.status == 7
+    assert torch.equal(out, torch.full_like(x, -1.0))         # the exchange was skipped, nothing half-written
+    ctx.poll_status()                                         # status cleared, context usable
+    g.reset()
+    g.loopback_fill(1, torch.full_like(x, 2.0), signal=True)
+    assert torch.equal(g.allreduce(x), torch.full_like(x, 3.0))
+    ctx.poll_status()

@@ -43,6 +43,17 @@ SIGNATURES = {
     "turq_qmatmul_host": (c_i32, [c_vp, c_vp, c_vp, c_i64, c_vp, c_i32, c_vp]),
     "turq_qmatmul_multi_host": (c_i32, [c_vp, c_i32, c_vp, c_vp, c_i64, c_vp, c_i32, c_vp]),
     "turq_qmatmul_static": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i64, c_vp, c_vp, c_vp]),
+    "turq_tp_create": (c_i32, [c_vp, c_i32, c_i32, c_sz, PP]),
+    "turq_tp_export": (c_i32, [c_vp, c_vp]),
+    "turq_tp_connect": (c_i32, [c_vp, c_vp]),
+    "turq_tp_destroy": (c_i32, [c_vp]),
+    "turq_tp_set_wait_limit": (c_i32, [c_vp, c_i64]),
+    "turq_tp_reset": (c_i32, [c_vp]),
+    "turq_tp_allreduce": (c_i32, [c_vp, c_vp, c_vp, c_i64, c_vp]),
+    "turq_tp_allgather": (c_i32, [c_vp, c_vp, c_i64, c_vp, c_vp, c_vp]),
+    "turq_qmatmul_rowparallel": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i64, c_vp, c_i32, c_vp, c_vp]),
+    "turq_tp_connect_loopback": (c_i32, [c_vp]),
+    "turq_tp_loopback_fill": (c_i32, [c_vp, c_i32, c_vp, c_i64, c_i32, c_vp]),
 }
 
 _lib = None

@@ -195,6 +195,7 @@ int32_t turq_ctx_destroy(turq_ctx* ctx) {
   cudaDeviceSynchronize();
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->io) cudaFree(ctx->io);
+  if (ctx->tmp) cudaFree(ctx->tmp);
   if (ctx->host_status) cudaFreeHost(ctx->host_status);
   if (ctx->gemv_ws) cudaFree(ctx->gemv_ws);
   if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
@@ -507,7 +508,7 @@ static int32_t qmatmul_multi_impl(turq_ctx* ctx, int32_t count, const turq_qtens
   if (st != TURQ_OK) return st;
   turq::GemvPart parts[4];
   for (int i = 0; i < count; i++)
-    parts[i] = turq::GemvPart{qts[i]->tiles, qts[i]->n_rows, dev_ys[i], dev_biases ? dev_biases[i] : nullptr, qts[i]->dtype};
+    parts[i] = turq::GemvPart{qts[i]->tiles, qts[i]->n_rows, dev_ys[i], dev_biases ? dev_biases[i] : nullptr, qts[i]->dtype, nullptr};
   int launches = 0;
   cudaError_t e = turq::launch_gemv_int8_multi(qts[0]->dtype, parts, count, k, dev_x, x_dtype, ctx->scratch, m, ctx->gemv_ws,
                                                ctx->dev_status, ctx->sm_count, static_cast<cudaStream_t>(stream), &launches,
@@ -611,3 +612,36 @@ int32_t turq_qmatmul_host(turq_ctx* ctx, const turq_qtensor* qt, const float* ho
 }
 
 }  // extern "C"
+
+namespace turq {
+
+int32_t qmatmul_for_exchange(turq_ctx* ctx, const turq_qtensor* qt, const void* dev_x, int32_t x_dtype, int64_t m, float* s0,
+                             float* s1, const unsigned* toggle, int32_t mode, cudaStream_t s, float** staged) {
+  *staged = nullptr;
+  if (x_dtype != TURQ_F32 && x_dtype != TURQ_BF16) return fail(ctx, TURQ_E_DTYPE, "activations must be F32 or BF16 (got %d)", x_dtype);
+  if (qt->device != ctx->device) return fail(ctx, TURQ_E_INVALID_ARG, "tensor lives on device %d, context on %d", qt->device, ctx->device);
+  if ((uintptr_t)dev_x % 16 != 0) return fail(ctx, TURQ_E_ALIGN, "dev_x must be 16-byte aligned");
+  if (mode == TURQ_MODE_AUTO) mode = auto_mode(ctx, qt->n_rows, qt->n_cols, m);
+  TQ_CUDA(ctx, cudaSetDevice(ctx->device));
+  if (mode == TURQ_MODE_INT8_ACT) {
+    const int64_t k = qt->n_cols;
+    const int fmt = qt->dtype == TURQ_Q8_0 ? TQ_Q8_0 : TQ_Q8_K;
+    int32_t st = ensure(ctx, &ctx->scratch, &ctx->scratch_bytes, plan_act_pack(fmt, m, k).total);
+    if (st != TURQ_OK) return st;
+    GemvPart part{qt->tiles, qt->n_rows, s0, nullptr, qt->dtype, s1};
+    int launches = 0;
+    cudaError_t e = launch_gemv_int8_multi(qt->dtype, &part, 1, k, dev_x, x_dtype, ctx->scratch, m, ctx->gemv_ws, ctx->dev_status,
+                                           ctx->sm_count, s, &launches, false, toggle);
+    ctx->launches += launches;
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "row-parallel GEMV launch");
+    return TURQ_OK;
+  }
+  int32_t st = ensure(ctx, &ctx->tmp, &ctx->tmp_bytes, (size_t)m * qt->n_rows * 4);
+  if (st != TURQ_OK) return st;
+  st = turq_qmatmul(ctx, qt, dev_x, x_dtype, m, reinterpret_cast<float*>(ctx->tmp), mode, nullptr, s);
+  if (st != TURQ_OK) return st;
+  *staged = reinterpret_cast<float*>(ctx->tmp);
+  return TURQ_OK;
+}
+
+}  // namespace turq

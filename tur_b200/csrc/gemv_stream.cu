@@ -109,6 +109,9 @@ struct StreamArgs {
   int rt_begin[MAX_PARTS + 1];
   int part_alt[MAX_PARTS];        // mixed launches: 1 = this part's tiles are of the second type (DT2)
   float* y[MAX_PARTS];            // outputs, already offset to the pass's first row
+  float* y_alt[MAX_PARTS];        // second output buffer, used instead of y when (*y_toggle + 1) is odd
+  const unsigned* y_toggle;       // nullptr: always y. Tensor-parallel exchange: the call counter, whose
+                                  // parity selects the exchange slot this launch has to fill
   const float* bias[MAX_PARTS];
   int nparts;
   int ktiles, k;
@@ -448,6 +451,7 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
     // tile of a row-tile owns it; later CTAs reach into it with the first tiles of their
     // ranges, so their sums are normally there long before the owner needs them.
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    const bool use_alt = a.y_toggle != nullptr && ((__ldcg(a.y_toggle) + 1u) & 1u) != 0u;
     StageWalk w;
     w.init(u0, u1, KU);
     int seg_ka = w.ku;
@@ -467,7 +471,7 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
       int part = 0;
       while (part + 1 < a.nparts && rt >= a.rt_begin[part + 1]) part++;
       const int64_t part_rows = a.n_rows[part];
-      float* const part_y = a.y[part];
+      float* const part_y = use_alt ? a.y_alt[part] : a.y[part];
       const float* const part_bias = a.bias[part];
       const int rt_local = rt - a.rt_begin[part];
       constexpr int EPL = (MG * 128 + 31) / 32;  // output elements per lane
@@ -603,7 +607,7 @@ static cudaError_t launch_one(StreamArgs a, int grid, int smem_bytes, cudaStream
 template <int DT, int DT2 = DT>
 static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const void* x, int x_dtype,
                              uint8_t* act_scratch, int64_t m, uint8_t* workspace, int* status, int sm_count,
-                             cudaStream_t s, int* launches, bool x_remote) {
+                             cudaStream_t s, int* launches, bool x_remote, const unsigned* y_toggle) {
   constexpr bool MIXED = DT2 != DT;
   constexpr int GROUP = TileGeom<DT>::GROUP;
   constexpr int UNIT_BYTES = (TileGeom<DT2>::BYTES > TileGeom<DT>::BYTES ? TileGeom<DT2>::BYTES : TileGeom<DT>::BYTES) * GROUP;
@@ -671,10 +675,12 @@ static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const
       a.tiles[p] = parts[p].tiles;
       a.n_rows[p] = parts[p].n_rows;
       a.y[p] = parts[p].y + m0 * parts[p].n_rows;
+      a.y_alt[p] = parts[p].y_alt ? parts[p].y_alt + m0 * parts[p].n_rows : nullptr;
       a.bias[p] = parts[p].bias;
       a.part_alt[p] = (MIXED && parts[p].dtype == DT2) ? 1 : 0;
     }
     for (int p = 0; p <= nparts; p++) a.rt_begin[p] = rt_begin[p];
+    a.y_toggle = y_toggle;
     a.nparts = nparts;
     a.ktiles = ktiles;
     a.k = (int)k;
@@ -723,11 +729,11 @@ static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const
   return cudaSuccess;
 }
 
-#define TQ_LAUNCH_ARGS k, x, x_dtype, act_scratch, m, workspace, status, sm_count, s, launches, x_remote
+#define TQ_LAUNCH_ARGS k, x, x_dtype, act_scratch, m, workspace, status, sm_count, s, launches, x_remote, y_toggle
 
 static cudaError_t launch_one_type(int dtype, const GemvPart* parts, int nparts, int64_t k, const void* x, int x_dtype,
                                    uint8_t* act_scratch, int64_t m, uint8_t* workspace, int* status, int sm_count,
-                                   cudaStream_t s, int* launches, bool x_remote) {
+                                   cudaStream_t s, int* launches, bool x_remote, const unsigned* y_toggle) {
   switch (dtype) {
     case TQ_Q8_0: return launch_dt<TQ_Q8_0>(parts, nparts, TQ_LAUNCH_ARGS);
     case TQ_Q4_K: return launch_dt<TQ_Q4_K>(parts, nparts, TQ_LAUNCH_ARGS);
@@ -741,7 +747,7 @@ static cudaError_t launch_one_type(int dtype, const GemvPart* parts, int nparts,
 // together with Q6_K parts too, where the mixed kernel exists; anything else one launch per type.
 cudaError_t launch_gemv_int8_multi(int dtype, const GemvPart* parts, int nparts, int64_t k, const void* x, int x_dtype,
                                    uint8_t* act_scratch, int64_t m, uint8_t* workspace, int* status, int sm_count,
-                                   cudaStream_t s, int* launches, bool x_remote) {
+                                   cudaStream_t s, int* launches, bool x_remote, const unsigned* y_toggle) {
   if (nparts < 1 || nparts > MAX_PARTS) return cudaErrorInvalidValue;
   GemvPart p[MAX_PARTS];
   int types[MAX_PARTS], ntypes = 0;
@@ -777,8 +783,9 @@ cudaError_t launch_gemv_int8_multi(int dtype, const GemvPart* parts, int nparts,
 cudaError_t launch_gemv_int8(int dtype, const uint8_t* tiles, int64_t n_rows, int64_t k, const void* x, int x_dtype,
                              uint8_t* act_scratch, int64_t m, float* y, const float* bias, uint8_t* workspace,
                              int* status, int sm_count, cudaStream_t s, int* launches) {
-  GemvPart part{tiles, n_rows, y, bias, dtype};
-  return launch_gemv_int8_multi(dtype, &part, 1, k, x, x_dtype, act_scratch, m, workspace, status, sm_count, s, launches, false);
+  GemvPart part{tiles, n_rows, y, bias, dtype, nullptr};
+  return launch_gemv_int8_multi(dtype, &part, 1, k, x, x_dtype, act_scratch, m, workspace, status, sm_count, s, launches, false,
+                                nullptr);
 }
 
 }  // namespace turq

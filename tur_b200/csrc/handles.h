@@ -13,6 +13,8 @@ struct turq_ctx {
   size_t scratch_bytes = 0;
   uint8_t* io = nullptr;  // device staging for the host-buffer entry (x, y, bias)
   size_t io_bytes = 0;
+  uint8_t* tmp = nullptr;  // results on their way to a tensor-parallel exchange slot / fused epilogues
+  size_t tmp_bytes = 0;
   int* host_status = nullptr;  // status word in mapped pinned host memory, written by kernels with bounded waits
   int* dev_status = nullptr;   // the same word's device address
   uint8_t* gemv_ws = nullptr;  // split row-tile workspace of the streaming GEMV (zeroed once)

@@ -1,0 +1,507 @@
+// Tensor-parallel exchange over peer memory (NVLink / NVSwitch): the all-reduce behind the
+// row-parallel linears (attn_output, ffn_down) and the all-gather behind the vocabulary-sharded
+// head, as kernels of this library instead of NCCL calls, so that a whole sharded decode pass
+// can live in one CUDA graph and the partial sums never take an extra copy.
+//
+// The reference is single-device (src/models/layers/norm.rs:50 passes Shard::default()
+// everywhere); this is the multi-GPU extension of its linear layers.
+//
+// Memory. Every rank owns one exchange region allocated with cudaMalloc and opened on the other
+// ranks through CUDA IPC handles (one process per GPU, one node):
+//     [ flags: MAX_BLOCKS x MAX_RANKS u32 | counter: 4 u32 | slot 0 | slot 1 ]
+// A linear's epilogue writes its partial result straight into a slot of the local region; the
+// exchange kernel then tells every peer "my slot is complete" (one system-scope release store per
+// peer and CTA), waits for the peers' signals, and reads the peers' slots with plain 128-bit peer
+// loads in rank order - a fixed summation order, no float atomics, no multicast loads of any
+// kind, no library kernel ever sees a peer pointer.
+//
+// Slots alternate by call parity. A rank can run at most one call ahead of the slowest peer (it
+// cannot pass the next call's wait before that peer has signalled, which the peer only does
+// after it finished reading), so the slot a fast rank writes next is never one a slow peer still
+// reads. The call number lives in device memory (counter[0]) and is advanced by the exchange
+// kernel itself, which is what lets a captured graph replay the same launches again and again;
+// the GEMV picks its output slot from the same word.
+//
+// Every wait is bounded by a cycle limit held in the handle; when it runs out the kernel records
+// TURQ_E_TIMEOUT in the context's status word, skips the exchange and returns. The sequence is
+// then out of step across ranks: the host reads the status (turq_ctx_poll_status) and every
+// rank calls turq_tp_reset before the group is used again.
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "../../include/turq.h"
+#include "handles.h"
+#include "turq_internal.h"
+
+namespace turq {
+
+constexpr int TP_MAX_RANKS = 8;
+constexpr int TP_MAX_BLOCKS = 128;
+constexpr int TP_THREADS = 256;
+constexpr size_t TP_FLAGS_BYTES = (size_t)TP_MAX_BLOCKS * TP_MAX_RANKS * 4;  // 4 KB
+constexpr size_t TP_HEADER_BYTES = TP_FLAGS_BYTES + 256;                     // + counter words, 256-byte aligned
+
+struct TpArgs {
+  const float* peer_data[TP_MAX_RANKS];  // slot 0 of every rank's region, in rank order (own: local pointer)
+  unsigned* peer_flags[TP_MAX_RANKS];    // flag array of every rank's region
+  unsigned* counter;                     // own region: [0] calls completed, [1] CTA ticket
+  size_t slot_elems;                     // floats per slot
+  int rank, world;
+  long long wait_cycles;
+  int* status;
+  // reduce: out[i] = sum_p peer[p][i] (+ bias[i % n]) for i < count
+  int64_t count, n;
+  const float* bias;
+  // gather: out[r, col0[p] + j] = peer[p][r * width[p] + j]
+  int64_t m, n_total;
+  int64_t col0[TP_MAX_RANKS + 1];
+  float* out;
+};
+
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// peer data: system-scope loads that do not linger in this SM's L1 across calls
+__device__ __forceinline__ float4 ld_peer_v4(const float* p) {
+  float4 v;
+  asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float ld_peer_f32(const float* p) {
+  float v;
+  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Signals this CTA's peers, waits for theirs. Returns false when the wait ran out.
+__device__ __forceinline__ bool tp_rendezvous(const TpArgs& a, unsigned seq, int* s_ok) {
+  const int b = blockIdx.x;
+  if (threadIdx.x == 0) *s_ok = 1;
+  __syncthreads();
+  if (threadIdx.x < a.world) {
+    const int p = threadIdx.x;
+    // everything this rank put into its slot was written by kernels that completed before this
+    // one started; the release store publishes it to the peer together with the flag
+    st_release_sys(a.peer_flags[p] + b * TP_MAX_RANKS + a.rank, seq);
+    const unsigned* mine = a.peer_flags[a.rank] + b * TP_MAX_RANKS + p;
+    const long long t0 = clock64();
+    for (;;) {
+      if ((int)(ld_acquire_sys(mine) - seq) >= 0) break;
+      if (clock64() - t0 > a.wait_cycles) {
+        *s_ok = 0;
+        break;
+      }
+      __nanosleep(40);
+    }
+  }
+  __syncthreads();
+  return *s_ok != 0;
+}
+
+// The last CTA to finish advances the call number (every CTA read it at its start).
+__device__ __forceinline__ void tp_finish(const TpArgs& a, unsigned seq, bool ok) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (!ok) {
+      *reinterpret_cast<volatile int*>(a.status) = TURQ_E_TIMEOUT;  // the word may be mapped host memory
+      __threadfence_system();
+    }
+    __threadfence();
+    const unsigned ticket = atomicAdd(a.counter + 1, 1u);
+    if (ticket == gridDim.x - 1) {
+      a.counter[1] = 0;
+      __threadfence();
+      *reinterpret_cast<volatile unsigned*>(a.counter) = seq;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(TP_THREADS) tp_allreduce_kernel(const TpArgs a) {
+  __shared__ int s_ok;
+  const unsigned seq = *reinterpret_cast<volatile unsigned*>(a.counter) + 1u;
+  const size_t slot_off = (seq & 1u) ? a.slot_elems : 0;
+  const bool ok = tp_rendezvous(a, seq, &s_ok);
+  if (ok) {
+    const int64_t nvec = a.count >> 2;
+    const bool vec_bias = a.bias && (a.n & 3) == 0;
+    for (int64_t v = (int64_t)blockIdx.x * TP_THREADS + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * TP_THREADS) {
+      float4 acc = ld_peer_v4(a.peer_data[0] + slot_off + 4 * v);
+      for (int p = 1; p < a.world; p++) {
+        const float4 t = ld_peer_v4(a.peer_data[p] + slot_off + 4 * v);
+        acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+      }
+      if (a.bias) {
+        if (vec_bias) {
+          const float4 bb = *reinterpret_cast<const float4*>(a.bias + (4 * v) % a.n);
+          acc.x += bb.x; acc.y += bb.y; acc.z += bb.z; acc.w += bb.w;
+        } else {
+          acc.x += a.bias[(4 * v) % a.n]; acc.y += a.bias[(4 * v + 1) % a.n];
+          acc.z += a.bias[(4 * v + 2) % a.n]; acc.w += a.bias[(4 * v + 3) % a.n];
+        }
+      }
+      *reinterpret_cast<float4*>(a.out + 4 * v) = acc;
+    }
+    // tail (count not a multiple of 4)
+    if (blockIdx.x == 0) {
+      for (int64_t i = (nvec << 2) + threadIdx.x; i < a.count; i += TP_THREADS) {
+        float acc = ld_peer_f32(a.peer_data[0] + slot_off + i);
+        for (int p = 1; p < a.world; p++) acc += ld_peer_f32(a.peer_data[p] + slot_off + i);
+        if (a.bias) acc += a.bias[i % a.n];
+        a.out[i] = acc;
+      }
+    }
+  }
+  tp_finish(a, seq, ok);
+}
+
+__global__ void __launch_bounds__(TP_THREADS) tp_allgather_kernel(const TpArgs a) {
+  __shared__ int s_ok;
+  const unsigned seq = *reinterpret_cast<volatile unsigned*>(a.counter) + 1u;
+  const size_t slot_off = (seq & 1u) ? a.slot_elems : 0;
+  const bool ok = tp_rendezvous(a, seq, &s_ok);
+  if (ok) {
+    // one (rank, row) run of columns at a time; widths are multiples of 4 floats
+    const int64_t runs = (int64_t)a.world * a.m;
+    for (int64_t run = blockIdx.x; run < runs; run += gridDim.x) {
+      const int p = (int)(run / a.m);
+      const int64_t r = run - (int64_t)p * a.m;
+      const int64_t width = a.col0[p + 1] - a.col0[p];
+      const float* src = a.peer_data[p] + slot_off + r * width;
+      float* dst = a.out + r * a.n_total + a.col0[p];
+      if ((width & 3) == 0 && ((a.col0[p] | a.n_total) & 3) == 0) {
+        for (int64_t v = threadIdx.x; v < (width >> 2); v += TP_THREADS)
+          *reinterpret_cast<float4*>(dst + 4 * v) = ld_peer_v4(src + 4 * v);
+      } else {
+        for (int64_t i = threadIdx.x; i < width; i += TP_THREADS) dst[i] = ld_peer_f32(src + i);
+      }
+    }
+  }
+  tp_finish(a, seq, ok);
+}
+
+// Copies a result that was computed elsewhere into the slot of the upcoming call.
+__global__ void __launch_bounds__(256) tp_stage_kernel(const float* __restrict__ src, float* __restrict__ slots,
+                                                        size_t slot_elems, const unsigned* counter, int64_t count) {
+  const unsigned seq = *reinterpret_cast<const volatile unsigned*>(counter) + 1u;
+  float* dst = slots + ((seq & 1u) ? slot_elems : 0);
+  const int64_t nvec = count >> 2;
+  for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * blockDim.x)
+    reinterpret_cast<float4*>(dst)[v] = reinterpret_cast<const float4*>(src)[v];
+  if (blockIdx.x == 0)
+    for (int64_t i = (nvec << 2) + threadIdx.x; i < count; i += blockDim.x) dst[i] = src[i];
+}
+
+}  // namespace turq
+
+struct turq_tp {
+  turq_ctx* ctx = nullptr;
+  int rank = 0, world = 1;
+  size_t slot_bytes = 0;                 // bytes per slot (multiple of 256)
+  uint8_t* region = nullptr;             // own region
+  size_t region_bytes = 0;
+  uint8_t* peers[turq::TP_MAX_RANKS] = {};  // every rank's region as this process sees it (own = region)
+  bool opened[turq::TP_MAX_RANKS] = {};     // true: mapped with cudaIpcOpenMemHandle (close on destroy)
+  bool loopback[turq::TP_MAX_RANKS] = {};   // true: a local stand-in allocated by turq_tp_connect_loopback
+  bool connected = false;
+  long long wait_cycles = 2000000000ll;  // about one second of SM clock
+};
+
+namespace {
+
+int32_t tp_fail(turq_tp* tp, int32_t st, const char* msg) {
+  if (tp && tp->ctx) {
+    try {
+      tp->ctx->err = msg;
+    } catch (...) {
+    }
+  }
+  return st;
+}
+int32_t tp_cuda_fail(turq_tp* tp, cudaError_t e, const char* what) {
+  char buf[256];
+  snprintf(buf, sizeof(buf), "%s: %s", what, cudaGetErrorString(e));
+  cudaGetLastError();
+  return tp_fail(tp, TURQ_E_CUDA, buf);
+}
+
+float* slot0(const turq_tp* tp, int p) { return reinterpret_cast<float*>(tp->peers[p] + turq::TP_HEADER_BYTES); }
+unsigned* flags_of(const turq_tp* tp, int p) { return reinterpret_cast<unsigned*>(tp->peers[p]); }
+unsigned* counter_of(const turq_tp* tp) { return reinterpret_cast<unsigned*>(tp->region + turq::TP_FLAGS_BYTES); }
+
+void fill_args(const turq_tp* tp, turq::TpArgs& a) {
+  for (int p = 0; p < tp->world; p++) {
+    a.peer_data[p] = slot0(tp, p);
+    a.peer_flags[p] = flags_of(tp, p);
+  }
+  a.counter = counter_of(tp);
+  a.slot_elems = tp->slot_bytes / 4;
+  a.rank = tp->rank;
+  a.world = tp->world;
+  a.wait_cycles = tp->wait_cycles;
+  a.status = tp->ctx->dev_status;
+}
+
+int grid_for(int64_t work_items, int sm_count) {
+  int64_t g = (work_items + turq::TP_THREADS - 1) / turq::TP_THREADS;
+  const int cap = sm_count < turq::TP_MAX_BLOCKS ? sm_count : turq::TP_MAX_BLOCKS;
+  if (g > cap) g = cap;
+  return g < 1 ? 1 : (int)g;
+}
+
+int32_t check_ready(turq_tp* tp) {
+  if (!tp || !tp->ctx) return TURQ_E_INVALID_ARG;
+  if (!tp->connected) return tp_fail(tp, TURQ_E_INVALID_ARG, "the tensor-parallel group is not connected yet (turq_tp_connect)");
+  return TURQ_OK;
+}
+
+int32_t launch_reduce(turq_tp* tp, int64_t count, int64_t n, const float* bias, float* out, cudaStream_t s) {
+  turq::TpArgs a{};
+  fill_args(tp, a);
+  a.count = count;
+  a.n = n > 0 ? n : 1;
+  a.bias = bias;
+  a.out = out;
+  // the same grid on every rank (CTA b pairs with CTA b of the peers): it depends on count only
+  const int grid = grid_for((count + 3) / 4, turq::TP_MAX_BLOCKS);
+  turq::tp_allreduce_kernel<<<grid, turq::TP_THREADS, 0, s>>>(a);
+  tp->ctx->launches++;
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return tp_cuda_fail(tp, e, "all-reduce launch");
+  return TURQ_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t turq_tp_create(turq_ctx* ctx, int32_t rank, int32_t world, size_t max_bytes, turq_tp** out) {
+  if (!ctx || !out) return TURQ_E_INVALID_ARG;
+  *out = nullptr;
+  auto bad = [&](int32_t st, const char* m) {
+    try { ctx->err = m; } catch (...) {}
+    return st;
+  };
+  if (world < 1 || world > turq::TP_MAX_RANKS || rank < 0 || rank >= world) return bad(TURQ_E_INVALID_ARG, "rank / world out of range (at most 8 ranks)");
+  if (max_bytes == 0 || max_bytes > ((size_t)1 << 31)) return bad(TURQ_E_LIMIT, "exchange slot size must be between 1 byte and 2 GiB");
+  turq_tp* tp = new (std::nothrow) turq_tp();
+  if (!tp) return bad(TURQ_E_INVALID_ARG, "out of host memory");
+  tp->ctx = ctx;
+  tp->rank = rank;
+  tp->world = world;
+  tp->slot_bytes = (max_bytes + 255) & ~(size_t)255;
+  tp->region_bytes = turq::TP_HEADER_BYTES + 2 * tp->slot_bytes;
+  cudaError_t e = cudaSetDevice(ctx->device);
+  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&tp->region), tp->region_bytes);
+  if (e == cudaSuccess) e = cudaMemset(tp->region, 0, turq::TP_HEADER_BYTES);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    if (tp->region) cudaFree(tp->region);
+    delete tp;
+    cudaGetLastError();
+    return bad(TURQ_E_CUDA, cudaGetErrorString(e));
+  }
+  tp->peers[rank] = tp->region;
+  if (world == 1) tp->connected = true;
+  *out = tp;
+  return TURQ_OK;
+}
+
+int32_t turq_tp_export(const turq_tp* tp, void* handle_out) {
+  if (!tp || !handle_out) return TURQ_E_INVALID_ARG;
+  static_assert(sizeof(cudaIpcMemHandle_t) <= TURQ_TP_HANDLE_BYTES, "handle blob too small");
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaSetDevice(tp->ctx->device);
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, tp->region);
+  if (e != cudaSuccess) return tp_cuda_fail(const_cast<turq_tp*>(tp), e, "cudaIpcGetMemHandle");
+  memset(handle_out, 0, TURQ_TP_HANDLE_BYTES);
+  memcpy(handle_out, &h, sizeof(h));
+  return TURQ_OK;
+}
+
+int32_t turq_tp_connect(turq_tp* tp, const void* handles) {
+  if (!tp || !handles) return TURQ_E_INVALID_ARG;
+  if (tp->connected) return tp_fail(tp, TURQ_E_INVALID_ARG, "the group is connected already");
+  cudaError_t e = cudaSetDevice(tp->ctx->device);
+  if (e != cudaSuccess) return tp_cuda_fail(tp, e, "cudaSetDevice");
+  for (int p = 0; p < tp->world; p++) {
+    if (p == tp->rank) continue;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, static_cast<const uint8_t*>(handles) + (size_t)p * TURQ_TP_HANDLE_BYTES, sizeof(h));
+    void* ptr = nullptr;
+    e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return tp_cuda_fail(tp, e, "cudaIpcOpenMemHandle (is peer access between the GPUs available?)");
+    tp->peers[p] = static_cast<uint8_t*>(ptr);
+    tp->opened[p] = true;
+  }
+  tp->connected = true;
+  return TURQ_OK;
+}
+
+int32_t turq_tp_connect_loopback(turq_tp* tp) {
+  if (!tp) return TURQ_E_INVALID_ARG;
+  if (tp->connected) return tp_fail(tp, TURQ_E_INVALID_ARG, "the group is connected already");
+  cudaError_t e = cudaSetDevice(tp->ctx->device);
+  for (int p = 0; p < tp->world && e == cudaSuccess; p++) {
+    if (p == tp->rank) continue;
+    e = cudaMalloc(reinterpret_cast<void**>(&tp->peers[p]), tp->region_bytes);
+    if (e == cudaSuccess) {
+      tp->loopback[p] = true;
+      e = cudaMemset(tp->peers[p], 0, tp->region_bytes);
+    }
+  }
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return tp_cuda_fail(tp, e, "loopback allocation");
+  tp->connected = true;
+  return TURQ_OK;
+}
+
+int32_t turq_tp_loopback_fill(turq_tp* tp, int32_t peer, const float* dev_src, int64_t count, int32_t signal, void* stream) {
+  int32_t st = check_ready(tp);
+  if (st != TURQ_OK) return st;
+  if (peer < 0 || peer >= tp->world || !tp->loopback[peer]) return tp_fail(tp, TURQ_E_INVALID_ARG, "not a loopback stand-in rank");
+  if (count < 0 || (size_t)count * 4 > tp->slot_bytes) return tp_fail(tp, TURQ_E_LIMIT, "more elements than an exchange slot holds");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaSetDevice(tp->ctx->device);
+  // The stand-in plays the peer's part for the NEXT call: data into the slot of that call and,
+  // with `signal`, its "slot complete" flags for every CTA. Needs the current call number.
+  unsigned done = 0;
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e == cudaSuccess) e = cudaMemcpy(&done, counter_of(tp), 4, cudaMemcpyDeviceToHost);
+  const unsigned seq = done + 1u;
+  if (e == cudaSuccess && dev_src && count > 0)
+    e = cudaMemcpyAsync(slot0(tp, peer) + ((seq & 1u) ? tp->slot_bytes / 4 : 0), dev_src, (size_t)count * 4, cudaMemcpyDeviceToDevice, s);
+  if (e == cudaSuccess && signal) {
+    unsigned host_flags[turq::TP_MAX_BLOCKS * turq::TP_MAX_RANKS];
+    e = cudaMemcpy(host_flags, flags_of(tp, tp->rank), sizeof(host_flags), cudaMemcpyDeviceToHost);
+    for (int b = 0; b < turq::TP_MAX_BLOCKS; b++) host_flags[b * turq::TP_MAX_RANKS + peer] = seq;
+    if (e == cudaSuccess) e = cudaMemcpy(flags_of(tp, tp->rank), host_flags, sizeof(host_flags), cudaMemcpyHostToDevice);
+  }
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) return tp_cuda_fail(tp, e, "loopback fill");
+  return TURQ_OK;
+}
+
+int32_t turq_tp_set_wait_limit(turq_tp* tp, int64_t cycles) {
+  if (!tp || cycles <= 0) return TURQ_E_INVALID_ARG;
+  tp->wait_cycles = cycles;
+  return TURQ_OK;
+}
+
+int32_t turq_tp_reset(turq_tp* tp) {
+  if (!tp) return TURQ_E_INVALID_ARG;
+  cudaError_t e = cudaSetDevice(tp->ctx->device);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemset(tp->region, 0, turq::TP_HEADER_BYTES);
+  for (int p = 0; p < tp->world && e == cudaSuccess; p++)
+    if (tp->loopback[p]) e = cudaMemset(tp->peers[p], 0, turq::TP_HEADER_BYTES);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return tp_cuda_fail(tp, e, "tp reset");
+  return TURQ_OK;
+}
+
+int32_t turq_tp_destroy(turq_tp* tp) {
+  if (!tp) return TURQ_E_INVALID_ARG;
+  cudaSetDevice(tp->ctx->device);
+  cudaDeviceSynchronize();
+  for (int p = 0; p < tp->world; p++) {
+    if (tp->opened[p]) cudaIpcCloseMemHandle(tp->peers[p]);
+    if (tp->loopback[p]) cudaFree(tp->peers[p]);
+  }
+  if (tp->region) cudaFree(tp->region);
+  cudaGetLastError();
+  delete tp;
+  return TURQ_OK;
+}
+
+int32_t turq_tp_allreduce(turq_tp* tp, const float* dev_in, float* dev_out, int64_t count, void* stream) {
+  int32_t st = check_ready(tp);
+  if (st != TURQ_OK) return st;
+  if (!dev_in || !dev_out) return tp_fail(tp, TURQ_E_INVALID_ARG, "null argument");
+  if (count <= 0) return tp_fail(tp, TURQ_E_SHAPE, "count must be positive");
+  if ((size_t)count * 4 > tp->slot_bytes) return tp_fail(tp, TURQ_E_LIMIT, "more elements than an exchange slot holds (turq_tp_create max_bytes)");
+  if ((uintptr_t)dev_in % 16 != 0 || (uintptr_t)dev_out % 16 != 0) return tp_fail(tp, TURQ_E_ALIGN, "buffers must be 16-byte aligned");
+  cudaError_t e = cudaSetDevice(tp->ctx->device);
+  if (e != cudaSuccess) return tp_cuda_fail(tp, e, "cudaSetDevice");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int64_t blocks = (count / 4 + 255) / 256;
+  if (blocks > 2 * (int64_t)tp->ctx->sm_count) blocks = 2 * (int64_t)tp->ctx->sm_count;
+  if (blocks < 1) blocks = 1;
+  turq::tp_stage_kernel<<<(unsigned)blocks, 256, 0, s>>>(dev_in, slot0(tp, tp->rank), tp->slot_bytes / 4, counter_of(tp), count);
+  tp->ctx->launches++;
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return tp_cuda_fail(tp, e, "stage launch");
+  return launch_reduce(tp, count, 1, nullptr, dev_out, s);
+}
+
+int32_t turq_tp_allgather(turq_tp* tp, const float* dev_in, int64_t m, const int64_t* widths, float* dev_out, void* stream) {
+  int32_t st = check_ready(tp);
+  if (st != TURQ_OK) return st;
+  if (!dev_in || !dev_out || !widths) return tp_fail(tp, TURQ_E_INVALID_ARG, "null argument");
+  if (m <= 0) return tp_fail(tp, TURQ_E_SHAPE, "m must be positive");
+  turq::TpArgs a{};
+  fill_args(tp, a);
+  int64_t widest = 0;
+  a.col0[0] = 0;
+  for (int p = 0; p < tp->world; p++) {
+    if (widths[p] <= 0) return tp_fail(tp, TURQ_E_SHAPE, "every rank's width must be positive");
+    a.col0[p + 1] = a.col0[p] + widths[p];
+    if (widths[p] > widest) widest = widths[p];
+  }
+  if ((size_t)m * (size_t)widest * 4 > tp->slot_bytes) return tp_fail(tp, TURQ_E_LIMIT, "a rank's share exceeds an exchange slot (turq_tp_create max_bytes)");
+  if ((uintptr_t)dev_in % 16 != 0 || (uintptr_t)dev_out % 16 != 0) return tp_fail(tp, TURQ_E_ALIGN, "buffers must be 16-byte aligned");
+  cudaError_t e = cudaSetDevice(tp->ctx->device);
+  if (e != cudaSuccess) return tp_cuda_fail(tp, e, "cudaSetDevice");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t count = m * widths[tp->rank];
+  int64_t blocks = (count / 4 + 255) / 256;
+  if (blocks > 2 * (int64_t)tp->ctx->sm_count) blocks = 2 * (int64_t)tp->ctx->sm_count;
+  if (blocks < 1) blocks = 1;
+  turq::tp_stage_kernel<<<(unsigned)blocks, 256, 0, s>>>(dev_in, slot0(tp, tp->rank), tp->slot_bytes / 4, counter_of(tp), count);
+  tp->ctx->launches++;
+  a.m = m;
+  a.n_total = a.col0[tp->world];
+  a.out = dev_out;
+  // the same grid on every rank: it depends on (world, m) only
+  const int grid = grid_for((int64_t)tp->world * m * turq::TP_THREADS, turq::TP_MAX_BLOCKS);
+  turq::tp_allgather_kernel<<<grid, turq::TP_THREADS, 0, s>>>(a);
+  tp->ctx->launches++;
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return tp_cuda_fail(tp, e, "all-gather launch");
+  return TURQ_OK;
+}
+
+int32_t turq_qmatmul_rowparallel(turq_tp* tp, const turq_qtensor* qt, const void* dev_x, int32_t x_dtype, int64_t m,
+                                 float* dev_y, int32_t mode, const float* dev_bias, void* stream) {
+  int32_t st = check_ready(tp);
+  if (st != TURQ_OK) return st;
+  turq_ctx* ctx = tp->ctx;
+  if (!qt || !dev_x || !dev_y) return tp_fail(tp, TURQ_E_INVALID_ARG, "null argument");
+  if (m <= 0 || m > INT32_MAX / 2) return tp_fail(tp, TURQ_E_SHAPE, "m out of range");
+  const int64_t count = m * qt->n_rows;
+  if ((size_t)count * 4 > tp->slot_bytes) return tp_fail(tp, TURQ_E_LIMIT, "m x out-features exceeds an exchange slot (turq_tp_create max_bytes)");
+  if ((uintptr_t)dev_y % 16 != 0) return tp_fail(tp, TURQ_E_ALIGN, "dev_y must be 16-byte aligned");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  float* s0 = slot0(tp, tp->rank);
+  float* s1 = s0 + tp->slot_bytes / 4;
+  float* staged = nullptr;
+  st = turq::qmatmul_for_exchange(ctx, qt, dev_x, x_dtype, m, s0, s1, counter_of(tp), mode, s, &staged);
+  if (st != TURQ_OK) return st;
+  if (staged) {
+    int64_t blocks = (count / 4 + 255) / 256;
+    if (blocks > 2 * (int64_t)ctx->sm_count) blocks = 2 * (int64_t)ctx->sm_count;
+    if (blocks < 1) blocks = 1;
+    turq::tp_stage_kernel<<<(unsigned)blocks, 256, 0, s>>>(staged, s0, tp->slot_bytes / 4, counter_of(tp), count);
+    ctx->launches++;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return tp_cuda_fail(tp, e, "stage launch");
+  }
+  return launch_reduce(tp, count, qt->n_rows, dev_bias, dev_y, s);
+}
+
+}  // extern "C"

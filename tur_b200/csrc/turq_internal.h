@@ -84,10 +84,12 @@ struct GemvPart {
   float* y;
   const float* bias;
   int dtype;  // TQ_* of this part's tiles; 0 = the launch's dtype argument
+  float* y_alt = nullptr;  // with y_toggle: the output buffer to use when (*y_toggle + 1) is odd
 };
 cudaError_t launch_gemv_int8_multi(int dtype, const GemvPart* parts, int nparts, int64_t k, const void* x,
                                    int x_dtype, uint8_t* act_scratch, int64_t m, uint8_t* workspace, int* status,
-                                   int sm_count, cudaStream_t s, int* launches, bool x_remote = false);
+                                   int sm_count, cudaStream_t s, int* launches, bool x_remote = false,
+                                   const unsigned* y_toggle = nullptr);
 // y[m, n] = x . dequant(W)^T with f32 FMAs on exact f32 weights.
 cudaError_t launch_gemv_f32(int dtype, const uint8_t* tiles, int64_t n_rows, int64_t k,
                             const void* x, int x_dtype, int64_t m, float* y, const float* bias,
@@ -100,5 +102,16 @@ cudaError_t launch_gemm_tc(int dtype, const uint8_t* tiles, int64_t n_rows, int6
                            const void* x, int x_dtype, int64_t m, float* y, const float* bias,
                            uint8_t* scratch, int sm_count, cudaStream_t s, int* launches,
                            int* dev_status_word);
+
+// QMatMul (no bias) whose result has to land in one of two buffers picked on the device: s1 when
+// (*toggle + 1) is odd, else s0 (the exchange slots of tp.cu). In the integer scheme the GEMV's
+// epilogue writes there itself and *staged comes back null; the other schemes compute into
+// context memory, returned in *staged, which the caller still has to copy into the slot.
+}  // namespace turq
+struct turq_ctx;
+struct turq_qtensor;
+namespace turq {
+int32_t qmatmul_for_exchange(turq_ctx* ctx, const turq_qtensor* qt, const void* dev_x, int32_t x_dtype, int64_t m, float* s0,
+                             float* s1, const unsigned* toggle, int32_t mode, cudaStream_t s, float** staged);
 
 }  // namespace turq

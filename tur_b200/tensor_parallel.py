@@ -118,6 +118,101 @@ def gather_columns(y_local, n_total: int, tp: int, row_unit: int, group=None):
     return torch.cat([o[:, : c * row_unit] for o, (_, c) in zip(out, parts)], dim=1)
 
 
+class TPGroup:
+    """The ranks of one tensor-parallel group (one process per GPU on one node), exchanging
+    through peer memory with the library's own kernels (include/turq.h, turq_tp_*): all-reduce
+    behind the row-parallel linears, all-gather behind the column-parallel head. No NCCL call is
+    made after construction, so a whole sharded pass can be captured in a CUDA graph.
+
+    Construction is collective: every rank exports a handle and receives everybody's through
+    `process_group` (torch.distributed, any backend). `loopback=True` builds a single-process
+    group whose other ranks are local stand-ins (tests)."""
+
+    def __init__(self, rank: int, world: int, max_bytes: int, ctx=None, process_group=None, loopback: bool = False):
+        import ctypes
+        import torch
+        from . import _lib
+        from .quantized import context
+        self._lib, self._ct = _lib.load(), ctypes
+        self.ctx = ctx or context()
+        self.rank, self.world = rank, world
+        h = ctypes.c_void_p()
+        self.ctx.check(self._lib.turq_tp_create(self.ctx.handle, rank, world, max_bytes, ctypes.byref(h)))
+        self._h = h
+        if world == 1:
+            return
+        if loopback:
+            self.ctx.check(self._lib.turq_tp_connect_loopback(h))
+            return
+        import torch.distributed as dist
+        blob = (ctypes.c_uint8 * 64)()
+        self.ctx.check(self._lib.turq_tp_export(h, blob))
+        mine = bytes(blob)
+        everyone = [None] * world
+        dist.all_gather_object(everyone, mine, group=process_group)
+        joined = (ctypes.c_uint8 * (64 * world)).from_buffer_copy(b"".join(everyone))
+        self.ctx.check(self._lib.turq_tp_connect(h, joined))
+        dist.barrier(group=process_group)
+        torch.cuda.synchronize()
+
+    def close(self) -> None:
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.turq_tp_destroy(h)
+
+    __del__ = close
+
+    def _stream(self):
+        import torch
+        return self._ct.c_void_p(torch.cuda.current_stream(self.ctx.device).cuda_stream)
+
+    def set_wait_limit(self, cycles: int) -> None:
+        self.ctx.check(self._lib.turq_tp_set_wait_limit(self._h, cycles))
+
+    def reset(self) -> None:
+        self.ctx.check(self._lib.turq_tp_reset(self._h))
+
+    def allreduce(self, x, out=None):
+        """Sum over the ranks, added in rank order on every rank (f32, contiguous)."""
+        import torch
+        out = torch.empty_like(x) if out is None else out
+        self.ctx.check(self._lib.turq_tp_allreduce(self._h, self._ct.c_void_p(x.data_ptr()), self._ct.c_void_p(out.data_ptr()),
+                                                   x.numel(), self._stream()))
+        return out
+
+    def allgather(self, x, widths: Sequence[int], out=None):
+        """x [m, widths[rank]] -> [m, sum(widths)] on every rank."""
+        import torch
+        m = x.shape[0]
+        out = torch.empty((m, sum(widths)), dtype=torch.float32, device=x.device) if out is None else out
+        w = (self._ct.c_int64 * self.world)(*widths)
+        self.ctx.check(self._lib.turq_tp_allgather(self._h, self._ct.c_void_p(x.data_ptr()), m, w, self._ct.c_void_p(out.data_ptr()),
+                                                   self._stream()))
+        return out
+
+    def qmatmul_rowparallel(self, mm, x, bias=None, mode=None, out=None):
+        """Row-parallel linear: this rank's column range of the weight times its slice of the
+        activations, summed over the ranks (+ bias). mm is a tur_b200.QMatMul on the shard."""
+        import torch
+        from .quantized import _TORCH_TO_GGML, Mode
+        qt = mm.qtensor
+        n, k = qt.shape()
+        x2 = x.reshape(-1, k).contiguous()
+        m = x2.shape[0]
+        out = torch.empty((m, n), dtype=torch.float32, device=x.device) if out is None else out
+        mode = (mm.mode if mode is None else mode)
+        self.ctx.check(self._lib.turq_qmatmul_rowparallel(
+            self._h, qt._h, self._ct.c_void_p(x2.data_ptr()), int(_TORCH_TO_GGML[x2.dtype]), m, self._ct.c_void_p(out.data_ptr()),
+            int(mode), self._ct.c_void_p(bias.data_ptr()) if bias is not None else None, self._stream()))
+        return out
+
+    def loopback_fill(self, peer: int, data=None, signal: bool = True) -> None:
+        """Tests: play rank `peer`'s part for the next call (its data and, with `signal`, its flags)."""
+        ptr = self._ct.c_void_p(data.data_ptr()) if data is not None else None
+        self.ctx.check(self._lib.turq_tp_loopback_fill(self._h, peer, ptr, data.numel() if data is not None else 0,
+                                                       1 if signal else 0, self._stream()))
+
+
 def row_unit_for(w: Weight, head_dim: Optional[int] = None) -> int:
     """Split unit of a weight inside a decoder layer: whole heads for attention projections
     (and the matching column blocks of attn_output), 256-wide blocks for the MLP."""
