@@ -200,6 +200,42 @@ int32_t turq_qmatmul_static(turq_ctx* ctx, const turq_qtensor* qt, const void* d
                             int32_t x_dtype, int64_t m, float* dev_y, const float* dev_bias,
                             void* stream);
 
+/* ---- Fused neighbours of the linears
+
+ * The MLP's first half (src/models/qwen3.rs:160-166: x.apply(gate_proj).apply(act_fn) *
+ * x.apply(up_proj)) as one call: dev_out[m, n] = silu(x . Wg^T) * (x . Wu^T), silu(v) =
+ * v / (1 + exp(-v)). In the integer scheme, for weights of one type, this is ONE kernel launch
+ * over the interleaved row-tiles of both weights whose epilogue applies SiLU and the product;
+ * the two [m, n] intermediates are never written. Other cases compute both products into
+ * context memory and finish with an elementwise launch. */
+int32_t turq_qmatmul_swiglu(turq_ctx* ctx, const turq_qtensor* gate, const turq_qtensor* up, const void* dev_x,
+                            int32_t x_dtype, int64_t m, float* dev_out, int32_t mode, void* stream);
+
+/* RMSNorm feeding linears (src/models/qwen3.rs:633-638: ln1 -> attn_q|k|v, ln2 -> ffn_gate|up;
+ * candle_nn::RmsNorm behind src/models/layers/norm.rs:25-41): h = x / sqrt(mean(x^2) + eps) *
+ * weight per row in f32, then turq_qmatmul_multi on h. One prologue launch normalises and writes
+ * the quantized activation planes the GEMV reads; h itself is only written when dev_h_out (f32
+ * [m, k]) is given. dev_norm_weight holds k f32 values. */
+int32_t turq_rmsnorm_qmatmul_multi(turq_ctx* ctx, int32_t count, const turq_qtensor* const* qts, const void* dev_x,
+                                   int32_t x_dtype, int64_t m, const float* dev_norm_weight, float eps,
+                                   float* dev_h_out, float* const* dev_ys, int32_t mode,
+                                   const float* const* dev_biases, void* stream);
+
+/* The k largest values of every row with their ids, best first, equal values by lower id (what a
+ * sequential arg-max scan returns; NaN ranks lowest). dev_vals is [m, n]; ids are the positions
+ * plus id_offset, or dev_ids[m, n] when given (merging candidates of several shards). k <= 64.
+ * Rows with fewer than k candidates are padded with (-inf, INT32_MAX). */
+int32_t turq_topk(turq_ctx* ctx, const float* dev_vals, const int32_t* dev_ids, int64_t m, int64_t n, int32_t k,
+                  int32_t id_offset, float* dev_out_vals, int32_t* dev_out_ids, void* stream);
+/* lm_head followed by sampling's first step (src/backend/engine.rs:528-529 single request,
+ * :810-824 batched: logits of the last position -> LogitsProcessor::sample, tokenizer.rs:9-29):
+ * the head's product and the k best (logit, token id) pairs per row in one call; greedy decoding
+ * is k = 1. The logits stay in context memory unless dev_logits ([m, n_rows] f32) is given.
+ * id_offset is the first vocabulary row of a sharded head. */
+int32_t turq_lm_head_topk(turq_ctx* ctx, const turq_qtensor* qt, const void* dev_x, int32_t x_dtype, int64_t m,
+                          int32_t k, int32_t id_offset, float* dev_out_vals, int32_t* dev_out_ids,
+                          float* dev_logits, int32_t mode, void* stream);
+
 /* ---- Tensor parallelism inside one node (no counterpart in the reference, which is
  * single-device: src/models/layers/norm.rs:50 passes Shard::default() everywhere).
  *

@@ -32,8 +32,9 @@ def test_single_rank_group_is_the_plain_matmul_and_replays_in_a_graph(tq):
     want = mm.forward(x, bias=bias, mode=tq.Mode.INT8_ACT)
     for _ in range(3):                                       # consecutive calls alternate the exchange slot
         assert torch.equal(g.qmatmul_rowparallel(mm, x, bias=bias, mode=tq.Mode.INT8_ACT), want)
-    assert torch.equal(g.allreduce(x), x)
-    assert torch.equal(g.allgather(x, [k]), x)
+    xs = x[:, :n].contiguous()                               # a slot holds m * n floats
+    assert torch.equal(g.allreduce(xs), xs)
+    assert torch.equal(g.allgather(xs, [n]), xs)
     # tensor-core scheme goes through the staging copy
     x64 = torch.from_numpy(rng.standard_normal((40, k)).astype(np.float32)).cuda()
     g2 = TPGroup(0, 1, 40 * n * 4)

@@ -8,7 +8,9 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libturq.so")
+# TURQ_LIBRARY_PATH points at another build of the same library (e.g. one compiled with
+# -DTURQ_TUNING or other Q8_K switches); default: the in-tree build
+LIB_PATH = os.environ.get("TURQ_LIBRARY_PATH") or os.path.join(_HERE, "libturq.so")
 
 c_i32, c_i64, c_sz, c_vp = ctypes.c_int32, ctypes.c_int64, ctypes.c_size_t, ctypes.c_void_p
 PP = ctypes.POINTER(c_vp)
@@ -43,6 +45,10 @@ SIGNATURES = {
     "turq_qmatmul_host": (c_i32, [c_vp, c_vp, c_vp, c_i64, c_vp, c_i32, c_vp]),
     "turq_qmatmul_multi_host": (c_i32, [c_vp, c_i32, c_vp, c_vp, c_i64, c_vp, c_i32, c_vp]),
     "turq_qmatmul_static": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i64, c_vp, c_vp, c_vp]),
+    "turq_qmatmul_swiglu": (c_i32, [c_vp, c_vp, c_vp, c_vp, c_i32, c_i64, c_vp, c_i32, c_vp]),
+    "turq_rmsnorm_qmatmul_multi": (c_i32, [c_vp, c_i32, c_vp, c_vp, c_i32, c_i64, c_vp, ctypes.c_float, c_vp, c_vp, c_i32, c_vp, c_vp]),
+    "turq_topk": (c_i32, [c_vp, c_vp, c_vp, c_i64, c_i64, c_i32, c_i32, c_vp, c_vp, c_vp]),
+    "turq_lm_head_topk": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i64, c_i32, c_i32, c_vp, c_vp, c_vp, c_i32, c_vp]),
     "turq_tp_create": (c_i32, [c_vp, c_i32, c_i32, c_sz, PP]),
     "turq_tp_export": (c_i32, [c_vp, c_vp]),
     "turq_tp_connect": (c_i32, [c_vp, c_vp]),

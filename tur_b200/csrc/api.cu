@@ -644,4 +644,11 @@ int32_t qmatmul_for_exchange(turq_ctx* ctx, const turq_qtensor* qt, const void* 
   return TURQ_OK;
 }
 
+// ---- helpers of this translation unit, shared with the fused entries (fused.cu)
+int32_t api_fail(turq_ctx* ctx, int32_t st, const char* msg) { return fail(ctx, st, "%s", msg); }
+int32_t api_cuda_fail(turq_ctx* ctx, cudaError_t e, const char* what) { return cuda_fail(ctx, e, what); }
+int32_t api_ensure_scratch(turq_ctx* ctx, size_t bytes) { return ensure(ctx, &ctx->scratch, &ctx->scratch_bytes, bytes); }
+int32_t api_ensure_tmp(turq_ctx* ctx, size_t bytes) { return ensure(ctx, &ctx->tmp, &ctx->tmp_bytes, bytes); }
+int32_t api_auto_mode(const turq_ctx* ctx, int64_t n_rows, int64_t n_cols, int64_t m) { return auto_mode(ctx, n_rows, n_cols, m); }
+
 }  // namespace turq

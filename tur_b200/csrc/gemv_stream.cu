@@ -114,6 +114,8 @@ struct StreamArgs {
                                   // parity selects the exchange slot this launch has to fill
   const float* bias[MAX_PARTS];
   int nparts;
+  int interleave;       // 1: two parts of equal shape (ffn_gate, ffn_up) walked as row-tiles g0, u0, g1, u1, ...;
+                        // the epilogue keeps silu-input g_t and writes silu(g_t) * u_t to y[0] only
   int ktiles, k;
   int KU;               // units (tiles; groups of 4 tiles for Q8_0) per row-tile
   int split_q, split_r; // CTA b owns units [b*q + min(b,r), (b+1)*q + min(b+1,r)), clamped to total_units
@@ -276,10 +278,16 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
         if (!mbar_wait(&empty[slot], ph ^ 1u, abort_flag)) break;
         // one copy per consumer warp (its tile, or its group of Q8_0 tiles), each completing on
         // that warp's own barrier: a warp starts as soon as its bytes are there
-        int part = 0;
-        while (part + 1 < a.nparts && w.rt >= a.rt_begin[part + 1]) part++;
+        int part = 0, rt_in_part;
+        if (a.interleave) {
+          part = w.rt & 1;
+          rt_in_part = w.rt >> 1;
+        } else {
+          while (part + 1 < a.nparts && w.rt >= a.rt_begin[part + 1]) part++;
+          rt_in_part = w.rt - a.rt_begin[part];
+        }
         const int tb = (MIXED && a.part_alt[part]) ? TB2 : TB;
-        const uint8_t* src = a.tiles[part] + ((int64_t)(w.rt - a.rt_begin[part]) * a.ktiles + (int64_t)w.ku * GROUP) * tb;
+        const uint8_t* src = a.tiles[part] + ((int64_t)rt_in_part * a.ktiles + (int64_t)w.ku * GROUP) * tb;
         uint8_t* dst = smem + sp.ring + slot * a.stage_bytes;
         for (int i = 0; i < n; i++) {
           int nt = a.ktiles - (w.ku + i) * GROUP;
@@ -457,6 +465,10 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
     int seg_ka = w.ku;
     int rs = 0;
     uint32_t rph = 0;
+    constexpr int EPL_ALL = (MG * 128 + 31) / 32;
+    float gate_keep[EPL_ALL];  // interleaved launches: the gate row-tile's sums until its up row-tile closes
+#pragma unroll
+    for (int j = 0; j < EPL_ALL; j++) gate_keep[j] = 0.f;
     while (!w.done()) {
       const int n = w.count();
       const int rt = w.rt;
@@ -468,12 +480,17 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
       const bool whole = owner && kb == KU;
       const int rt_end = (rt + 1) * KU;
       const int ncols = a.rows < 8 * MG ? a.rows : 8 * MG;
-      int part = 0;
-      while (part + 1 < a.nparts && rt >= a.rt_begin[part + 1]) part++;
+      int part = 0, rt_local;
+      if (a.interleave) {
+        part = rt & 1;
+        rt_local = rt >> 1;
+      } else {
+        while (part + 1 < a.nparts && rt >= a.rt_begin[part + 1]) part++;
+        rt_local = rt - a.rt_begin[part];
+      }
       const int64_t part_rows = a.n_rows[part];
-      float* const part_y = use_alt ? a.y_alt[part] : a.y[part];
+      float* const part_y = a.interleave ? a.y[0] : (use_alt ? a.y_alt[part] : a.y[part]);
       const float* const part_bias = a.bias[part];
-      const int rt_local = rt - a.rt_begin[part];
       constexpr int EPL = (MG * 128 + 31) / 32;  // output elements per lane
       float other[EPL];
 #pragma unroll
@@ -520,7 +537,17 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
             const int64_t nn = (int64_t)rt_local * TQ_TILE_ROWS + row;
             if (nn < part_rows) {
               if (part_bias) s += part_bias[nn];
-              part_y[(int64_t)col * part_rows + nn] = s;
+              if (a.interleave) {
+                // the split gives every CTA whole (gate, up) pairs, gate first
+                if (part == 0) {
+                  gate_keep[j] = s;
+                } else {
+                  const float gv = gate_keep[j];
+                  part_y[(int64_t)col * part_rows + nn] = (gv / (1.f + expf(-gv))) * s;
+                }
+              } else {
+                part_y[(int64_t)col * part_rows + nn] = s;
+              }
             }
           }
         }
@@ -607,7 +634,8 @@ static cudaError_t launch_one(StreamArgs a, int grid, int smem_bytes, cudaStream
 template <int DT, int DT2 = DT>
 static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const void* x, int x_dtype,
                              uint8_t* act_scratch, int64_t m, uint8_t* workspace, int* status, int sm_count,
-                             cudaStream_t s, int* launches, bool x_remote, const unsigned* y_toggle) {
+                             cudaStream_t s, int* launches, bool x_remote, const unsigned* y_toggle, bool planes_ready,
+                             bool interleave = false) {
   constexpr bool MIXED = DT2 != DT;
   constexpr int GROUP = TileGeom<DT>::GROUP;
   constexpr int UNIT_BYTES = (TileGeom<DT2>::BYTES > TileGeom<DT>::BYTES ? TileGeom<DT2>::BYTES : TileGeom<DT>::BYTES) * GROUP;
@@ -619,6 +647,7 @@ static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const
     rt_begin[p + 1] = rt_begin[p] + (int)((parts[p].n_rows + TQ_TILE_ROWS - 1) / TQ_TILE_ROWS);
   const int64_t T = (int64_t)rt_begin[nparts] * KU;
   if (T > (int64_t)1 << 30) return cudaErrorInvalidValue;
+  if (interleave && (MIXED || nparts != 2 || parts[0].n_rows != parts[1].n_rows)) return cudaErrorNotSupported;
   // The tile split (hence the summation order) must not depend on M: always two CTAs per SM.
   static const int cps_env = tuning_env("TURQ_GEMV_CPS", 0);
   const int ctas_per_sm = cps_env > 0 ? cps_env : 2;
@@ -643,7 +672,9 @@ static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const
   // they fit beside a two-stage ring) or read from global memory by the MMA loop.
   // x_remote: x lives in mapped host memory - every CTA reading it over the bus would cost far
   // more than the one pass of the quantization launch, so the planes are always staged.
-  int act_mode = (gemv_int8_fuses_act(DT, m, k) && !x_remote) ? ACT_FUSED : ACT_GLOBAL;
+  // planes_ready: a preceding launch of the caller (RMSNorm prologue) already left the planes of
+  // these rows in act_scratch.
+  int act_mode = (gemv_int8_fuses_act(DT, m, k) && !x_remote && !planes_ready) ? ACT_FUSED : ACT_GLOBAL;
   {
     const int rows0 = (int)(m < 32 ? m : 32), mg0 = rows0 <= 8 ? 1 : rows0 <= 16 ? 2 : 4;
     if (act_mode == ACT_FUSED && stages_for(true, ctas_per_sm, rows0, mg0) < 2) act_mode = ACT_GLOBAL;
@@ -658,11 +689,14 @@ static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const
   const int slots = sm_count * ctas_per_sm;
   const int row_tiles_all = rt_begin[nparts];
   static const int split_env = tuning_env("TURQ_GEMV_SPLIT", -1);
-  const GemvSplit split = plan_gemv_split(row_tiles_all, KU, slots, split_env);
+  // interleaved (gate, up) launches are split in whole pairs of row-tiles, and only when whole
+  // pairs keep the CTA slots busy: a pair cut between CTAs would need both halves handed over
+  GemvSplit split = interleave ? plan_gemv_split(row_tiles_all / 2, 2 * KU, slots, -1) : plan_gemv_split(row_tiles_all, KU, slots, split_env);
+  if (interleave && !split.aligned) return cudaErrorNotSupported;
   const int grid = split.grid, split_q = split.split_q, split_r = split.split_r;
   const size_t x_es = x_dtype == TQ_BF16 ? 2 : 4;
   ActPackPlan plan = plan_act_pack(fmt, m, k);
-  if (!fused) {
+  if (!fused && !planes_ready) {
     cudaError_t e = launch_quantize_act_pack(fmt, x, x_dtype, m, k, act_scratch, s);
     if (launches) (*launches)++;
     if (e != cudaSuccess) return e;
@@ -681,6 +715,7 @@ static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const
     }
     for (int p = 0; p <= nparts; p++) a.rt_begin[p] = rt_begin[p];
     a.y_toggle = y_toggle;
+    a.interleave = interleave ? 1 : 0;
     a.nparts = nparts;
     a.ktiles = ktiles;
     a.k = (int)k;
@@ -729,11 +764,11 @@ static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const
   return cudaSuccess;
 }
 
-#define TQ_LAUNCH_ARGS k, x, x_dtype, act_scratch, m, workspace, status, sm_count, s, launches, x_remote, y_toggle
+#define TQ_LAUNCH_ARGS k, x, x_dtype, act_scratch, m, workspace, status, sm_count, s, launches, x_remote, y_toggle, planes_ready
 
 static cudaError_t launch_one_type(int dtype, const GemvPart* parts, int nparts, int64_t k, const void* x, int x_dtype,
                                    uint8_t* act_scratch, int64_t m, uint8_t* workspace, int* status, int sm_count,
-                                   cudaStream_t s, int* launches, bool x_remote, const unsigned* y_toggle) {
+                                   cudaStream_t s, int* launches, bool x_remote, const unsigned* y_toggle, bool planes_ready) {
   switch (dtype) {
     case TQ_Q8_0: return launch_dt<TQ_Q8_0>(parts, nparts, TQ_LAUNCH_ARGS);
     case TQ_Q4_K: return launch_dt<TQ_Q4_K>(parts, nparts, TQ_LAUNCH_ARGS);
@@ -747,7 +782,7 @@ static cudaError_t launch_one_type(int dtype, const GemvPart* parts, int nparts,
 // together with Q6_K parts too, where the mixed kernel exists; anything else one launch per type.
 cudaError_t launch_gemv_int8_multi(int dtype, const GemvPart* parts, int nparts, int64_t k, const void* x, int x_dtype,
                                    uint8_t* act_scratch, int64_t m, uint8_t* workspace, int* status, int sm_count,
-                                   cudaStream_t s, int* launches, bool x_remote, const unsigned* y_toggle) {
+                                   cudaStream_t s, int* launches, bool x_remote, const unsigned* y_toggle, bool planes_ready) {
   if (nparts < 1 || nparts > MAX_PARTS) return cudaErrorInvalidValue;
   GemvPart p[MAX_PARTS];
   int types[MAX_PARTS], ntypes = 0;
@@ -778,14 +813,34 @@ cudaError_t launch_gemv_int8_multi(int dtype, const GemvPart* parts, int nparts,
   }
   return cudaSuccess;
 }
-#undef TQ_LAUNCH_ARGS
+#define TQ_LAUNCH_ARGS_DECL k, x, x_dtype, act_scratch, m, workspace, status, sm_count, s, launches, x_remote, y_toggle, planes_ready
+
+// silu(x . Wg^T) * (x . Wu^T) in one launch (two weights of one type and shape). Returns
+// cudaErrorNotSupported, before anything is launched, where the interleaved split does not apply.
+cudaError_t launch_gemv_int8_swiglu(int dtype, const uint8_t* gate_tiles, const uint8_t* up_tiles, int64_t n_rows, int64_t k,
+                                    const void* x, int x_dtype, uint8_t* act_scratch, int64_t m, float* out, uint8_t* workspace,
+                                    int* status, int sm_count, cudaStream_t s, int* launches) {
+  GemvPart parts[2] = {{gate_tiles, n_rows, out, nullptr, dtype, nullptr}, {up_tiles, n_rows, out, nullptr, dtype, nullptr}};
+  const bool x_remote = false, planes_ready = false;
+  const unsigned* y_toggle = nullptr;
+  switch (dtype) {
+    case TQ_Q8_0: return launch_dt<TQ_Q8_0>(parts, 2, TQ_LAUNCH_ARGS_DECL, true);
+    case TQ_Q4_K: return launch_dt<TQ_Q4_K>(parts, 2, TQ_LAUNCH_ARGS_DECL, true);
+    case TQ_Q5_K: return launch_dt<TQ_Q5_K>(parts, 2, TQ_LAUNCH_ARGS_DECL, true);
+    case TQ_Q6_K: return launch_dt<TQ_Q6_K>(parts, 2, TQ_LAUNCH_ARGS_DECL, true);
+    default: return cudaErrorInvalidValue;
+  }
+}
 
 cudaError_t launch_gemv_int8(int dtype, const uint8_t* tiles, int64_t n_rows, int64_t k, const void* x, int x_dtype,
                              uint8_t* act_scratch, int64_t m, float* y, const float* bias, uint8_t* workspace,
                              int* status, int sm_count, cudaStream_t s, int* launches) {
   GemvPart part{tiles, n_rows, y, bias, dtype, nullptr};
   return launch_gemv_int8_multi(dtype, &part, 1, k, x, x_dtype, act_scratch, m, workspace, status, sm_count, s, launches, false,
-                                nullptr);
+                                nullptr, false);
 }
+
+#undef TQ_LAUNCH_ARGS
+#undef TQ_LAUNCH_ARGS_DECL
 
 }  // namespace turq

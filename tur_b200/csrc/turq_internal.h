@@ -77,7 +77,8 @@ cudaError_t launch_gemv_int8(int dtype, const uint8_t* tiles, int64_t n_rows, in
 // The same for several weights of one in-feature count that share x: one launch over the
 // concatenated rows (q|k|v, gate|up) per weight type - and a single one for Q4_K or Q5_K parts
 // beside Q6_K parts at up to 8 rows - each part with its own output and bias. x_remote: x is
-// mapped host memory; it is then read exactly once, by the quantization launch.
+// mapped host memory; it is then read exactly once, by the quantization launch. planes_ready: the
+// caller's own prologue launch already wrote the quantized planes of these rows to act_scratch.
 struct GemvPart {
   const uint8_t* tiles;
   int64_t n_rows;
@@ -89,7 +90,12 @@ struct GemvPart {
 cudaError_t launch_gemv_int8_multi(int dtype, const GemvPart* parts, int nparts, int64_t k, const void* x,
                                    int x_dtype, uint8_t* act_scratch, int64_t m, uint8_t* workspace, int* status,
                                    int sm_count, cudaStream_t s, int* launches, bool x_remote = false,
-                                   const unsigned* y_toggle = nullptr);
+                                   const unsigned* y_toggle = nullptr, bool planes_ready = false);
+// out[m, n] = silu(x . Wg^T) * (x . Wu^T) as ONE integer-scheme launch over the row-tiles of both
+// weights interleaved (same type and shape). cudaErrorNotSupported = not applicable, nothing launched.
+cudaError_t launch_gemv_int8_swiglu(int dtype, const uint8_t* gate_tiles, const uint8_t* up_tiles, int64_t n_rows, int64_t k,
+                                    const void* x, int x_dtype, uint8_t* act_scratch, int64_t m, float* out, uint8_t* workspace,
+                                    int* status, int sm_count, cudaStream_t s, int* launches);
 // y[m, n] = x . dequant(W)^T with f32 FMAs on exact f32 weights.
 cudaError_t launch_gemv_f32(int dtype, const uint8_t* tiles, int64_t n_rows, int64_t k,
                             const void* x, int x_dtype, int64_t m, float* y, const float* bias,
@@ -111,6 +117,11 @@ cudaError_t launch_gemm_tc(int dtype, const uint8_t* tiles, int64_t n_rows, int6
 struct turq_ctx;
 struct turq_qtensor;
 namespace turq {
+int32_t api_fail(turq_ctx* ctx, int32_t st, const char* msg);
+int32_t api_cuda_fail(turq_ctx* ctx, cudaError_t e, const char* what);
+int32_t api_ensure_scratch(turq_ctx* ctx, size_t bytes);  // the context's growable activation scratch
+int32_t api_ensure_tmp(turq_ctx* ctx, size_t bytes);      // the context's growable result staging
+int32_t api_auto_mode(const turq_ctx* ctx, int64_t n_rows, int64_t n_cols, int64_t m);
 int32_t qmatmul_for_exchange(turq_ctx* ctx, const turq_qtensor* qt, const void* dev_x, int32_t x_dtype, int64_t m, float* s0,
                              float* s1, const unsigned* toggle, int32_t mode, cudaStream_t s, float** staged);
 

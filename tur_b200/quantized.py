@@ -255,16 +255,17 @@ class QMatMul:
         lib = _lib.load()
         ctx = qt._ctx
         if not x.is_cuda:
-            x2 = x.reshape(-1, k).to(torch.float32).contiguous()
+            # (the common case - a dense f32 matrix - skips the conversions: this entry is called
+            # once per linear and its host-side cost is part of every round trip)
+            x2 = x if (x.dim() == 2 and x.dtype is torch.float32 and x.is_contiguous()) else x.reshape(-1, k).to(torch.float32).contiguous()
             if out is not None and (out.is_cuda or out.dtype != torch.float32 or not out.is_contiguous()
                                     or out.numel() != x2.shape[0] * n):
                 raise TurqError(1, "out must be a contiguous f32 host tensor of m x n elements when x is a host tensor")
             y = out if out is not None else torch.empty((x2.shape[0], n), dtype=torch.float32, pin_memory=x2.is_pinned())
             b = bias.to(torch.float32).contiguous() if bias is not None else None
-            ctx.check(lib.turq_qmatmul_host(ctx.handle, qt._h, ctypes.c_void_p(x2.data_ptr()), x2.shape[0],
-                                            ctypes.c_void_p(y.data_ptr()), int(mode),
-                                            ctypes.c_void_p(b.data_ptr()) if b is not None else None))
-            return y.reshape(*lead, n)
+            ctx.check(lib.turq_qmatmul_host(ctx.handle, qt._h, x2.data_ptr(), x2.shape[0], y.data_ptr(), int(mode),
+                                            b.data_ptr() if b is not None else None))
+            return y if y.shape == (*lead, n) else y.reshape(*lead, n)
         if x.dtype not in (torch.float32, torch.bfloat16):
             x = x.to(torch.float32)
         x2 = x.reshape(-1, k).contiguous()
@@ -302,20 +303,20 @@ class QMatMul:
         lead = tuple(x.shape[:-1])
         if not x.is_cuda:
             # host tensors: one round trip for all the weights (turq_qmatmul_multi_host)
-            x2 = x.reshape(-1, k).to(torch.float32).contiguous()
+            x2 = x if (x.dim() == 2 and x.dtype is torch.float32 and x.is_contiguous()) else x.reshape(-1, k).to(torch.float32).contiguous()
             m = x2.shape[0]
             if outs is None:
                 outs = [torch.empty((m, mm.qtensor.shape()[0]), dtype=torch.float32, pin_memory=x2.is_pinned()) for mm in mms]
             for o, mm in zip(outs, mms):
                 if o.is_cuda or o.dtype != torch.float32 or not o.is_contiguous() or o.numel() != m * mm.qtensor.shape()[0]:
                     raise TurqError(1, "outs must be contiguous f32 host tensors of m x n elements when x is a host tensor")
-            ys = arr(*[ctypes.c_void_p(o.data_ptr()) for o in outs])
+            ys = arr(*[o.data_ptr() for o in outs])
             bs, keep = None, []
             if biases is not None:
                 keep = [b.to(torch.float32).contiguous() if b is not None else None for b in biases]
-                bs = arr(*[ctypes.c_void_p(b.data_ptr()) if b is not None else None for b in keep])
-            ctx.check(lib.turq_qmatmul_multi_host(ctx.handle, n, qts, ctypes.c_void_p(x2.data_ptr()), m, ys, int(mode), bs))
-            return [o.reshape(*lead, o.shape[-1]) for o in outs]
+                bs = arr(*[b.data_ptr() if b is not None else None for b in keep])
+            ctx.check(lib.turq_qmatmul_multi_host(ctx.handle, n, qts, x2.data_ptr(), m, ys, int(mode), bs))
+            return [o if o.shape == (*lead, o.shape[-1]) else o.reshape(*lead, o.shape[-1]) for o in outs]
         if x.dtype not in (torch.float32, torch.bfloat16):
             x = x.to(torch.float32)
         x2 = x.reshape(-1, k).contiguous()
@@ -339,3 +340,96 @@ class QMatMul:
         ctx.check(lib.turq_qmatmul_multi(ctx.handle, n, qts, ctypes.c_void_p(x2.data_ptr()), int(_TORCH_TO_GGML[x2.dtype]), m,
                                          ys, int(mode), bs, _stream_ptr(ctx.device)))
         return [o.reshape(*lead, o.shape[-1]) for o in outs]
+
+    # ---- fused neighbours of the linears (include/turq.h, "Fused neighbours")
+
+    @staticmethod
+    def swiglu(gate: "QMatMul", up: "QMatMul", x: torch.Tensor, mode: Mode = Mode.AUTO,
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """silu(x . Wg^T) * (x . Wu^T) (tur's Qwen3MLP, src/models/qwen3.rs:160-166), one launch in
+        the integer scheme."""
+        ctx = gate.qtensor._ctx
+        n, k = gate.qtensor.shape()
+        if x.dtype not in (torch.float32, torch.bfloat16):
+            x = x.to(torch.float32)
+        x2 = x.reshape(-1, k).contiguous()
+        _check_operand(x2, "x", ctx.device, (torch.float32, torch.bfloat16))
+        m = x2.shape[0]
+        if out is not None:
+            _check_operand(out, "out", ctx.device, (torch.float32,))
+        y = out if out is not None else torch.empty((m, n), dtype=torch.float32, device=x2.device)
+        ctx.check(_lib.load().turq_qmatmul_swiglu(ctx.handle, gate.qtensor._h, up.qtensor._h, x2.data_ptr(),
+                                                  int(_TORCH_TO_GGML[x2.dtype]), m, y.data_ptr(), int(mode), _stream_ptr(ctx.device)))
+        return y.reshape(*x.shape[:-1], n)
+
+    @staticmethod
+    def rmsnorm_forward_multi(mms: Sequence["QMatMul"], x: torch.Tensor, norm_weight: torch.Tensor, eps: float,
+                              biases: Optional[Sequence[Optional[torch.Tensor]]] = None, mode: Mode = Mode.AUTO,
+                              return_normed: bool = False):
+        """y_i = rmsnorm(x; weight, eps) . W_i^T for linears that share the normalised input
+        (ln1 -> attn_q|k|v, ln2 -> ffn_gate|up: src/models/qwen3.rs:633-638). Returns the outputs,
+        and the normalised rows too with return_normed."""
+        ctx = mms[0].qtensor._ctx
+        k = mms[0].qtensor.shape()[1]
+        if x.dtype not in (torch.float32, torch.bfloat16):
+            x = x.to(torch.float32)
+        x2 = x.reshape(-1, k).contiguous()
+        _check_operand(x2, "x", ctx.device, (torch.float32, torch.bfloat16))
+        _check_operand(norm_weight, "norm_weight", ctx.device, (torch.float32,))
+        if norm_weight.numel() != k:
+            raise TurqError(2, f"norm weight has {norm_weight.numel()} elements, the linears {k} in-features")
+        m, n = x2.shape[0], len(mms)
+        outs = [torch.empty((m, mm.qtensor.shape()[0]), dtype=torch.float32, device=x2.device) for mm in mms]
+        h = torch.empty((m, k), dtype=torch.float32, device=x2.device) if return_normed else None
+        arr = ctypes.c_void_p * n
+        bs = None
+        if biases is not None:
+            for i, b in enumerate(biases):
+                if b is not None:
+                    _check_operand(b, f"biases[{i}]", ctx.device, (torch.float32,))
+            bs = arr(*[b.data_ptr() if b is not None else None for b in biases])
+        ctx.check(_lib.load().turq_rmsnorm_qmatmul_multi(
+            ctx.handle, n, arr(*[mm.qtensor._h for mm in mms]), x2.data_ptr(), int(_TORCH_TO_GGML[x2.dtype]), m,
+            norm_weight.data_ptr(), float(eps), h.data_ptr() if h is not None else None, arr(*[o.data_ptr() for o in outs]),
+            int(mode), bs, _stream_ptr(ctx.device)))
+        lead = tuple(x.shape[:-1])
+        outs = [o.reshape(*lead, o.shape[-1]) for o in outs]
+        return (outs, h.reshape(*lead, k)) if return_normed else outs
+
+    def lm_head_topk(self, x: torch.Tensor, k: int = 1, id_offset: int = 0, mode: Optional[Mode] = None,
+                     logits_out: Optional[torch.Tensor] = None) -> tuple[torch.Tensor, torch.Tensor]:
+        """The k best (logit, token id) pairs per row of x . W^T, best first, ties to the lower id
+        (greedy decoding: k = 1). tur samples from the last position's logits
+        (src/backend/engine.rs:528-529, 810-824)."""
+        qt = self.qtensor
+        ctx = qt._ctx
+        n, kk = qt.shape()
+        if x.dtype not in (torch.float32, torch.bfloat16):
+            x = x.to(torch.float32)
+        x2 = x.reshape(-1, kk).contiguous()
+        _check_operand(x2, "x", ctx.device, (torch.float32, torch.bfloat16))
+        m = x2.shape[0]
+        vals = torch.empty((m, k), dtype=torch.float32, device=x2.device)
+        ids = torch.empty((m, k), dtype=torch.int32, device=x2.device)
+        if logits_out is not None:
+            _check_operand(logits_out, "logits_out", ctx.device, (torch.float32,))
+        ctx.check(_lib.load().turq_lm_head_topk(ctx.handle, qt._h, x2.data_ptr(), int(_TORCH_TO_GGML[x2.dtype]), m, k, id_offset,
+                                                vals.data_ptr(), ids.data_ptr(),
+                                                logits_out.data_ptr() if logits_out is not None else None,
+                                                int(self.mode if mode is None else mode), _stream_ptr(ctx.device)))
+        return vals, ids
+
+
+def topk(vals: torch.Tensor, k: int, ids: Optional[torch.Tensor] = None, id_offset: int = 0) -> tuple[torch.Tensor, torch.Tensor]:
+    """k largest per row of vals [m, n] (f32, CUDA) with their ids (positions + id_offset, or the
+    given int32 ids [m, n]): best first, ties to the lower id."""
+    ctx = context(vals.device)
+    _check_operand(vals, "vals", ctx.device, (torch.float32,))
+    if ids is not None:
+        _check_operand(ids, "ids", ctx.device, (torch.int32,))
+    m, n = vals.shape
+    ov = torch.empty((m, k), dtype=torch.float32, device=vals.device)
+    oi = torch.empty((m, k), dtype=torch.int32, device=vals.device)
+    ctx.check(_lib.load().turq_topk(ctx.handle, vals.data_ptr(), ids.data_ptr() if ids is not None else None, m, n, k, id_offset,
+                                    ov.data_ptr(), oi.data_ptr(), _stream_ptr(ctx.device)))
+    return ov, oi
