@@ -126,7 +126,7 @@ def test_topk_matches_a_stable_sort(tq, n, m, k):
 def test_lm_head_topk_and_sharded_merge(tq):
     """Greedy / top-k straight from the head, and a vocabulary-sharded head: each shard's k best
     with id offsets, merged, equal the unsharded k best."""
-    n, kdim, m, k = 20000, 1024, 3, 16
+    n, kdim, m, k = 20480, 1024, 3, 16
     w = make_weight(oracle.Q6_K, n, kdim, SEED + 77)
     qt = tq.QTensor.new(w, tq.GgmlDType.Q6K, (n, kdim))
     mm = tq.QMatMul.from_arc(qt)
@@ -142,8 +142,8 @@ def test_lm_head_topk_and_sharded_merge(tq):
     # four vocabulary shards
     cand_v, cand_i = [], []
     for r in range(4):
-        sh = tq.QMatMul.from_arc(qt.slice_rows(r * 5000, 5000))
-        v_r, i_r = sh.lm_head_topk(x, k, id_offset=r * 5000, mode=tq.Mode.INT8_ACT)
+        sh = tq.QMatMul.from_arc(qt.slice_rows(r * 5120, 5120))
+        v_r, i_r = sh.lm_head_topk(x, k, id_offset=r * 5120, mode=tq.Mode.INT8_ACT)
         cand_v.append(v_r)
         cand_i.append(i_r)
     mv, mi = tq.topk(torch.cat(cand_v, 1).contiguous(), k, ids=torch.cat(cand_i, 1).contiguous())
