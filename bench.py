@@ -263,39 +263,24 @@ class Stack:
             y = {w.name: torch.empty((m, w.n), dtype=torch.float32, device=self.dev) for w in self.weights()}
         return x, y
 
-    def make_pass(self, x, y, mode, multi=True, hints=True):
+    def make_pass(self, x, y, mode, multi=True):
         """One pass over every linear of the stack, issued as a caller integrating the library
-        would: linears that read the same x (attn_q|k|v, ffn_gate|up) as one multi-weight call,
-        and - a decoder walks its layers in a fixed order - every call preceded by the read-ahead
-        hint naming the weights of the call after it (turq_ctx_hint_next). Host tensors get no
-        hints (a synchronize separates the launches anyway)."""
+        would: linears that read the same x (attn_q|k|v, ffn_gate|up) as one multi-weight call."""
         from tur_b200 import QMatMul
-        calls = []
-        for layer in self.layers:
-            by_name = {w.name: (w, mm) for w, mm in layer}
-            for grp in GROUPS:
-                members = [by_name[n] for n in grp if n in by_name]
-                if len(members) > 1 and multi:
-                    calls.append(members)
-                else:
-                    calls.extend([mem] for mem in members)
-        if self.head:
-            calls.append([self.head])
-        hints = hints and all(t.is_cuda for t in x.values())
-        ctx = calls[0][0][1].qtensor._ctx
 
         def run():
-            for i, members in enumerate(calls):
-                if hints:
-                    ctx.hint_next([mm for _, mm in calls[(i + 1) % len(calls)]])
-                if len(members) > 1:
-                    QMatMul.forward_multi([mm for _, mm in members], x[members[0][0].source], mode=mode,
-                                          outs=[y[w.name] for w, _ in members])
-                else:
-                    w, mm = members[0]
-                    mm.forward(x[w.source], mode=mode, out=y[w.name])
-            if hints:
-                ctx.hint_next([])
+            for layer in self.layers:
+                by_name = {w.name: (w, mm) for w, mm in layer}
+                for grp in GROUPS:
+                    members = [by_name[n] for n in grp if n in by_name]
+                    if len(members) > 1 and multi:
+                        QMatMul.forward_multi([mm for _, mm in members], x[members[0][0].source], mode=mode,
+                                              outs=[y[w.name] for w, _ in members])
+                    else:
+                        for w, mm in members:
+                            mm.forward(x[w.source], mode=mode, out=y[w.name])
+            if self.head:
+                self.head[1].forward(x["hidden"], mode=mode, out=y[self.head[0].name])
         return run
 
 
@@ -394,7 +379,7 @@ def run_gpu(args):
 
     stack = Stack(wl, dev, gen="oracle", head=not args.no_head)
     x_dev, y_dev = stack.buffers(m, args.xdtype)
-    one_pass_device = stack.make_pass(x_dev, y_dev, mode, multi=not args.no_multi, hints=not args.no_hints)
+    one_pass_device = stack.make_pass(x_dev, y_dev, mode, multi=not args.no_multi)
 
     def barrier():
         if world > 1:
@@ -450,11 +435,8 @@ def run_gpu(args):
     dom = dom_ws[0]
 
     def dom_pass():
-        for li, layer in enumerate(stack.layers):
+        for layer in stack.layers:
             members = [(w, mm) for w, mm in layer if w.name in dom_names]
-            if not args.no_hints:
-                ctx.hint_next([mm for w, mm in stack.layers[(li + 1) % len(stack.layers)] if w.name in dom_names]
-                              if len(members) > 1 and not args.no_multi else [])
             if len(members) > 1 and not args.no_multi:
                 QMatMul.forward_multi([mm for _, mm in members], x_dev[dom.source], mode=mode, outs=[y_dev[w.name] for w, _ in members])
             else:
@@ -528,7 +510,7 @@ def run_gpu(args):
             "mode": mode.name, "x_dtype": args.xdtype, "weight_bytes_per_step_per_gpu": pass_bytes,
             "tflops": pass_flops * world * args.steps / (ms * 1e-3) / 1e12, "parallelism": f"replicas x{world}",
             "l2": "weights per pass exceed L2 (distinct buffers per layer); CUDA-graph replay per step",
-            "multi_weight_launch": not args.no_multi, "read_ahead_hints": not args.no_hints,
+            "multi_weight_launch": not args.no_multi,
             "tokens_per_s": m * world * args.steps / (ms * 1e-3),
         },
         "e2e": None if e2e_ms is None else {
@@ -868,7 +850,6 @@ def main():
     ap.add_argument("--cpu-steps", type=int, default=20, help="steps of about half a second each in the cpu_baseline leg")
     ap.add_argument("--tp", action="store_true", help="tensor-parallel over all ranks (the sharded cfg5 workload)")
     ap.add_argument("--no-multi", action="store_true", help="one launch per weight (no q|k, gate|up multi-weight launches)")
-    ap.add_argument("--no-hints", action="store_true", help="do not give the library read-ahead hints (turq_ctx_hint_next)")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of the timed pass's outputs")
     ap.add_argument("--no-extras", action="store_true", help="skip the sweep / prefill / other-config objects of the default run")
     ap.add_argument("--nccl", action="store_true", help="tensor-parallel arm: NCCL collectives and eager launches instead of the "

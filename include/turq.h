@@ -99,15 +99,6 @@ const char* turq_last_error(const turq_ctx* ctx);
  * its largest call reserves once, up front: afterwards no call with m <= max_m rows, in-features
  * <= max_k and out-features <= max_n allocates (turq_qmatmul, _multi, _host, _multi_host). */
 int32_t turq_ctx_reserve(turq_ctx* ctx, int64_t max_m, int64_t max_k, int64_t max_n);
-/* Read-ahead across launches (optional, best effort). Weights never depend on activations, so a
- * host that knows its call sequence (a decoder walks its layers in order) may name, before a
- * matmul call, the weights the call AFTER it will read: the launch of the upcoming call then
- * asks L2 for the first tiles of those weights while it finishes, and the following launch starts
- * on cache hits instead of a cold HBM burst. count 0 / NULL clears; flags bit 0: the hinted call
- * is turq_qmatmul_swiglu. The hint is consumed by the next integer-scheme launch on the context
- * and is baked into a CUDA graph like any other launch argument; the handles must stay alive as
- * long as such a graph is replayed. */
-int32_t turq_ctx_hint_next(turq_ctx* ctx, int32_t count, const turq_qtensor* const* qts, int32_t flags);
 /* What TURQ_MODE_AUTO means on this context: TURQ_MODE_AUTO (default) = by row count as described
  * above; INT8_ACT, EXACT_F32 or TENSOR_CORE = that scheme for every row count (TENSOR_CORE still
  * falls back to INT8_ACT for in-features that are not a multiple of 64). */

@@ -30,7 +30,6 @@ SIGNATURES = {
     "turq_ctx_poll_status": (c_i32, [c_vp, c_vp]),
     "turq_ctx_reserve": (c_i32, [c_vp, c_i64, c_i64, c_i64]),
     "turq_ctx_set_auto_policy": (c_i32, [c_vp, c_i32]),
-    "turq_ctx_hint_next": (c_i32, [c_vp, c_i32, c_vp, c_i32]),
     "turq_qtensor_from_host": (c_i32, [c_vp, c_i32, c_i64, c_i64, c_vp, c_sz, PP]),
     "turq_qtensor_from_device": (c_i32, [c_vp, c_i32, c_i64, c_i64, c_vp, c_sz, c_vp, PP]),
     "turq_qtensor_slice_rows": (c_i32, [c_vp, c_vp, c_i64, c_i64, PP]),

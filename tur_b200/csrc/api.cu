@@ -228,20 +228,6 @@ int32_t turq_ctx_reserve(turq_ctx* ctx, int64_t max_m, int64_t max_k, int64_t ma
                 up((size_t)max_m * max_k * 4) + 4 * up((size_t)max_m * max_n * 4) + 4 * up((size_t)max_n * 4));
 }
 
-int32_t turq_ctx_hint_next(turq_ctx* ctx, int32_t count, const turq_qtensor* const* qts, int32_t flags) {
-  if (!ctx) return TURQ_E_INVALID_ARG;
-  ctx->next_count = 0;
-  if (count == 0 || !qts) return TURQ_OK;
-  if (count < 0 || count > 4) return fail(ctx, TURQ_E_INVALID_ARG, "count %d outside 0..4", count);
-  for (int i = 0; i < count; i++) {
-    if (!qts[i] || qts[i]->device != ctx->device || qts[i]->n_cols != qts[0]->n_cols) return fail(ctx, TURQ_E_INVALID_ARG, "hinted weights must live on the context's device and share the in-feature count");
-    ctx->next_qts[i] = qts[i];
-  }
-  ctx->next_count = count;
-  ctx->next_flags = flags;
-  return TURQ_OK;
-}
-
 int32_t turq_ctx_set_auto_policy(turq_ctx* ctx, int32_t mode) {
   if (!ctx) return TURQ_E_INVALID_ARG;
   if (mode < TURQ_MODE_AUTO || mode > TURQ_MODE_TENSOR_CORE) return fail(ctx, TURQ_E_INVALID_ARG, "unknown mode %d", mode);
@@ -434,16 +420,6 @@ int32_t turq_quantize_act(turq_ctx* ctx, int32_t fmt, const void* dev_x, int32_t
 // TURQ_MODE_AUTO: the integer GEMV up to 16 rows, the tcgen05 GEMM above (64-row activation
 // tiles with split-K for decode batches, 128/256-row tiles for prefill). Measured on B200 at 32
 // and 64 rows the GEMM is ahead for every weight shape of the benchmark configurations.
-// Hands the context's pending read-ahead hint to the GEMV launcher of this thread (one shot).
-static void arm_next_hint(turq_ctx* ctx) {
-  if (ctx->next_count <= 0) return;
-  turq::GemvPart parts[4];
-  for (int i = 0; i < ctx->next_count; i++)
-    parts[i] = turq::GemvPart{ctx->next_qts[i]->tiles, ctx->next_qts[i]->n_rows, nullptr, nullptr, ctx->next_qts[i]->dtype, nullptr};
-  turq::gemv_set_next_hint(parts, ctx->next_count, ctx->next_qts[0]->n_cols, (ctx->next_flags & 1) != 0);
-  ctx->next_count = 0;
-}
-
 // A context whose policy was pinned with turq_ctx_set_auto_policy uses that one scheme for every
 // row count, so a token's result does not depend on the batch or chunk it arrives in.
 static int32_t auto_mode(const turq_ctx* ctx, int64_t n_rows, int64_t n_cols, int64_t m) {
@@ -476,7 +452,6 @@ int32_t turq_qmatmul(turq_ctx* ctx, const turq_qtensor* qt, const void* dev_x, i
     turq::ActPackPlan plan = turq::plan_act_pack(fmt, m, k);
     int32_t st = ensure(ctx, &ctx->scratch, &ctx->scratch_bytes, plan.total);
     if (st != TURQ_OK) return st;
-    arm_next_hint(ctx);
     e = turq::launch_gemv_int8(qt->dtype, qt->tiles, qt->n_rows, k, dev_x, x_dtype, ctx->scratch, m, dev_y, dev_bias,
                                ctx->gemv_ws, ctx->dev_status, ctx->sm_count, s, &launches);
   } else if (mode == TURQ_MODE_EXACT_F32) {
@@ -535,7 +510,6 @@ static int32_t qmatmul_multi_impl(turq_ctx* ctx, int32_t count, const turq_qtens
   for (int i = 0; i < count; i++)
     parts[i] = turq::GemvPart{qts[i]->tiles, qts[i]->n_rows, dev_ys[i], dev_biases ? dev_biases[i] : nullptr, qts[i]->dtype, nullptr};
   int launches = 0;
-  arm_next_hint(ctx);
   cudaError_t e = turq::launch_gemv_int8_multi(qts[0]->dtype, parts, count, k, dev_x, x_dtype, ctx->scratch, m, ctx->gemv_ws,
                                                ctx->dev_status, ctx->sm_count, static_cast<cudaStream_t>(stream), &launches,
                                                x_remote);
@@ -676,6 +650,5 @@ int32_t api_cuda_fail(turq_ctx* ctx, cudaError_t e, const char* what) { return c
 int32_t api_ensure_scratch(turq_ctx* ctx, size_t bytes) { return ensure(ctx, &ctx->scratch, &ctx->scratch_bytes, bytes); }
 int32_t api_ensure_tmp(turq_ctx* ctx, size_t bytes) { return ensure(ctx, &ctx->tmp, &ctx->tmp_bytes, bytes); }
 int32_t api_auto_mode(const turq_ctx* ctx, int64_t n_rows, int64_t n_cols, int64_t m) { return auto_mode(ctx, n_rows, n_cols, m); }
-void api_arm_next_hint(turq_ctx* ctx) { arm_next_hint(ctx); }
 
 }  // namespace turq

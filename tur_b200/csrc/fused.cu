@@ -242,7 +242,6 @@ int32_t turq_qmatmul_swiglu(turq_ctx* ctx, const turq_qtensor* gate, const turq_
     int32_t st = turq::api_ensure_scratch(ctx, turq::plan_act_pack(fmt, m, k).total);
     if (st != TURQ_OK) return st;
     int launches = 0;
-    turq::api_arm_next_hint(ctx);
     e = turq::launch_gemv_int8_swiglu(gate->dtype, gate->tiles, up->tiles, n, k, dev_x, x_dtype, ctx->scratch, m, dev_out,
                                       ctx->gemv_ws, ctx->dev_status, ctx->sm_count, s, &launches);
     ctx->launches += launches;
@@ -324,7 +323,6 @@ int32_t turq_rmsnorm_qmatmul_multi(turq_ctx* ctx, int32_t count, const turq_qten
     parts[i] = turq::GemvPart{qts[i]->tiles, qts[i]->n_rows, dev_ys[i], dev_biases ? dev_biases[i] : nullptr, qts[i]->dtype, nullptr};
   int launches = 0;
   // the GEMV only ever reads the planes; x is passed for completeness
-  turq::api_arm_next_hint(ctx);
   e = turq::launch_gemv_int8_multi(qts[0]->dtype, parts, count, k, dev_x, x_dtype, ctx->scratch, m, ctx->gemv_ws, ctx->dev_status,
                                    ctx->sm_count, s, &launches, false, nullptr, true);
   ctx->launches += launches;

@@ -102,20 +102,6 @@ struct SmemPlan {
 
 constexpr int MAX_PARTS = 4;  // weights that share one activation and one launch (q|k|v, gate|up)
 
-// Where the NEXT launch on this context will start reading (best effort): after its last copy a
-// producer warp asks L2 to fetch the first units of the next launch's CTAs, so HBM keeps working
-// across the launch boundary and the next grid's first ring fill is an L2 hit. Weights never
-// depend on a preceding kernel, which is what makes reading ahead legal. grid == 0: no hint.
-struct NextHint {
-  const uint8_t* tiles[MAX_PARTS];
-  int rt_begin[MAX_PARTS + 1];
-  int tile_bytes[MAX_PARTS];
-  int nparts, interleave;
-  int ktiles, KU, group;
-  int split_q, split_r, total_units, grid;
-  int units;  // units per CTA to prefetch
-};
-
 struct StreamArgs {
   // part p covers row-tiles [rt_begin[p], rt_begin[p+1]) of the concatenated row space
   const uint8_t* tiles[MAX_PARTS];
@@ -144,7 +130,6 @@ struct StreamArgs {
   int stages;
   int stage_bytes;
   SmemPlan sp;
-  NextHint next;
 };
 
 inline SmemPlan plan_smem(int dtype, int mg, bool fused /* planes in shared memory */, int rows_cap, int k, int stages, int stage_bytes,
@@ -315,34 +300,6 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
         w.advance(n);
         w.next_row_if_needed();
         if (++slot == a.stages) { slot = 0; ph ^= 1u; }
-      }
-    }
-    __syncwarp();
-    if (a.next.grid > 0) {
-      // read-ahead for the next launch (see NextHint): one unit per lane and round
-      const NextHint& nx = a.next;
-      for (int nb = b; nb < nx.grid; nb += G) {
-        int n0 = nb * nx.split_q + (nb < nx.split_r ? nb : nx.split_r);
-        int n1 = (nb + 1) * nx.split_q + (nb + 1 < nx.split_r ? nb + 1 : nx.split_r);
-        if (n0 > nx.total_units) n0 = nx.total_units;
-        if (n1 > nx.total_units) n1 = nx.total_units;
-        const int cnt = n1 - n0 < nx.units ? n1 - n0 : nx.units;
-        for (int i = lane; i < cnt; i += 32) {
-          const int u = n0 + i;
-          const int rt = u / nx.KU, ku = u - rt * nx.KU;
-          int part = 0, rt_in_part;
-          if (nx.interleave) {
-            part = rt & 1;
-            rt_in_part = rt >> 1;
-          } else {
-            while (part + 1 < nx.nparts && rt >= nx.rt_begin[part + 1]) part++;
-            rt_in_part = rt - nx.rt_begin[part];
-          }
-          int nt = nx.ktiles - ku * nx.group;
-          if (nt > nx.group) nt = nx.group;
-          const uint8_t* src = nx.tiles[part] + ((int64_t)rt_in_part * nx.ktiles + (int64_t)ku * nx.group) * nx.tile_bytes[part];
-          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"((uint32_t)(nt * nx.tile_bytes[part])) : "memory");
-        }
       }
     }
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -641,64 +598,6 @@ size_t gemv_workspace_bytes(int sms) { return (size_t)sms * 4 * 4 * 128 * 4 + (s
 size_t gemv_workspace_flags_offset(int sms) { return (size_t)sms * 4 * 4 * 128 * 4; }
 size_t gemv_workspace_flags_bytes(int sms) { return (size_t)sms * 4 * 4; }
 
-// ---- read-ahead hint (NextHint): set by the C-ABI layer right before a launch, consumed by it
-struct PendingHint {
-  GemvPart parts[MAX_PARTS];
-  int nparts = 0;
-  int64_t k = 0;
-  bool interleave = false;
-};
-static thread_local PendingHint t_hint;
-
-void gemv_set_next_hint(const GemvPart* parts, int nparts, int64_t k, bool interleave) {
-  t_hint.nparts = 0;
-  if (!parts || nparts < 1 || nparts > MAX_PARTS) return;
-  for (int i = 0; i < nparts; i++) t_hint.parts[i] = parts[i];
-  t_hint.nparts = nparts;
-  t_hint.k = k;
-  t_hint.interleave = interleave;
-}
-
-// Plans the hinted launch the way launch_dt will (same split arithmetic) and clears the hint.
-static NextHint take_next_hint(int sm_count) {
-  NextHint nx{};
-  const PendingHint h = t_hint;
-  t_hint.nparts = 0;
-  static const int units = tuning_env("TURQ_GEMV_PREFETCH_UNITS", 24);
-  if (h.nparts < 1 || units <= 0) return nx;
-  const int dt0 = h.parts[0].dtype;
-  const int elems = tq_block_elems(dt0);
-  if (elems == 0 || h.k % elems != 0) return nx;
-  for (int i = 0; i < h.nparts; i++)
-    if (!tq_is_weight_type(h.parts[i].dtype) || tq_block_elems(h.parts[i].dtype) != elems) return nx;
-  nx.group = dt0 == TQ_Q8_0 ? 4 : 1;
-  nx.ktiles = (int)(h.k / elems);
-  nx.KU = (nx.ktiles + nx.group - 1) / nx.group;
-  for (int i = 0; i < h.nparts; i++) {
-    nx.tiles[i] = h.parts[i].tiles;
-    nx.tile_bytes[i] = tq_tile_bytes(h.parts[i].dtype);
-    nx.rt_begin[i + 1] = nx.rt_begin[i] + (int)((h.parts[i].n_rows + TQ_TILE_ROWS - 1) / TQ_TILE_ROWS);
-  }
-  nx.nparts = h.nparts;
-  const int slots = sm_count * 2;
-  const int row_tiles = nx.rt_begin[h.nparts];
-  if ((int64_t)row_tiles * nx.KU > (int64_t)1 << 30) return NextHint{};
-  GemvSplit sp = plan_gemv_split(row_tiles, nx.KU, slots, -1);
-  if (h.interleave && h.nparts == 2 && h.parts[0].n_rows == h.parts[1].n_rows) {
-    const GemvSplit pairs = plan_gemv_split(row_tiles / 2, 2 * nx.KU, slots, -1);
-    if (pairs.aligned) {
-      sp = pairs;
-      nx.interleave = 1;
-    }
-  }
-  nx.split_q = sp.split_q;
-  nx.split_r = sp.split_r;
-  nx.total_units = row_tiles * nx.KU;
-  nx.grid = sp.grid;
-  nx.units = units;
-  return nx;
-}
-
 // Launches with the programmatic-stream-serialization attribute (the kernel orders itself
 // against its predecessor with griddepcontrol.wait).
 template <int DT, int MG, int ACT, int DT2 = DT>
@@ -802,7 +701,6 @@ static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const
     if (launches) (*launches)++;
     if (e != cudaSuccess) return e;
   }
-  const NextHint next_hint = take_next_hint(sm_count);
   for (int64_t m0 = 0; m0 < m; m0 += 32) {
     const int rows = (int)(m - m0 < 32 ? m - m0 : 32);
     const int mg = rows <= 8 ? 1 : rows <= 16 ? 2 : 4;
@@ -845,7 +743,6 @@ static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const
     a.stages = stages;
     a.stage_bytes = stage_bytes;
     a.sp = sp;
-    if (m0 + 32 >= m) a.next = next_hint;  // the last pass of this call reads ahead
     cudaError_t e;
     if constexpr (MIXED) {
       e = act_mode == ACT_FUSED ? launch_one<DT, 1, ACT_FUSED, DT2>(a, grid, sp.total, s)

@@ -6,8 +6,6 @@
 
 #include <string>
 
-struct turq_qtensor;
-
 struct turq_ctx {
   int device = 0;
   int sm_count = 0;
@@ -21,10 +19,6 @@ struct turq_ctx {
   int* dev_status = nullptr;   // the same word's device address
   uint8_t* gemv_ws = nullptr;  // split row-tile workspace of the streaming GEMV (zeroed once)
   cudaStream_t own_stream = nullptr;
-  // turq_ctx_hint_next: weights the call after the upcoming one will read (best-effort read-ahead)
-  const turq_qtensor* next_qts[4] = {nullptr, nullptr, nullptr, nullptr};
-  int next_count = 0;
-  int next_flags = 0;
   int auto_policy = 0;  // what TURQ_MODE_AUTO resolves to: 0 = by row count, else a fixed turq_mode
   int64_t launches = 0;
   std::string err;

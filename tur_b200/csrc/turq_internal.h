@@ -91,10 +91,6 @@ cudaError_t launch_gemv_int8_multi(int dtype, const GemvPart* parts, int nparts,
                                    int x_dtype, uint8_t* act_scratch, int64_t m, uint8_t* workspace, int* status,
                                    int sm_count, cudaStream_t s, int* launches, bool x_remote = false,
                                    const unsigned* y_toggle = nullptr, bool planes_ready = false);
-// Read-ahead hint for the calling thread's next integer-scheme launch: the weights (and k) the
-// launch AFTER it will read; that next launch's producer warps ask L2 for their first tiles.
-// interleave: the hinted call is a SwiGLU launch. Consumed (cleared) by the next launch.
-void gemv_set_next_hint(const GemvPart* parts, int nparts, int64_t k, bool interleave);
 // out[m, n] = silu(x . Wg^T) * (x . Wu^T) as ONE integer-scheme launch over the row-tiles of both
 // weights interleaved (same type and shape). cudaErrorNotSupported = not applicable, nothing launched.
 cudaError_t launch_gemv_int8_swiglu(int dtype, const uint8_t* gate_tiles, const uint8_t* up_tiles, int64_t n_rows, int64_t k,
@@ -126,7 +122,6 @@ int32_t api_cuda_fail(turq_ctx* ctx, cudaError_t e, const char* what);
 int32_t api_ensure_scratch(turq_ctx* ctx, size_t bytes);  // the context's growable activation scratch
 int32_t api_ensure_tmp(turq_ctx* ctx, size_t bytes);      // the context's growable result staging
 int32_t api_auto_mode(const turq_ctx* ctx, int64_t n_rows, int64_t n_cols, int64_t m);
-void api_arm_next_hint(turq_ctx* ctx);  // passes the context's pending turq_ctx_hint_next to this thread's next GEMV launch
 int32_t qmatmul_for_exchange(turq_ctx* ctx, const turq_qtensor* qt, const void* dev_x, int32_t x_dtype, int64_t m, float* s0,
                              float* s1, const unsigned* toggle, int32_t mode, cudaStream_t s, float** staged);
 

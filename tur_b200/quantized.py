@@ -83,12 +83,6 @@ class _Context:
         (required before capturing calls into a CUDA graph)."""
         self.check(_lib.load().turq_ctx_reserve(self.handle, max_m, max_k, max_n))
 
-    def hint_next(self, mms: Sequence["QMatMul"] = (), swiglu: bool = False) -> None:
-        """Names the weights the call AFTER the upcoming one will read (read-ahead into L2)."""
-        n = len(mms)
-        arr = (ctypes.c_void_p * max(n, 1))(*[mm.qtensor._h for mm in mms])
-        self.check(_lib.load().turq_ctx_hint_next(self.handle, n, arr if n else None, 1 if swiglu else 0))
-
     def set_auto_policy(self, mode: "Mode") -> None:
         """Pins what Mode.AUTO means on this context to one scheme for every row count."""
         self.check(_lib.load().turq_ctx_set_auto_policy(self.handle, int(mode)))
