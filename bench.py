@@ -669,11 +669,12 @@ class TPStack:
                         if sh0.parallel == "row" and world > 1:
                             dist.all_reduce(y)
             if self.head:
-                y = self.head[2].forward(xs[("hidden", wl.hidden)], mode=mode, out=ys["output_local"])
                 if world > 1 and group is not None:
-                    group.allgather(y, self.head_widths, out=ys["output"])
-                elif world > 1:
-                    gather_columns(y, wl.head.n, world, 16)
+                    group.qmatmul_gather(self.head[2], xs[("hidden", wl.hidden)], self.head_widths, mode=mode, out=ys["output"])
+                else:
+                    y = self.head[2].forward(xs[("hidden", wl.hidden)], mode=mode, out=ys["output_local"])
+                    if world > 1:
+                        gather_columns(y, wl.head.n, world, 16)
         return run
 
     def collectives_per_pass(self):

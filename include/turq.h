@@ -272,9 +272,18 @@ int32_t turq_tp_allgather(turq_tp* tp, const float* dev_in, int64_t m, const int
 /* Row-parallel LinearX::forward: qt holds this rank's range of input columns, dev_x the matching
  * activation columns [m, n_cols of the shard]; dev_y [m, n_rows] receives the sum over the ranks
  * (+ bias) on every rank. In the integer scheme the GEMV's epilogue writes its partial result
- * straight into the exchange memory; one small kernel then signals, waits and adds. */
+ * straight into the exchange memory. For results up to 64 KB (decode) the CTA of that launch
+ * that finishes last then signals the peers, waits and adds: compute and all-reduce are ONE
+ * kernel. Larger results get a multi-CTA exchange launch behind the matmul. */
 int32_t turq_qmatmul_rowparallel(turq_tp* tp, const turq_qtensor* qt, const void* dev_x, int32_t x_dtype,
                                  int64_t m, float* dev_y, int32_t mode, const float* dev_bias, void* stream);
+/* Column-parallel LinearX::forward with gathered output (the vocabulary-sharded head): qt holds
+ * this rank's rows, dev_x the full activations; dev_out [m, sum(widths)] receives every rank's
+ * columns on every rank, widths[p] = out-features of rank p's shard. The product lands straight
+ * in the exchange memory. dev_bias: this shard's bias rows or NULL. */
+int32_t turq_qmatmul_gather(turq_tp* tp, const turq_qtensor* qt, const void* dev_x, int32_t x_dtype, int64_t m,
+                            const int64_t* widths, float* dev_out, int32_t mode, const float* dev_bias,
+                            void* stream);
 /* Test support on a single GPU: connects the group to local stand-ins for the other ranks, which
  * never signal by themselves (a call then runs into its wait limit), and lets the host play a
  * peer's part for the next call: its data (count floats, may be NULL / 0) and, with signal != 0,

@@ -89,6 +89,27 @@ def test_reduction_adds_the_ranks_in_rank_order(tq, world, rank):
         if p != rank:
             g.loopback_fill(p, shares[p], signal=True)
     assert torch.equal(g.allgather(shares[rank], widths), torch.cat(shares, dim=1))
+    # the head's product gathered in one call: this rank's columns come from its matmul
+    widths2 = [n if p == rank else 16 * (2 + p) for p in range(world)]
+    shares2 = [torch.from_numpy(rng.standard_normal((m, wd)).astype(np.float32)).cuda() for wd in widths2]
+    shares2[rank] = mm.forward(x, bias=bias, mode=tq.Mode.INT8_ACT)
+    for p in range(world):
+        if p != rank:
+            g.loopback_fill(p, shares2[p], signal=True)
+    assert torch.equal(g.qmatmul_gather(mm, x, widths2, bias=bias, mode=tq.Mode.INT8_ACT), torch.cat(shares2, dim=1))
+    # a result larger than the fused limit takes the separate exchange launch: same arithmetic
+    big_m = 40                                                 # 40 x 528 x 4 B = 84 KB > 64 KB
+    xb = torch.from_numpy(rng.standard_normal((big_m, k)).astype(np.float32)).cuda()
+    gb = TPGroup(rank, world, big_m * n * 4, loopback=True)
+    parts = [torch.from_numpy(rng.standard_normal((big_m, n)).astype(np.float32)).cuda() for _ in range(world)]
+    parts[rank] = mm.forward(xb, mode=tq.Mode.INT8_ACT)
+    for p in range(world):
+        if p != rank:
+            gb.loopback_fill(p, parts[p], signal=True)
+    want = parts[0].clone()
+    for p in range(1, world):
+        want += parts[p]
+    assert torch.equal(gb.qmatmul_rowparallel(mm, xb, mode=tq.Mode.INT8_ACT), want)
     tq.context().poll_status()
 
 

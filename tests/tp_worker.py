@@ -80,6 +80,7 @@ def main() -> None:
             widths = [c * 256 for _, c in split_units(w.n // 256, world)]
             y = g.allgather(yl, widths)
             assert torch.equal(y, ref), "column-parallel gather"
+            assert torch.equal(g.qmatmul_gather(mine, x, widths, mode=Mode.INT8_ACT), ref), "gather fused behind the matmul"
     ctx.poll_status()
     dist.barrier()
     g.close()

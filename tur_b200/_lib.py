@@ -58,6 +58,7 @@ SIGNATURES = {
     "turq_tp_allreduce": (c_i32, [c_vp, c_vp, c_vp, c_i64, c_vp]),
     "turq_tp_allgather": (c_i32, [c_vp, c_vp, c_i64, c_vp, c_vp, c_vp]),
     "turq_qmatmul_rowparallel": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i64, c_vp, c_i32, c_vp, c_vp]),
+    "turq_qmatmul_gather": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i64, c_vp, c_vp, c_i32, c_vp, c_vp]),
     "turq_tp_connect_loopback": (c_i32, [c_vp]),
     "turq_tp_loopback_fill": (c_i32, [c_vp, c_i32, c_vp, c_i64, c_i32, c_vp]),
 }

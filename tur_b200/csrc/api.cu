@@ -616,8 +616,10 @@ int32_t turq_qmatmul_host(turq_ctx* ctx, const turq_qtensor* qt, const float* ho
 namespace turq {
 
 int32_t qmatmul_for_exchange(turq_ctx* ctx, const turq_qtensor* qt, const void* dev_x, int32_t x_dtype, int64_t m, float* s0,
-                             float* s1, const unsigned* toggle, int32_t mode, cudaStream_t s, float** staged) {
+                             float* s1, const unsigned* toggle, int32_t mode, cudaStream_t s, float** staged,
+                             const TpArgs* fuse, bool* fused, const float* local_bias) {
   *staged = nullptr;
+  *fused = false;
   if (x_dtype != TURQ_F32 && x_dtype != TURQ_BF16) return fail(ctx, TURQ_E_DTYPE, "activations must be F32 or BF16 (got %d)", x_dtype);
   if (qt->device != ctx->device) return fail(ctx, TURQ_E_INVALID_ARG, "tensor lives on device %d, context on %d", qt->device, ctx->device);
   if ((uintptr_t)dev_x % 16 != 0) return fail(ctx, TURQ_E_ALIGN, "dev_x must be 16-byte aligned");
@@ -628,17 +630,19 @@ int32_t qmatmul_for_exchange(turq_ctx* ctx, const turq_qtensor* qt, const void* 
     const int fmt = qt->dtype == TURQ_Q8_0 ? TQ_Q8_0 : TQ_Q8_K;
     int32_t st = ensure(ctx, &ctx->scratch, &ctx->scratch_bytes, plan_act_pack(fmt, m, k).total);
     if (st != TURQ_OK) return st;
-    GemvPart part{qt->tiles, qt->n_rows, s0, nullptr, qt->dtype, s1};
+    GemvPart part{qt->tiles, qt->n_rows, s0, local_bias, qt->dtype, s1};
     int launches = 0;
+    const bool fuse_now = fuse != nullptr && m <= 32;
     cudaError_t e = launch_gemv_int8_multi(qt->dtype, &part, 1, k, dev_x, x_dtype, ctx->scratch, m, ctx->gemv_ws, ctx->dev_status,
-                                           ctx->sm_count, s, &launches, false, toggle);
+                                           ctx->sm_count, s, &launches, false, toggle, false, fuse_now ? fuse : nullptr);
+    *fused = fuse_now;
     ctx->launches += launches;
     if (e != cudaSuccess) return cuda_fail(ctx, e, "row-parallel GEMV launch");
     return TURQ_OK;
   }
   int32_t st = ensure(ctx, &ctx->tmp, &ctx->tmp_bytes, (size_t)m * qt->n_rows * 4);
   if (st != TURQ_OK) return st;
-  st = turq_qmatmul(ctx, qt, dev_x, x_dtype, m, reinterpret_cast<float*>(ctx->tmp), mode, nullptr, s);
+  st = turq_qmatmul(ctx, qt, dev_x, x_dtype, m, reinterpret_cast<float*>(ctx->tmp), mode, local_bias, s);
   if (st != TURQ_OK) return st;
   *staged = reinterpret_cast<float*>(ctx->tmp);
   return TURQ_OK;

@@ -29,6 +29,7 @@
 #include "actquant.cuh"
 #include "gemv_tile.cuh"
 #include "launch_plan.h"
+#include "tp_exchange.cuh"
 #include "turq_internal.h"
 
 namespace turq {
@@ -130,6 +131,12 @@ struct StreamArgs {
   int stages;
   int stage_bytes;
   SmemPlan sp;
+  // Row-parallel linear of a tensor-parallel group, small outputs: the CTA that finishes last
+  // performs the exchange itself (signal the peers, wait, add all ranks' partial results in rank
+  // order into xchg.out) - compute and collective in one kernel. y / y_alt are then the two
+  // exchange slots and y_toggle the group's call counter.
+  int xchg_on;
+  TpArgs xchg;
 };
 
 inline SmemPlan plan_smem(int dtype, int mg, bool fused /* planes in shared memory */, int rows_cap, int k, int stages, int stage_bytes,
@@ -574,6 +581,32 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
       __threadfence_system();
     }
   }
+  if (a.xchg_on) {
+    __shared__ int s_last, s_ok;
+    if (threadIdx.x == 0) {
+      __threadfence();  // this CTA's outputs (written before the barrier above) before its ticket
+      s_last = atomicAdd(a.xchg.counter + 2, 1u) == gridDim.x - 1 ? 1 : 0;
+    }
+    __syncthreads();
+    if (s_last) {
+      // every CTA of this launch has written its part of the exchange slot
+      __threadfence();
+      const unsigned seq = *reinterpret_cast<volatile unsigned*>(a.xchg.counter) + 1u;
+      const size_t slot_off = (seq & 1u) ? a.xchg.slot_elems : 0;
+      const bool ok = tp_rendezvous(a.xchg, seq, &s_ok, 0);
+      if (ok) tp_reduce_range(a.xchg, slot_off, threadIdx.x, THREADS, true);
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        if (!ok) {
+          *reinterpret_cast<volatile int*>(a.status) = TURQ_E_TIMEOUT;
+          __threadfence_system();
+        }
+        a.xchg.counter[2] = 0;
+        __threadfence();
+        *reinterpret_cast<volatile unsigned*>(a.xchg.counter) = seq;
+      }
+    }
+  }
 }
 
 // ------------------------------------------------------------------ host side
@@ -635,7 +668,7 @@ template <int DT, int DT2 = DT>
 static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const void* x, int x_dtype,
                              uint8_t* act_scratch, int64_t m, uint8_t* workspace, int* status, int sm_count,
                              cudaStream_t s, int* launches, bool x_remote, const unsigned* y_toggle, bool planes_ready,
-                             bool interleave = false) {
+                             const TpArgs* xchg, bool interleave = false) {
   constexpr bool MIXED = DT2 != DT;
   constexpr int GROUP = TileGeom<DT>::GROUP;
   constexpr int UNIT_BYTES = (TileGeom<DT2>::BYTES > TileGeom<DT>::BYTES ? TileGeom<DT2>::BYTES : TileGeom<DT>::BYTES) * GROUP;
@@ -715,6 +748,10 @@ static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const
     }
     for (int p = 0; p <= nparts; p++) a.rt_begin[p] = rt_begin[p];
     a.y_toggle = y_toggle;
+    if (xchg && m <= 32) {  // single pass: the launch's last CTA exchanges
+      a.xchg_on = 1;
+      a.xchg = *xchg;
+    }
     a.interleave = interleave ? 1 : 0;
     a.nparts = nparts;
     a.ktiles = ktiles;
@@ -764,11 +801,12 @@ static cudaError_t launch_dt(const GemvPart* parts, int nparts, int64_t k, const
   return cudaSuccess;
 }
 
-#define TQ_LAUNCH_ARGS k, x, x_dtype, act_scratch, m, workspace, status, sm_count, s, launches, x_remote, y_toggle, planes_ready
+#define TQ_LAUNCH_ARGS k, x, x_dtype, act_scratch, m, workspace, status, sm_count, s, launches, x_remote, y_toggle, planes_ready, xchg
 
 static cudaError_t launch_one_type(int dtype, const GemvPart* parts, int nparts, int64_t k, const void* x, int x_dtype,
                                    uint8_t* act_scratch, int64_t m, uint8_t* workspace, int* status, int sm_count,
-                                   cudaStream_t s, int* launches, bool x_remote, const unsigned* y_toggle, bool planes_ready) {
+                                   cudaStream_t s, int* launches, bool x_remote, const unsigned* y_toggle, bool planes_ready,
+                                   const TpArgs* xchg) {
   switch (dtype) {
     case TQ_Q8_0: return launch_dt<TQ_Q8_0>(parts, nparts, TQ_LAUNCH_ARGS);
     case TQ_Q4_K: return launch_dt<TQ_Q4_K>(parts, nparts, TQ_LAUNCH_ARGS);
@@ -782,7 +820,8 @@ static cudaError_t launch_one_type(int dtype, const GemvPart* parts, int nparts,
 // together with Q6_K parts too, where the mixed kernel exists; anything else one launch per type.
 cudaError_t launch_gemv_int8_multi(int dtype, const GemvPart* parts, int nparts, int64_t k, const void* x, int x_dtype,
                                    uint8_t* act_scratch, int64_t m, uint8_t* workspace, int* status, int sm_count,
-                                   cudaStream_t s, int* launches, bool x_remote, const unsigned* y_toggle, bool planes_ready) {
+                                   cudaStream_t s, int* launches, bool x_remote, const unsigned* y_toggle, bool planes_ready,
+                                   const TpArgs* xchg) {
   if (nparts < 1 || nparts > MAX_PARTS) return cudaErrorInvalidValue;
   GemvPart p[MAX_PARTS];
   int types[MAX_PARTS], ntypes = 0;
@@ -813,7 +852,7 @@ cudaError_t launch_gemv_int8_multi(int dtype, const GemvPart* parts, int nparts,
   }
   return cudaSuccess;
 }
-#define TQ_LAUNCH_ARGS_DECL k, x, x_dtype, act_scratch, m, workspace, status, sm_count, s, launches, x_remote, y_toggle, planes_ready
+#define TQ_LAUNCH_ARGS_DECL k, x, x_dtype, act_scratch, m, workspace, status, sm_count, s, launches, x_remote, y_toggle, planes_ready, xchg
 
 // silu(x . Wg^T) * (x . Wu^T) in one launch (two weights of one type and shape). Returns
 // cudaErrorNotSupported, before anything is launched, where the interleaved split does not apply.
@@ -823,6 +862,7 @@ cudaError_t launch_gemv_int8_swiglu(int dtype, const uint8_t* gate_tiles, const 
   GemvPart parts[2] = {{gate_tiles, n_rows, out, nullptr, dtype, nullptr}, {up_tiles, n_rows, out, nullptr, dtype, nullptr}};
   const bool x_remote = false, planes_ready = false;
   const unsigned* y_toggle = nullptr;
+  const TpArgs* xchg = nullptr;
   switch (dtype) {
     case TQ_Q8_0: return launch_dt<TQ_Q8_0>(parts, 2, TQ_LAUNCH_ARGS_DECL, true);
     case TQ_Q4_K: return launch_dt<TQ_Q4_K>(parts, 2, TQ_LAUNCH_ARGS_DECL, true);
@@ -837,7 +877,7 @@ cudaError_t launch_gemv_int8(int dtype, const uint8_t* tiles, int64_t n_rows, in
                              int* status, int sm_count, cudaStream_t s, int* launches) {
   GemvPart part{tiles, n_rows, y, bias, dtype, nullptr};
   return launch_gemv_int8_multi(dtype, &part, 1, k, x, x_dtype, act_scratch, m, workspace, status, sm_count, s, launches, false,
-                                nullptr, false);
+                                nullptr, false, nullptr);
 }
 
 #undef TQ_LAUNCH_ARGS

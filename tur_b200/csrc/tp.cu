@@ -32,131 +32,18 @@
 
 #include "../../include/turq.h"
 #include "handles.h"
+#include "tp_exchange.cuh"
 #include "turq_internal.h"
 
 namespace turq {
-
-constexpr int TP_MAX_RANKS = 8;
-constexpr int TP_MAX_BLOCKS = 128;
-constexpr int TP_THREADS = 256;
-constexpr size_t TP_FLAGS_BYTES = (size_t)TP_MAX_BLOCKS * TP_MAX_RANKS * 4;  // 4 KB
-constexpr size_t TP_HEADER_BYTES = TP_FLAGS_BYTES + 256;                     // + counter words, 256-byte aligned
-
-struct TpArgs {
-  const float* peer_data[TP_MAX_RANKS];  // slot 0 of every rank's region, in rank order (own: local pointer)
-  unsigned* peer_flags[TP_MAX_RANKS];    // flag array of every rank's region
-  unsigned* counter;                     // own region: [0] calls completed, [1] CTA ticket
-  size_t slot_elems;                     // floats per slot
-  int rank, world;
-  long long wait_cycles;
-  int* status;
-  // reduce: out[i] = sum_p peer[p][i] (+ bias[i % n]) for i < count
-  int64_t count, n;
-  const float* bias;
-  // gather: out[r, col0[p] + j] = peer[p][r * width[p] + j]
-  int64_t m, n_total;
-  int64_t col0[TP_MAX_RANKS + 1];
-  float* out;
-};
-
-__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-// peer data: system-scope loads that do not linger in this SM's L1 across calls
-__device__ __forceinline__ float4 ld_peer_v4(const float* p) {
-  float4 v;
-  asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ float ld_peer_f32(const float* p) {
-  float v;
-  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
-  return v;
-}
-
-// Signals this CTA's peers, waits for theirs. Returns false when the wait ran out.
-__device__ __forceinline__ bool tp_rendezvous(const TpArgs& a, unsigned seq, int* s_ok) {
-  const int b = blockIdx.x;
-  if (threadIdx.x == 0) *s_ok = 1;
-  __syncthreads();
-  if (threadIdx.x < a.world) {
-    const int p = threadIdx.x;
-    // everything this rank put into its slot was written by kernels that completed before this
-    // one started; the release store publishes it to the peer together with the flag
-    st_release_sys(a.peer_flags[p] + b * TP_MAX_RANKS + a.rank, seq);
-    const unsigned* mine = a.peer_flags[a.rank] + b * TP_MAX_RANKS + p;
-    const long long t0 = clock64();
-    for (;;) {
-      if ((int)(ld_acquire_sys(mine) - seq) >= 0) break;
-      if (clock64() - t0 > a.wait_cycles) {
-        *s_ok = 0;
-        break;
-      }
-      __nanosleep(40);
-    }
-  }
-  __syncthreads();
-  return *s_ok != 0;
-}
-
-// The last CTA to finish advances the call number (every CTA read it at its start).
-__device__ __forceinline__ void tp_finish(const TpArgs& a, unsigned seq, bool ok) {
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    if (!ok) {
-      *reinterpret_cast<volatile int*>(a.status) = TURQ_E_TIMEOUT;  // the word may be mapped host memory
-      __threadfence_system();
-    }
-    __threadfence();
-    const unsigned ticket = atomicAdd(a.counter + 1, 1u);
-    if (ticket == gridDim.x - 1) {
-      a.counter[1] = 0;
-      __threadfence();
-      *reinterpret_cast<volatile unsigned*>(a.counter) = seq;
-    }
-  }
-}
 
 __global__ void __launch_bounds__(TP_THREADS) tp_allreduce_kernel(const TpArgs a) {
   __shared__ int s_ok;
   const unsigned seq = *reinterpret_cast<volatile unsigned*>(a.counter) + 1u;
   const size_t slot_off = (seq & 1u) ? a.slot_elems : 0;
-  const bool ok = tp_rendezvous(a, seq, &s_ok);
-  if (ok) {
-    const int64_t nvec = a.count >> 2;
-    const bool vec_bias = a.bias && (a.n & 3) == 0;
-    for (int64_t v = (int64_t)blockIdx.x * TP_THREADS + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * TP_THREADS) {
-      float4 acc = ld_peer_v4(a.peer_data[0] + slot_off + 4 * v);
-      for (int p = 1; p < a.world; p++) {
-        const float4 t = ld_peer_v4(a.peer_data[p] + slot_off + 4 * v);
-        acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
-      }
-      if (a.bias) {
-        if (vec_bias) {
-          const float4 bb = *reinterpret_cast<const float4*>(a.bias + (4 * v) % a.n);
-          acc.x += bb.x; acc.y += bb.y; acc.z += bb.z; acc.w += bb.w;
-        } else {
-          acc.x += a.bias[(4 * v) % a.n]; acc.y += a.bias[(4 * v + 1) % a.n];
-          acc.z += a.bias[(4 * v + 2) % a.n]; acc.w += a.bias[(4 * v + 3) % a.n];
-        }
-      }
-      *reinterpret_cast<float4*>(a.out + 4 * v) = acc;
-    }
-    // tail (count not a multiple of 4)
-    if (blockIdx.x == 0) {
-      for (int64_t i = (nvec << 2) + threadIdx.x; i < a.count; i += TP_THREADS) {
-        float acc = ld_peer_f32(a.peer_data[0] + slot_off + i);
-        for (int p = 1; p < a.world; p++) acc += ld_peer_f32(a.peer_data[p] + slot_off + i);
-        if (a.bias) acc += a.bias[i % a.n];
-        a.out[i] = acc;
-      }
-    }
-  }
+  const bool ok = tp_rendezvous(a, seq, &s_ok, blockIdx.x);
+  if (ok)
+    tp_reduce_range(a, slot_off, (int64_t)blockIdx.x * TP_THREADS + threadIdx.x, (int64_t)gridDim.x * TP_THREADS, blockIdx.x == 0);
   tp_finish(a, seq, ok);
 }
 
@@ -164,7 +51,7 @@ __global__ void __launch_bounds__(TP_THREADS) tp_allgather_kernel(const TpArgs a
   __shared__ int s_ok;
   const unsigned seq = *reinterpret_cast<volatile unsigned*>(a.counter) + 1u;
   const size_t slot_off = (seq & 1u) ? a.slot_elems : 0;
-  const bool ok = tp_rendezvous(a, seq, &s_ok);
+  const bool ok = tp_rendezvous(a, seq, &s_ok, blockIdx.x);
   if (ok) {
     // one (rank, row) run of columns at a time; widths are multiples of 4 floats
     const int64_t runs = (int64_t)a.world * a.m;
@@ -210,6 +97,7 @@ struct turq_tp {
   bool loopback[turq::TP_MAX_RANKS] = {};   // true: a local stand-in allocated by turq_tp_connect_loopback
   bool connected = false;
   long long wait_cycles = 2000000000ll;  // about one second of SM clock
+  size_t fuse_max_bytes = 64 << 10;      // results up to this size are exchanged by the GEMV's own last CTA
 };
 
 namespace {
@@ -490,8 +378,19 @@ int32_t turq_qmatmul_rowparallel(turq_tp* tp, const turq_qtensor* qt, const void
   float* s0 = slot0(tp, tp->rank);
   float* s1 = s0 + tp->slot_bytes / 4;
   float* staged = nullptr;
-  st = turq::qmatmul_for_exchange(ctx, qt, dev_x, x_dtype, m, s0, s1, counter_of(tp), mode, s, &staged);
+  // Small results (decode): the GEMV's last CTA does the exchange - one kernel computes and
+  // reduces. Larger ones get the multi-CTA exchange launch.
+  turq::TpArgs fuse{};
+  fill_args(tp, fuse);
+  fuse.count = count;
+  fuse.n = qt->n_rows;
+  fuse.bias = dev_bias;
+  fuse.out = dev_y;
+  bool fused = false;
+  st = turq::qmatmul_for_exchange(ctx, qt, dev_x, x_dtype, m, s0, s1, counter_of(tp), mode, s, &staged,
+                                  (size_t)count * 4 <= tp->fuse_max_bytes ? &fuse : nullptr, &fused);
   if (st != TURQ_OK) return st;
+  if (fused) return TURQ_OK;
   if (staged) {
     int64_t blocks = (count / 4 + 255) / 256;
     if (blocks > 2 * (int64_t)ctx->sm_count) blocks = 2 * (int64_t)ctx->sm_count;
@@ -502,6 +401,51 @@ int32_t turq_qmatmul_rowparallel(turq_tp* tp, const turq_qtensor* qt, const void
     if (e != cudaSuccess) return tp_cuda_fail(tp, e, "stage launch");
   }
   return launch_reduce(tp, count, qt->n_rows, dev_bias, dev_y, s);
+}
+
+int32_t turq_qmatmul_gather(turq_tp* tp, const turq_qtensor* qt, const void* dev_x, int32_t x_dtype, int64_t m,
+                            const int64_t* widths, float* dev_out, int32_t mode, const float* dev_bias, void* stream) {
+  int32_t st = check_ready(tp);
+  if (st != TURQ_OK) return st;
+  turq_ctx* ctx = tp->ctx;
+  if (!qt || !dev_x || !dev_out || !widths) return tp_fail(tp, TURQ_E_INVALID_ARG, "null argument");
+  if (m <= 0 || m > INT32_MAX / 2) return tp_fail(tp, TURQ_E_SHAPE, "m out of range");
+  if (widths[tp->rank] != qt->n_rows) return tp_fail(tp, TURQ_E_SHAPE, "widths[rank] must equal the shard's out-features");
+  turq::TpArgs a{};
+  fill_args(tp, a);
+  int64_t widest = 0;
+  a.col0[0] = 0;
+  for (int p = 0; p < tp->world; p++) {
+    if (widths[p] <= 0) return tp_fail(tp, TURQ_E_SHAPE, "every rank's width must be positive");
+    a.col0[p + 1] = a.col0[p] + widths[p];
+    if (widths[p] > widest) widest = widths[p];
+  }
+  if ((size_t)m * (size_t)widest * 4 > tp->slot_bytes) return tp_fail(tp, TURQ_E_LIMIT, "a rank's share exceeds an exchange slot (turq_tp_create max_bytes)");
+  if ((uintptr_t)dev_out % 16 != 0) return tp_fail(tp, TURQ_E_ALIGN, "dev_out must be 16-byte aligned");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  float* s0 = slot0(tp, tp->rank);
+  float* s1 = s0 + tp->slot_bytes / 4;
+  const int64_t count = m * qt->n_rows;
+  float* staged = nullptr;
+  bool fused = false;
+  st = turq::qmatmul_for_exchange(ctx, qt, dev_x, x_dtype, m, s0, s1, counter_of(tp), mode, s, &staged, nullptr, &fused, dev_bias);
+  if (st != TURQ_OK) return st;
+  if (staged) {
+    int64_t blocks = (count / 4 + 255) / 256;
+    if (blocks > 2 * (int64_t)ctx->sm_count) blocks = 2 * (int64_t)ctx->sm_count;
+    if (blocks < 1) blocks = 1;
+    turq::tp_stage_kernel<<<(unsigned)blocks, 256, 0, s>>>(staged, s0, tp->slot_bytes / 4, counter_of(tp), count);
+    ctx->launches++;
+  }
+  a.m = m;
+  a.n_total = a.col0[tp->world];
+  a.out = dev_out;
+  const int grid = grid_for((int64_t)tp->world * m * turq::TP_THREADS, turq::TP_MAX_BLOCKS);
+  turq::tp_allgather_kernel<<<grid, turq::TP_THREADS, 0, s>>>(a);
+  ctx->launches++;
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return tp_cuda_fail(tp, e, "gather launch");
+  return TURQ_OK;
 }
 
 }  // extern "C"

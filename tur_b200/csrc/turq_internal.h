@@ -79,6 +79,8 @@ cudaError_t launch_gemv_int8(int dtype, const uint8_t* tiles, int64_t n_rows, in
 // beside Q6_K parts at up to 8 rows - each part with its own output and bias. x_remote: x is
 // mapped host memory; it is then read exactly once, by the quantization launch. planes_ready: the
 // caller's own prologue launch already wrote the quantized planes of these rows to act_scratch.
+struct TpArgs;  // tp_exchange.cuh: xchg != nullptr (one part, m <= 32) makes the launch's last CTA run
+                // the tensor-parallel all-reduce of the result itself
 struct GemvPart {
   const uint8_t* tiles;
   int64_t n_rows;
@@ -90,7 +92,8 @@ struct GemvPart {
 cudaError_t launch_gemv_int8_multi(int dtype, const GemvPart* parts, int nparts, int64_t k, const void* x,
                                    int x_dtype, uint8_t* act_scratch, int64_t m, uint8_t* workspace, int* status,
                                    int sm_count, cudaStream_t s, int* launches, bool x_remote = false,
-                                   const unsigned* y_toggle = nullptr, bool planes_ready = false);
+                                   const unsigned* y_toggle = nullptr, bool planes_ready = false,
+                                   const struct TpArgs* xchg = nullptr);
 // out[m, n] = silu(x . Wg^T) * (x . Wu^T) as ONE integer-scheme launch over the row-tiles of both
 // weights interleaved (same type and shape). cudaErrorNotSupported = not applicable, nothing launched.
 cudaError_t launch_gemv_int8_swiglu(int dtype, const uint8_t* gate_tiles, const uint8_t* up_tiles, int64_t n_rows, int64_t k,
@@ -112,7 +115,10 @@ cudaError_t launch_gemm_tc(int dtype, const uint8_t* tiles, int64_t n_rows, int6
 // QMatMul (no bias) whose result has to land in one of two buffers picked on the device: s1 when
 // (*toggle + 1) is odd, else s0 (the exchange slots of tp.cu). In the integer scheme the GEMV's
 // epilogue writes there itself and *staged comes back null; the other schemes compute into
-// context memory, returned in *staged, which the caller still has to copy into the slot.
+// context memory, returned in *staged, which the caller still has to copy into the slot. With
+// `fuse` (the exchange's arguments) an integer-scheme launch of at most 32 rows performs the
+// exchange in its last CTA and *fused comes back true: no exchange launch is needed then.
+// local_bias is added by the matmul itself (column-parallel shards own their bias rows).
 }  // namespace turq
 struct turq_ctx;
 struct turq_qtensor;
@@ -123,6 +129,7 @@ int32_t api_ensure_scratch(turq_ctx* ctx, size_t bytes);  // the context's growa
 int32_t api_ensure_tmp(turq_ctx* ctx, size_t bytes);      // the context's growable result staging
 int32_t api_auto_mode(const turq_ctx* ctx, int64_t n_rows, int64_t n_cols, int64_t m);
 int32_t qmatmul_for_exchange(turq_ctx* ctx, const turq_qtensor* qt, const void* dev_x, int32_t x_dtype, int64_t m, float* s0,
-                             float* s1, const unsigned* toggle, int32_t mode, cudaStream_t s, float** staged);
+                             float* s1, const unsigned* toggle, int32_t mode, cudaStream_t s, float** staged,
+                             const TpArgs* fuse, bool* fused, const float* local_bias = nullptr);
 
 }  // namespace turq

@@ -206,6 +206,22 @@ class TPGroup:
             int(mode), self._ct.c_void_p(bias.data_ptr()) if bias is not None else None, self._stream()))
         return out
 
+    def qmatmul_gather(self, mm, x, widths: Sequence[int], bias=None, mode=None, out=None):
+        """Column-parallel linear with gathered output (the vocabulary-sharded head): this rank's
+        rows of the weight times the full activations, every rank's columns on every rank."""
+        import torch
+        from .quantized import _TORCH_TO_GGML
+        qt = mm.qtensor
+        n, k = qt.shape()
+        x2 = x.reshape(-1, k).contiguous()
+        m = x2.shape[0]
+        out = torch.empty((m, sum(widths)), dtype=torch.float32, device=x.device) if out is None else out
+        w = (self._ct.c_int64 * self.world)(*widths)
+        self.ctx.check(self._lib.turq_qmatmul_gather(
+            self._h, qt._h, x2.data_ptr(), int(_TORCH_TO_GGML[x2.dtype]), m, w, out.data_ptr(), int(mm.mode if mode is None else mode),
+            bias.data_ptr() if bias is not None else None, self._stream()))
+        return out
+
     def loopback_fill(self, peer: int, data=None, signal: bool = True) -> None:
         """Tests: play rank `peer`'s part for the next call (its data and, with `signal`, its flags)."""
         ptr = self._ct.c_void_p(data.data_ptr()) if data is not None else None
