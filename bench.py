@@ -730,7 +730,7 @@ def tp_parity(stack, group, dev, ctx, m=4):
     return out
 
 
-def tp_measure(wl, dev, ctx, rank, world, rows_modes, steps, head=True, own=True, one_gpu=True):
+def tp_measure(wl, dev, ctx, rank, world, rows_modes, steps, head=True, own=True, one_gpu=True, fuse_limit=None):
     """Strong scaling of one sharded pass: ms per pass at `world` ranks (CUDA-graph replay with the
     library's own exchange kernels when own=True, eager launches with NCCL collectives otherwise)
     and, measured by rank 0 alone in the same run, the unsharded pass on one GPU."""
@@ -743,6 +743,8 @@ def tp_measure(wl, dev, ctx, rank, world, rows_modes, steps, head=True, own=True
     points, parity = [], None
     if own and world > 1:
         group = TPGroup(rank, world, max(stack.exchange_bytes(max(r for r, _, _ in rows_modes)), 4 * 25600 * 4), ctx=ctx)
+        if fuse_limit is not None:
+            group.set_fuse_limit(fuse_limit)
         parity = tp_parity(stack, group, dev, ctx)
     for rows, mode_name, xdtype in rows_modes:
         mode = Mode[mode_name]
@@ -810,7 +812,7 @@ def run_gpu_tp(args):
     sampler = ClockSampler(local)
     with sampler:
         obj = tp_measure(wl, dev, ctx, rank, world, [(m, args.mode, args.xdtype)], args.steps, head=not args.no_head,
-                         own=not args.nccl, one_gpu=not args.no_extras)
+                         own=not args.nccl, one_gpu=not args.no_extras, fuse_limit=args.tp_fuse_limit)
     if rank == 0:
         pt = obj["points"][0]
         ms = pt["ms_per_step"]
@@ -850,6 +852,7 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=20)
     ap.add_argument("--cpu-steps", type=int, default=20, help="steps of about half a second each in the cpu_baseline leg")
     ap.add_argument("--tp", action="store_true", help="tensor-parallel over all ranks (the sharded cfg5 workload)")
+    ap.add_argument("--tp-fuse-limit", type=int, default=None, help="tensor-parallel arm: largest result (bytes) exchanged inside the matmul kernel")
     ap.add_argument("--no-multi", action="store_true", help="one launch per weight (no q|k, gate|up multi-weight launches)")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of the timed pass's outputs")
     ap.add_argument("--no-extras", action="store_true", help="skip the sweep / prefill / other-config objects of the default run")

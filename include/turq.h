@@ -260,6 +260,9 @@ int32_t turq_tp_connect(turq_tp* tp, const void* handles /* world * TURQ_TP_HAND
 int32_t turq_tp_destroy(turq_tp* tp);
 /* Upper bound of every device-side wait for a peer, in SM clock cycles (default 2e9, about 1 s). */
 int32_t turq_tp_set_wait_limit(turq_tp* tp, int64_t cycles);
+/* Largest result (m * n * 4 bytes) turq_qmatmul_rowparallel exchanges inside the matmul kernel
+ * itself (default 64 KB); 0 = always use the separate exchange launch. Same value on every rank. */
+int32_t turq_tp_set_fuse_limit(turq_tp* tp, int64_t bytes);
 /* Clears this rank's flags and call counter. Collective in effect: call it on every rank, with
  * no group call in flight (the host synchronizes the ranks around it). */
 int32_t turq_tp_reset(turq_tp* tp);

@@ -54,6 +54,7 @@ SIGNATURES = {
     "turq_tp_connect": (c_i32, [c_vp, c_vp]),
     "turq_tp_destroy": (c_i32, [c_vp]),
     "turq_tp_set_wait_limit": (c_i32, [c_vp, c_i64]),
+    "turq_tp_set_fuse_limit": (c_i32, [c_vp, c_i64]),
     "turq_tp_reset": (c_i32, [c_vp]),
     "turq_tp_allreduce": (c_i32, [c_vp, c_vp, c_vp, c_i64, c_vp]),
     "turq_tp_allgather": (c_i32, [c_vp, c_vp, c_i64, c_vp, c_vp, c_vp]),

@@ -582,7 +582,11 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
     }
   }
   if (a.xchg_on) {
-    __shared__ int s_last, s_ok;
+    // two words of the dynamic shared memory behind the barriers (static shared memory would
+    // eat into the opt-in maximum the launch configuration asks for)
+    int* s_words = reinterpret_cast<int*>(act_full + 1);
+    int& s_last = s_words[0];
+    int& s_ok = s_words[1];
     if (threadIdx.x == 0) {
       __threadfence();  // this CTA's outputs (written before the barrier above) before its ticket
       s_last = atomicAdd(a.xchg.counter + 2, 1u) == gridDim.x - 1 ? 1 : 0;

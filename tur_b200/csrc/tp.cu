@@ -281,6 +281,12 @@ int32_t turq_tp_set_wait_limit(turq_tp* tp, int64_t cycles) {
   return TURQ_OK;
 }
 
+int32_t turq_tp_set_fuse_limit(turq_tp* tp, int64_t bytes) {
+  if (!tp || bytes < 0) return TURQ_E_INVALID_ARG;
+  tp->fuse_max_bytes = (size_t)bytes;
+  return TURQ_OK;
+}
+
 int32_t turq_tp_reset(turq_tp* tp) {
   if (!tp) return TURQ_E_INVALID_ARG;
   cudaError_t e = cudaSetDevice(tp->ctx->device);

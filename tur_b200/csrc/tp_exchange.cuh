@@ -84,11 +84,15 @@ __device__ __forceinline__ void tp_reduce_range(const TpArgs& a, size_t slot_off
   const int64_t nvec = a.count >> 2;
   const bool vec_bias = a.bias && (a.n & 3) == 0;
   for (int64_t v = first_vec; v < nvec; v += vec_stride) {
-    float4 acc = ld_peer_v4(a.peer_data[0] + slot_off + 4 * v);
-    for (int p = 1; p < a.world; p++) {
-      const float4 t = ld_peer_v4(a.peer_data[p] + slot_off + 4 * v);
-      acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
-    }
+    // all ranks' loads go out before the first add: one peer round trip per group, not one per rank
+    float4 t[TP_MAX_RANKS];
+#pragma unroll
+    for (int p = 0; p < TP_MAX_RANKS; p++)
+      if (p < a.world) t[p] = ld_peer_v4(a.peer_data[p] + slot_off + 4 * v);
+    float4 acc = t[0];
+#pragma unroll
+    for (int p = 1; p < TP_MAX_RANKS; p++)
+      if (p < a.world) { acc.x += t[p].x; acc.y += t[p].y; acc.z += t[p].z; acc.w += t[p].w; }
     if (a.bias) {
       if (vec_bias) {
         const float4 bb = *reinterpret_cast<const float4*>(a.bias + (4 * v) % a.n);

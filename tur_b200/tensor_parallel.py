@@ -169,6 +169,10 @@ class TPGroup:
     def set_wait_limit(self, cycles: int) -> None:
         self.ctx.check(self._lib.turq_tp_set_wait_limit(self._h, cycles))
 
+    def set_fuse_limit(self, nbytes: int) -> None:
+        """Largest result the row-parallel matmul exchanges inside its own kernel (0: never)."""
+        self.ctx.check(self._lib.turq_tp_set_fuse_limit(self._h, nbytes))
+
     def reset(self) -> None:
         self.ctx.check(self._lib.turq_tp_reset(self._h))
 
