@@ -275,9 +275,8 @@ int32_t turq_tp_allgather(turq_tp* tp, const float* dev_in, int64_t m, const int
 /* Row-parallel LinearX::forward: qt holds this rank's range of input columns, dev_x the matching
  * activation columns [m, n_cols of the shard]; dev_y [m, n_rows] receives the sum over the ranks
  * (+ bias) on every rank. In the integer scheme the GEMV's epilogue writes its partial result
- * straight into the exchange memory. For results up to 64 KB (decode) the CTA of that launch
- * that finishes last then signals the peers, waits and adds: compute and all-reduce are ONE
- * kernel. Larger results get a multi-CTA exchange launch behind the matmul. */
+ * straight into the exchange memory. For results up to 64 KB (decode) the CTAs of that launch
+ * that finish last then signal the peers, wait and add: compute and all-reduce are ONE kernel. Larger results get a multi-CTA exchange launch behind the matmul. */
 int32_t turq_qmatmul_rowparallel(turq_tp* tp, const turq_qtensor* qt, const void* dev_x, int32_t x_dtype,
                                  int64_t m, float* dev_y, int32_t mode, const float* dev_bias, void* stream);
 /* Column-parallel LinearX::forward with gathered output (the vocabulary-sharded head): qt holds

@@ -131,8 +131,8 @@ struct StreamArgs {
   int stages;
   int stage_bytes;
   SmemPlan sp;
-  // Row-parallel linear of a tensor-parallel group, small outputs: the CTA that finishes last
-  // performs the exchange itself (signal the peers, wait, add all ranks' partial results in rank
+  // Row-parallel linear of a tensor-parallel group, small outputs: the CTAs that finish last
+  // perform the exchange themselves (signal the peers, wait, add all ranks' partial results in rank
   // order into xchg.out) - compute and collective in one kernel. y / y_alt are then the two
   // exchange slots and y_toggle the group's call counter.
   int xchg_on;
@@ -582,32 +582,53 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
     }
   }
   if (a.xchg_on) {
-    // two words of the dynamic shared memory behind the barriers (static shared memory would
-    // eat into the opt-in maximum the launch configuration asks for)
+    // The CTAs that finish last exchange: the last `nb` tickets (nb = enough CTAs for one float4
+    // group per thread, at most 16) wait the short while until every CTA of the launch has
+    // written its part of the slot, then ticket order gives each its share of the result and the
+    // row of flags it pairs on with the peers' CTA of the same role.
+    // Two words of the dynamic shared memory behind the barriers hold the CTA-wide decisions
+    // (static shared memory would eat into the opt-in maximum the launch configuration asks for).
     int* s_words = reinterpret_cast<int*>(act_full + 1);
-    int& s_last = s_words[0];
+    int& s_role = s_words[0];
     int& s_ok = s_words[1];
+    const int G2 = (int)gridDim.x;
+    const int64_t nvec = (a.xchg.count + 3) >> 2;
+    int nb = (int)((nvec + THREADS - 1) / THREADS);
+    if (nb > 16) nb = 16;
+    if (nb > G2) nb = G2;
+    if (nb < 1) nb = 1;
     if (threadIdx.x == 0) {
       __threadfence();  // this CTA's outputs (written before the barrier above) before its ticket
-      s_last = atomicAdd(a.xchg.counter + 2, 1u) == gridDim.x - 1 ? 1 : 0;
+      const int ticket = (int)atomicAdd(a.xchg.counter + 2, 1u);
+      s_role = ticket - (G2 - nb);
+      if (s_role >= 0) {
+        const long long t0 = clock64();
+        while (*reinterpret_cast<volatile unsigned*>(a.xchg.counter + 2) < (unsigned)G2) {
+          if (clock64() - t0 > a.xchg.wait_cycles) break;  // a CTA of this launch gave up: the rendezvous below reports it
+          __nanosleep(32);
+        }
+        __threadfence();
+      }
     }
     __syncthreads();
-    if (s_last) {
-      // every CTA of this launch has written its part of the exchange slot
-      __threadfence();
+    if (s_role >= 0) {
       const unsigned seq = *reinterpret_cast<volatile unsigned*>(a.xchg.counter) + 1u;
       const size_t slot_off = (seq & 1u) ? a.xchg.slot_elems : 0;
-      const bool ok = tp_rendezvous(a.xchg, seq, &s_ok, 0);
-      if (ok) tp_reduce_range(a.xchg, slot_off, threadIdx.x, THREADS, true);
+      const bool ok = tp_rendezvous(a.xchg, seq, &s_ok, s_role);
+      if (ok) tp_reduce_range(a.xchg, slot_off, (int64_t)s_role * THREADS + threadIdx.x, (int64_t)nb * THREADS, s_role == 0);
       __syncthreads();
       if (threadIdx.x == 0) {
         if (!ok) {
           *reinterpret_cast<volatile int*>(a.status) = TURQ_E_TIMEOUT;
           __threadfence_system();
         }
-        a.xchg.counter[2] = 0;
         __threadfence();
-        *reinterpret_cast<volatile unsigned*>(a.xchg.counter) = seq;
+        if (atomicAdd(a.xchg.counter + 1, 1u) == (unsigned)nb - 1) {  // last of the exchanging CTAs
+          a.xchg.counter[1] = 0;
+          a.xchg.counter[2] = 0;
+          __threadfence();
+          *reinterpret_cast<volatile unsigned*>(a.xchg.counter) = seq;
+        }
       }
     }
   }
