@@ -35,6 +35,8 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--pair", action="store_true", help="qmatmul: two weights of this shape that share x as ONE multi-weight "
+                                                        "launch (how a decoder pass issues ffn_gate|up)")
     args = ap.parse_args()
 
     dev = torch.device("cuda", 0)
@@ -43,6 +45,8 @@ def main() -> None:
     be, bb = BLOCK[dt]
     wbytes = args.n * (args.k // be) * bb
     copies = args.copies or max(2, min(64, int(4 * 126e6 / wbytes) + 1))
+    if args.pair:
+        copies = 2 * ((copies + 1) // 2)
     ws = []
     for i in range(copies):
         blocks = random_blocks(dt, args.n, args.k, SEED + i, dev)
@@ -57,9 +61,13 @@ def main() -> None:
     if args.op == "qmatmul":
         y = torch.empty((args.m, args.n), dtype=torch.float32, device=dev)
 
+        y2 = torch.empty_like(y)
+
         def call(w):
             w.forward(x, mode=mode, out=y)
         alg_bytes = wbytes + args.m * args.k * x.element_size() + args.m * args.n * 4
+        if args.pair:
+            alg_bytes = 2 * (wbytes + args.m * args.n * 4) + args.m * args.k * x.element_size()
         flops = 2.0 * args.m * args.n * args.k
     elif args.op == "embedding":
         # --m ids drawn from the table's rows; algorithmic bytes = the rows read + the f32 rows written
@@ -81,6 +89,10 @@ def main() -> None:
         flops = 0.0
 
     def one_round():
+        if args.pair and args.op == "qmatmul":
+            for a, b in zip(ws[0::2], ws[1::2]):
+                QMatMul.forward_multi([a, b], x, mode=mode, outs=[y, y2])
+            return
         for w in ws:
             call(w)
 
@@ -97,7 +109,7 @@ def main() -> None:
             one_round()
         runner = graph.replay
         runner()
-    launches_per_call = (ctx.launch_count() - l0) / copies if not args.no_graph else None
+    launches_per_call = (ctx.launch_count() - l0) / (copies // 2 if (args.pair and args.op == "qmatmul") else copies) if not args.no_graph else None
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -105,10 +117,13 @@ def main() -> None:
         runner()
     e1.record()
     torch.cuda.synchronize()
-    us = e0.elapsed_time(e1) * 1e3 / (args.iters * copies)
+    calls = copies // 2 if (args.pair and args.op == "qmatmul") else copies
+    us = e0.elapsed_time(e1) * 1e3 / (args.iters * calls)
+    if args.pair and args.op == "qmatmul":
+        wbytes, flops = 2 * wbytes, 2 * flops
     print(json.dumps({
         "op": args.op, "dtype": args.dtype, "n": args.n, "k": args.k, "m": args.m, "mode": args.mode,
-        "copies": copies, "iters": args.iters, "us_per_call": us, "launches_per_call": launches_per_call,
+        "copies": copies, "pair": bool(args.pair), "iters": args.iters, "us_per_call": us, "launches_per_call": launches_per_call,
         "algorithmic_bytes": alg_bytes, "GBps": alg_bytes / us / 1e3, "weight_GBps": wbytes / us / 1e3,
         "TFLOPs": flops / us / 1e6,
     }))
