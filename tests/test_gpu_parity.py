@@ -554,3 +554,22 @@ def test_tensor_core_mode_keeps_its_accuracy_for_tiny_and_huge_rows(tq, dt):
     want = oracle.matmul_f64(dt, w, n, k, x)
     for r in range(m):
         assert oracle.rel_fro(y[r], want[r]) < TOL, r
+
+
+def test_tensor_core_multi_call_converts_x_once_and_matches_separate_calls(tq):
+    """q|k|v / gate|up in the tensor-core scheme: one f16 conversion of x for all the weights, the
+    bits of the separate calls."""
+    k, m = 1024, 200
+    shapes = [(oracle.Q4_K, 384), (oracle.Q4_K, 128), (oracle.Q6_K, 256)]
+    ws = [make_weight(t, n, k, SEED + 600 + n) for t, n in shapes]
+    mms = [tq.QMatMul.from_arc(tq.QTensor.new(w, tq.GgmlDType(t), (n, k))) for w, (t, n) in zip(ws, shapes)]
+    x = torch.from_numpy(np.random.default_rng(SEED + 601).standard_normal((m, k)).astype(np.float32)).cuda()
+    bias = torch.from_numpy(np.random.default_rng(SEED + 602).standard_normal(128).astype(np.float32)).cuda()
+    sep = [mm.forward(x, bias=bias if i == 1 else None, mode=tq.Mode.TENSOR_CORE) for i, mm in enumerate(mms)]
+    l0 = tq.context().launch_count()
+    got = tq.QMatMul.forward_multi(mms, x, biases=[None, bias, None], mode=tq.Mode.TENSOR_CORE)
+    assert tq.context().launch_count() - l0 == 1 + len(mms)          # one conversion, one GEMM per weight
+    tq.context().poll_status()
+    for g, s_, w, (t, n) in zip(got, sep, ws, shapes):
+        assert torch.equal(g, s_)
+    assert oracle.rel_fro(got[2].cpu().numpy(), oracle.matmul_f64(oracle.Q6_K, ws[2], 256, k, x.cpu().numpy())) < TOL

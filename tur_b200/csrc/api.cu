@@ -488,6 +488,29 @@ static int32_t qmatmul_multi_impl(turq_ctx* ctx, int32_t count, const turq_qtens
     for (int i = 0; i < count; i++) rows_all += qts[i]->n_rows;
     eff = auto_mode(ctx, rows_all, qts[0]->n_cols, m);
   }
+  if (eff == TURQ_MODE_TENSOR_CORE && count > 1 && !x_remote && qts[0]->n_cols % 64 == 0 && m > 0 && m <= INT32_MAX / 2 &&
+      (x_dtype == TURQ_F32 || x_dtype == TURQ_BF16) && (uintptr_t)dev_x % 16 == 0) {
+    // tensor-core scheme: x is converted to the f16 operand once for all the weights
+    const int64_t k = qts[0]->n_cols;
+    size_t need = 0;
+    for (int i = 0; i < count; i++) {
+      if (qts[i]->device != ctx->device) return fail(ctx, TURQ_E_INVALID_ARG, "tensor lives on device %d, context on %d", qts[i]->device, ctx->device);
+      const size_t b = turq::gemm_tc_scratch_bytes(m, k, qts[i]->n_rows, ctx->sm_count);
+      if (b > need) need = b;
+    }
+    TQ_CUDA(ctx, cudaSetDevice(ctx->device));
+    int32_t st = ensure(ctx, &ctx->scratch, &ctx->scratch_bytes, need);
+    if (st != TURQ_OK) return st;
+    for (int i = 0; i < count; i++) {
+      int launches = 0;
+      cudaError_t e = turq::launch_gemm_tc(qts[i]->dtype, qts[i]->tiles, qts[i]->n_rows, k, dev_x, x_dtype, m, dev_ys[i],
+                                           dev_biases ? dev_biases[i] : nullptr, ctx->scratch, ctx->sm_count,
+                                           static_cast<cudaStream_t>(stream), &launches, ctx->dev_status, i > 0);
+      ctx->launches += launches;
+      if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_multi launch");
+    }
+    return TURQ_OK;
+  }
   if (!same || eff != TURQ_MODE_INT8_ACT || (count == 1 && !x_remote)) {
     if (x_remote) return fail(ctx, TURQ_E_INVALID_ARG, "host-mapped activations need the integer scheme and one activation format");
     for (int i = 0; i < count; i++) {

@@ -578,16 +578,19 @@ size_t gemm_tc_scratch_bytes(int64_t m, int64_t k, int64_t n_rows, int sm_count)
 
 cudaError_t launch_gemm_tc(int dtype, const uint8_t* tiles, int64_t n_rows, int64_t k, const void* x, int x_dtype,
                            int64_t m, float* y, const float* bias, uint8_t* scratch, int sm_count, cudaStream_t s,
-                           int* launches, int* dev_status_word) {
+                           int* launches, int* dev_status_word, bool x_prepared) {
   if (k % BK != 0 || m <= 0 || m > INT32_MAX || k > INT32_MAX) return cudaErrorInvalidValue;
   EncodeTiledFn enc = encode_fn();
   if (!enc) return cudaErrorNotSupported;
   __half* xh = reinterpret_cast<__half*>(scratch);
   float* rscale = reinterpret_cast<float*>(scratch + (((size_t)m * (size_t)k * 2 + 255) & ~(size_t)255));
-  prep_act_kernel<<<(unsigned)m, 256, 0, s>>>(x, x_dtype == TQ_BF16, k, xh, rscale);
-  if (launches) (*launches)++;
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return e;
+  cudaError_t e = cudaSuccess;
+  if (!x_prepared) {  // several weights that read the same x share one conversion
+    prep_act_kernel<<<(unsigned)m, 256, 0, s>>>(x, x_dtype == TQ_BF16, k, xh, rscale);
+    if (launches) (*launches)++;
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+  }
 
   CUtensorMap map;
   const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)m};
