@@ -92,6 +92,14 @@ def _rank_main(rank, world, port, q):
         want_y = oracle.matmul_f64(Q6_K, db, hidden, inter, want_h)
         err = oracle.rel_fro(y.numpy(), want_y)
         assert err < 1e-5, err
+        # an attention projection split by whole heads of 80 rows, three heads on two ranks (2 + 1):
+        # the gather inside TPLinear must use the shard's own unit, not a fixed 16
+        attn_q = Weight("attn_q", 240, hidden, Q4_K, "hidden", "column")
+        qb = oracle.quantize(Q4_K, (rng.standard_normal((240, hidden)) * 0.02).astype(np.float32))
+        qsh = shard_of(attn_q, world, rank, row_unit_for(attn_q, 80))
+        assert qsh.unit == 80 and qsh.shape[0] == (160 if rank == 0 else 80)
+        q_full = TPLinear(attn_q, qsh, cpu_matmul(attn_q, qb, qsh), gather_output=True)(torch.from_numpy(x))
+        assert np.array_equal(q_full.numpy(), oracle.matmul_f64(Q4_K, qb, 240, hidden, x))
         # every rank ends with the same, complete result
         ys = [torch.empty_like(y) for _ in range(world)]
         dist.all_gather(ys, y)

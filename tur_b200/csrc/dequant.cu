@@ -74,9 +74,11 @@ static cudaError_t launch_dt(const uint8_t* tiles, void* out, int out_dtype, int
   return cudaGetLastError();
 }
 
-// Embedding lookup on the quantized table: out[i, :] = dequantize(row ids[i]). One warp per
-// (id, K-tile); the warp decodes the tile holding the row with the same code as the full
-// dequantize (so the values are the same bits) and the four lanes that own the row store it.
+// Embedding lookup on the quantized table: out[i, :] = dequantize(row ids[i]). Four lanes per
+// (id, K-tile): in the fragment layout lane 4g + c of a full-tile decode holds rows g and g + 8,
+// so the four lanes of column group c = 0..3 with g = row % 8 hold the whole row. Each quad runs
+// the full dequantize's per-lane code for that lane position only (the values are the same bits)
+// and reads an eighth of the tile instead of all of it. A warp serves eight (id, K-tile) pairs.
 // An id outside [0, n_rows) gives a row of zeros and raises the status word.
 template <int DT, class T>
 __global__ void __launch_bounds__(256) gather_rows_kernel(const uint8_t* __restrict__ tiles, const int32_t* __restrict__ ids,
@@ -85,17 +87,17 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const uint8_t* __restr
   constexpr int TB = 16 * (DT == TQ_Q8_0 ? 34 : DT == TQ_Q4_K ? 144 : DT == TQ_Q5_K ? 176 : 210);
   constexpr int KE = DT == TQ_Q8_0 ? 32 : 256;
   const int lane = threadIdx.x & 31;
-  const int g = lane >> 2;
-  int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
-  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const int c = lane & 3;
+  const int64_t quad = (((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5) * 8 + (lane >> 2);
+  const int64_t nquads = (((int64_t)gridDim.x * blockDim.x) >> 5) * 8;
   const int64_t total = n_ids * ktiles;
-  for (int64_t u = warp; u < total; u += nwarps) {
+  for (int64_t u = quad; u < total; u += nquads) {
     const int64_t i = u / ktiles, kt = u - i * ktiles;
     const int64_t row = ids[i];
     T* dst = out + i * k + kt * KE;
     if (row < 0 || row >= n_rows) {
-      for (int e = lane; e < KE; e += 32) dst[e] = cvt_out<T>(0.f);
-      if (lane == 0 && kt == 0) {
+      for (int e = c; e < KE; e += 4) dst[e] = cvt_out<T>(0.f);
+      if (c == 0 && kt == 0) {
         *reinterpret_cast<volatile int*>(status) = 1;  // TURQ_E_INVALID_ARG; the word may be mapped host memory
         __threadfence_system();
       }
@@ -103,8 +105,9 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const uint8_t* __restr
     }
     const int r16 = (int)(row & 15);
     const uint8_t* t = tiles + ((row >> 4) * ktiles + kt) * TB;
-    decode_tile<DT>(t, lane, [&](int hr, int off, const auto& v) {
-      if (g + 8 * hr == r16) store_run(dst + off, v);
+    const int want_hr = r16 >> 3;
+    decode_tile<DT>(t, 4 * (r16 & 7) + c, [&](int hr, int off, const auto& v) {
+      if (hr == want_hr) store_run(dst + off, v);
     });
   }
 }
@@ -115,7 +118,7 @@ static cudaError_t launch_gather_dt(const uint8_t* tiles, const int32_t* ids, vo
   const int64_t ktiles = k / tq_block_elems(DT);
   const int64_t total = n_ids * ktiles;
   if (total == 0) return cudaSuccess;
-  int64_t blocks = (total + 7) / 8;
+  int64_t blocks = (total + 63) / 64;  // eight (id, K-tile) pairs per warp, eight warps per block
   if (blocks > (int64_t)device_sm_count() * 16) blocks = (int64_t)device_sm_count() * 16;
   switch (out_dtype) {
     case TQ_F32:

@@ -232,18 +232,28 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
   };
   const int u0 = start_of(b), u1 = start_of(b + 1);
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < a.stages; s++) {
-      for (int w = 0; w < NW; w++) mbar_init(&full[s * NW + w], 1);
-      mbar_init(&empty[s], NW);
+  {
+    // one barrier per thread: ~60 mbarrier.init in sequence on one thread cost most of a
+    // microsecond before the first copy could be issued
+    const int tid = (int)threadIdx.x;
+    const int nfull = a.stages * NW;
+    int i = tid;
+    bool did = true;
+    if (i < nfull) {
+      mbar_init(&full[i], 1);
+    } else if ((i -= nfull) < a.stages) {
+      mbar_init(&empty[i], NW);
+    } else if ((i -= a.stages) < RED_SLOTS) {
+      mbar_init(&red_full[i], NW);
+    } else if ((i -= RED_SLOTS) < RED_SLOTS) {
+      mbar_init(&red_empty[i], 1);
+    } else if (i == RED_SLOTS) {
+      mbar_init(act_full, 1);
+      *abort_flag = 0;
+    } else {
+      did = false;
     }
-    for (int s = 0; s < RED_SLOTS; s++) {
-      mbar_init(&red_full[s], NW);
-      mbar_init(&red_empty[s], 1);
-    }
-    mbar_init(act_full, 1);
-    *abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (did) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
   // Programmatic dependent launch (when the launch carries the attribute): the next kernel of
