@@ -42,9 +42,12 @@ struct ActOut {
 // One warp per 256-element block: lane owns elements 8*lane .. 8*lane+7.
 __global__ void __launch_bounds__(128) quant_q8k_kernel(const void* __restrict__ x, int is_bf16, int64_t m,
                                                         int64_t k, ActOut out) {
-  // A GEMV launched with programmatic stream serialization may start (and prefetch weights)
-  // while this grid runs; it waits for this grid's completion before it reads the planes.
+  // Both this launch and the GEMV behind it carry the programmatic-stream-serialization
+  // attribute. Trigger first: the GEMV may become resident and stream weights at once (it waits
+  // for this grid's completion before it reads the planes). Then wait: the preceding kernel may
+  // still be reading the planes this grid is about to overwrite, and may be producing x.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int lane = threadIdx.x & 31;
   const int64_t nblk = k >> 8;
   const int64_t total = m * nblk;
@@ -77,9 +80,12 @@ __global__ void __launch_bounds__(128) quant_q8k_kernel(const void* __restrict__
 // Four lanes per 32-element block; a warp covers 8 consecutive blocks of one row.
 __global__ void __launch_bounds__(128) quant_q8_0_kernel(const void* __restrict__ x, int is_bf16, int64_t m,
                                                          int64_t k, ActOut out) {
-  // A GEMV launched with programmatic stream serialization may start (and prefetch weights)
-  // while this grid runs; it waits for this grid's completion before it reads the planes.
+  // Both this launch and the GEMV behind it carry the programmatic-stream-serialization
+  // attribute. Trigger first: the GEMV may become resident and stream weights at once (it waits
+  // for this grid's completion before it reads the planes). Then wait: the preceding kernel may
+  // still be reading the planes this grid is about to overwrite, and may be producing x.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int lane = threadIdx.x & 31;
   const int64_t nblk = k >> 5;
   const int64_t groups = (nblk + 7) >> 3;  // warp-sized groups of 8 blocks per row
@@ -116,6 +122,22 @@ __global__ void __launch_bounds__(128) quant_q8_0_kernel(const void* __restrict_
   }
 }
 
+// Launch that may be scheduled while the preceding kernel of the stream still runs (the kernels
+// order themselves with griddepcontrol.wait).
+template <class... Args>
+static cudaError_t launch_pdl(void (*kernel)(Args...), unsigned blocks, int threads, cudaStream_t s, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(blocks);
+  cfg.blockDim = dim3((unsigned)threads);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 static cudaError_t launch_act(int fmt, const void* x, int x_dtype, int64_t m, int64_t k, ActOut out,
                               cudaStream_t s) {
   if (m == 0 || k == 0) return cudaSuccess;
@@ -125,12 +147,12 @@ static cudaError_t launch_act(int fmt, const void* x, int x_dtype, int64_t m, in
     int64_t warps = m * (k >> 8);
     int64_t blocks = (warps + 3) / 4;
     if (blocks > (int64_t)device_sm_count() * 16) blocks = (int64_t)device_sm_count() * 16;
-    quant_q8k_kernel<<<(unsigned)blocks, threads, 0, s>>>(x, is_bf16, m, k, out);
+    return launch_pdl(quant_q8k_kernel, (unsigned)blocks, threads, s, x, is_bf16, m, k, out);
   } else if (fmt == TQ_Q8_0) {
     int64_t warps = m * (((k >> 5) + 7) >> 3);
     int64_t blocks = (warps + 3) / 4;
     if (blocks > (int64_t)device_sm_count() * 16) blocks = (int64_t)device_sm_count() * 16;
-    quant_q8_0_kernel<<<(unsigned)blocks, threads, 0, s>>>(x, is_bf16, m, k, out);
+    return launch_pdl(quant_q8_0_kernel, (unsigned)blocks, threads, s, x, is_bf16, m, k, out);
   } else {
     return cudaErrorInvalidValue;
   }

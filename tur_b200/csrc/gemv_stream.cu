@@ -285,13 +285,21 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
         if constexpr (NEED16) bulk_g2s(smem + sp.act_bs16, a.gact.bs16, s16_bytes, act_full);
         if constexpr (NEED32) bulk_g2s(smem + sp.act_bs32, a.gact.bs32, s32_bytes, act_full);
       };
-      if constexpr (ACT == ACT_STAGED) copy_planes();
+      // The first ring fill goes out before the planes: weights never depend on the preceding
+      // kernels, the planes have to wait for them. The consumers cannot free a stage before they
+      // have the planes, so the planes are requested before the first wait that needs a free stage.
+      bool planes_pending = ACT == ACT_STAGED;
       StageWalk w;
       w.init(u0, u1, KU);
-      int slot = 0;
+      int slot = 0, issued = 0;
       uint32_t ph = 0;
       while (!w.done()) {
         const int n = w.count();
+        if (planes_pending && issued == a.stages) {
+          copy_planes();
+          planes_pending = false;
+        }
+        issued++;
         if (!mbar_wait(&empty[slot], ph ^ 1u, abort_flag)) break;
         // one copy per consumer warp (its tile, or its group of Q8_0 tiles), each completing on
         // that warp's own barrier: a warp starts as soon as its bytes are there
@@ -318,6 +326,7 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
         w.next_row_if_needed();
         if (++slot == a.stages) { slot = 0; ph ^= 1u; }
       }
+      if (planes_pending) copy_planes();  // fewer stages of work than the ring holds
     }
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   } else if (warp < NW) {
@@ -688,9 +697,13 @@ static cudaError_t launch_one(StreamArgs a, int grid, int smem_bytes, cudaStream
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  // Always-on variant for testing (TURQ_GEMV_PDL=1); by default only the launch that follows
-  // its own quantization launch overlaps with it (TURQ_GEMV_PDL_PAIR=0 turns that off).
-  static const int pdl = tuning_env("TURQ_GEMV_PDL", 0);
+  // Every GEMV launch carries the attribute: its CTAs may become resident, set up and start
+  // streaming weights while the preceding kernel of the stream still runs (measured on B200:
+  // cfg2 decode pass 1.75 -> 1.67 ms, cfg1 0.53 -> 0.42 ms, cfg4 1.33 -> 1.22 ms, nothing slower;
+  // triggering from the kernel's start instead of after the last copy made no difference).
+  // TURQ_GEMV_PDL=0 (tuning builds) restricts it to the launch that follows its own quantization
+  // launch, TURQ_GEMV_PDL_PAIR=0 turns that off too.
+  static const int pdl = tuning_env("TURQ_GEMV_PDL", 1);
   static const int pdl_pair = tuning_env("TURQ_GEMV_PDL_PAIR", 1);
   cfg.numAttrs = (pdl || (after_quant && pdl_pair)) ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<DT, MG, ACT, DT2>, a);
