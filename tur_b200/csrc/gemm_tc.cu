@@ -308,6 +308,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (activations)
     if (lane == 0) {
+      // launched with programmatic stream serialization: the f16 operand comes from the
+      // conversion launch before this one (the weight side below starts without waiting)
+      asm volatile("griddepcontrol.wait;" ::: "memory");
       for (int kb = 0; kb < kblocks; kb++) {
         const int s = kb % ST;
         const uint32_t ph = (uint32_t)(kb / ST) & 1u;
@@ -415,6 +418,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
       }
     }
     // ---- epilogue: TMEM lanes 32*(warp%4).., columns split over the warps of each lane quarter
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the next launch may set up behind this one
+    asm volatile("griddepcontrol.wait;" ::: "memory");               // y / the partial sums may still be read by the predecessor
     if (ok) ok = bar_wait(accum, 0, abort_flag);
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -470,6 +475,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
 __global__ void __launch_bounds__(256) prep_act_kernel(const void* __restrict__ x, int is_bf16, int64_t k,
                                                         __half* __restrict__ xh, float* __restrict__ rscale) {
   __shared__ float wmax[8];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the GEMM behind may start on its weights
+  asm volatile("griddepcontrol.wait;" ::: "memory");               // x may still be written, the operand buffer still read
   const int64_t row = blockIdx.x;
   float amax = 0.f;
   for (int64_t i = threadIdx.x; i < k; i += blockDim.x) amax = fmaxf(amax, fabsf(load_act_f32(x, is_bf16, row * k + i)));
@@ -497,6 +504,8 @@ __global__ void __launch_bounds__(256) prep_act_kernel(const void* __restrict__ 
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part, int splits, int64_t total,
                                                              int64_t n_rows, const float* __restrict__ bias,
                                                              float* __restrict__ y) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int64_t i4 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (i4 >= total) return;
   if (i4 + 4 <= total && (n_rows & 3) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0) {
@@ -518,6 +527,23 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
       y[i] = acc;
     }
   }
+}
+
+// Launch with programmatic stream serialization: the kernel may be scheduled while its
+// predecessor in the stream still runs and orders itself with griddepcontrol.wait.
+template <class... Params, class... Args>
+cudaError_t launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -549,8 +575,7 @@ cudaError_t launch_tc_bn(const CUtensorMap& map, const GemmArgs& a, cudaStream_t
     configured.set(dev);
   }
   dim3 grid((unsigned)((a.n_rows + BM - 1) / BM), (unsigned)((a.m + BN - 1) / BN), (unsigned)a.splits);
-  gemm_tc_kernel<DT, BN><<<grid, TC_THREADS, SMEM, s>>>(map, a);
-  return cudaGetLastError();
+  return launch_pdl(gemm_tc_kernel<DT, BN>, grid, dim3(TC_THREADS), (size_t)SMEM, s, map, a);
 }
 
 template <int DT>
@@ -586,9 +611,8 @@ cudaError_t launch_gemm_tc(int dtype, const uint8_t* tiles, int64_t n_rows, int6
   float* rscale = reinterpret_cast<float*>(scratch + (((size_t)m * (size_t)k * 2 + 255) & ~(size_t)255));
   cudaError_t e = cudaSuccess;
   if (!x_prepared) {  // several weights that read the same x share one conversion
-    prep_act_kernel<<<(unsigned)m, 256, 0, s>>>(x, x_dtype == TQ_BF16, k, xh, rscale);
+    e = launch_pdl(prep_act_kernel, dim3((unsigned)m), dim3(256), 0, s, x, (int)(x_dtype == TQ_BF16), k, xh, rscale);
     if (launches) (*launches)++;
-    e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }
 
@@ -626,9 +650,10 @@ cudaError_t launch_gemm_tc(int dtype, const uint8_t* tiles, int64_t n_rows, int6
   if (launches) (*launches)++;
   if (e != cudaSuccess || splits == 1) return e;
   const int64_t total = m * n_rows;
-  splitk_reduce_kernel<<<(unsigned)((total + 1023) / 1024), 256, 0, s>>>(partial, splits, total, n_rows, bias, y);
+  e = launch_pdl(splitk_reduce_kernel, dim3((unsigned)((total + 1023) / 1024)), dim3(256), 0, s, (const float*)partial, splits,
+                 total, n_rows, bias, y);
   if (launches) (*launches)++;
-  return cudaGetLastError();
+  return e;
 }
 
 }  // namespace turq
