@@ -37,8 +37,13 @@
 
 namespace turq {
 
+// The exchange kernels are launched with programmatic stream serialization: they let the next
+// launch (a GEMV that starts by streaming weights) be scheduled at once, and wait themselves for
+// the kernel that filled the slot before they tell the peers about it.
 __global__ void __launch_bounds__(TP_THREADS) tp_allreduce_kernel(const TpArgs a) {
   __shared__ int s_ok;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const unsigned seq = *reinterpret_cast<volatile unsigned*>(a.counter) + 1u;
   const size_t slot_off = (seq & 1u) ? a.slot_elems : 0;
   const bool ok = tp_rendezvous(a, seq, &s_ok, blockIdx.x);
@@ -49,6 +54,8 @@ __global__ void __launch_bounds__(TP_THREADS) tp_allreduce_kernel(const TpArgs a
 
 __global__ void __launch_bounds__(TP_THREADS) tp_allgather_kernel(const TpArgs a) {
   __shared__ int s_ok;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const unsigned seq = *reinterpret_cast<volatile unsigned*>(a.counter) + 1u;
   const size_t slot_off = (seq & 1u) ? a.slot_elems : 0;
   const bool ok = tp_rendezvous(a, seq, &s_ok, blockIdx.x);
@@ -75,6 +82,8 @@ __global__ void __launch_bounds__(TP_THREADS) tp_allgather_kernel(const TpArgs a
 // Copies a result that was computed elsewhere into the slot of the upcoming call.
 __global__ void __launch_bounds__(256) tp_stage_kernel(const float* __restrict__ src, float* __restrict__ slots,
                                                         size_t slot_elems, const unsigned* counter, int64_t count) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const unsigned seq = *reinterpret_cast<const volatile unsigned*>(counter) + 1u;
   float* dst = slots + ((seq & 1u) ? slot_elems : 0);
   const int64_t nvec = count >> 2;
@@ -85,6 +94,22 @@ __global__ void __launch_bounds__(256) tp_stage_kernel(const float* __restrict__
 }
 
 }  // namespace turq
+
+namespace {
+template <class... Params, class... Args>
+cudaError_t tp_launch_pdl(void (*kernel)(Params...), unsigned grid, unsigned block, cudaStream_t s, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+}  // namespace
 
 struct turq_tp {
   turq_ctx* ctx = nullptr;
@@ -157,9 +182,8 @@ int32_t launch_reduce(turq_tp* tp, int64_t count, int64_t n, const float* bias, 
   a.out = out;
   // the same grid on every rank (CTA b pairs with CTA b of the peers): it depends on count only
   const int grid = grid_for((count + 3) / 4, turq::TP_MAX_BLOCKS);
-  turq::tp_allreduce_kernel<<<grid, turq::TP_THREADS, 0, s>>>(a);
+  cudaError_t e = tp_launch_pdl(turq::tp_allreduce_kernel, (unsigned)grid, (unsigned)turq::TP_THREADS, s, a);
   tp->ctx->launches++;
-  cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return tp_cuda_fail(tp, e, "all-reduce launch");
   return TURQ_OK;
 }
@@ -363,9 +387,8 @@ int32_t turq_tp_allgather(turq_tp* tp, const float* dev_in, int64_t m, const int
   a.out = dev_out;
   // the same grid on every rank: it depends on (world, m) only
   const int grid = grid_for((int64_t)tp->world * m * turq::TP_THREADS, turq::TP_MAX_BLOCKS);
-  turq::tp_allgather_kernel<<<grid, turq::TP_THREADS, 0, s>>>(a);
+  e = tp_launch_pdl(turq::tp_allgather_kernel, (unsigned)grid, (unsigned)turq::TP_THREADS, s, a);
   tp->ctx->launches++;
-  e = cudaGetLastError();
   if (e != cudaSuccess) return tp_cuda_fail(tp, e, "all-gather launch");
   return TURQ_OK;
 }
@@ -447,9 +470,8 @@ int32_t turq_qmatmul_gather(turq_tp* tp, const turq_qtensor* qt, const void* dev
   a.n_total = a.col0[tp->world];
   a.out = dev_out;
   const int grid = grid_for((int64_t)tp->world * m * turq::TP_THREADS, turq::TP_MAX_BLOCKS);
-  turq::tp_allgather_kernel<<<grid, turq::TP_THREADS, 0, s>>>(a);
+  cudaError_t e = tp_launch_pdl(turq::tp_allgather_kernel, (unsigned)grid, (unsigned)turq::TP_THREADS, s, a);
   ctx->launches++;
-  cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return tp_cuda_fail(tp, e, "gather launch");
   return TURQ_OK;
 }
