@@ -284,6 +284,35 @@ class Stack:
         return run
 
 
+def _make_host_pass(self, x, y, mode, multi=True, bound=True):
+    """The pass on page-locked host buffers. bound: every group of linears sharing x is a
+    tur_b200.HostCall created once (device aliases resolved, launches recorded), as a decoder
+    that reuses its activation buffers token after token would hold them; a step then runs them
+    in order. Otherwise (or for more than 64 rows / other schemes) per-call host entries."""
+    from tur_b200 import HostCall, Mode
+    if not bound or mode != Mode.INT8_ACT or next(iter(x.values())).shape[0] > 64:
+        return self.make_pass(x, y, mode, multi=multi)
+    calls = []
+    for layer in self.layers:
+        by_name = {w.name: (w, mm) for w, mm in layer}
+        for grp in GROUPS:
+            members = [by_name[n] for n in grp if n in by_name]
+            groups = [members] if (len(members) > 1 and multi) else [[mem] for mem in members]
+            for g in groups:
+                calls.append(HostCall([mm for _, mm in g], x[g[0][0].source], [y[w.name] for w, _ in g]))
+    if self.head:
+        calls.append(HostCall([self.head[1]], x["hidden"], [y[self.head[0].name]]))
+    self._bound_calls = calls
+
+    def run():
+        for c in calls:
+            c.run()
+    return run
+
+
+Stack.make_host_pass = _make_host_pass
+
+
 def graph_of(fn, dev, ctx, warm=3):
     """Warm-up runs (they also size the context's scratch), then the pass captured as one CUDA
     graph. Returns (graph, launches per pass)."""
@@ -409,7 +438,7 @@ def run_gpu(args):
     e2e_steps = max(1, min(args.steps, args.e2e_steps))
     if not args.no_e2e:
         x_host, y_host = stack.buffers(m, host=True)
-        one_pass_host = stack.make_pass(x_host, y_host, mode, multi=not args.no_multi)
+        one_pass_host = stack.make_host_pass(x_host, y_host, mode, multi=not args.no_multi, bound=not args.no_bound)
         for _ in range(3):
             one_pass_host()
         barrier()
@@ -516,9 +545,11 @@ def run_gpu(args):
         "e2e": None if e2e_ms is None else {
             "value": total_bytes * e2e_steps / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "steps": e2e_steps,
             "ms_per_step": e2e_ms / e2e_steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-            "api": "turq_qmatmul_multi_host / turq_qmatmul_host per group of linears sharing x: page-locked host x in, "
-                   "page-locked host y out, one synchronize per call; the activation rows cross the bus once per "
-                   "call (read in place by the quantization launch), every output once (written in place by the GEMV)"},
+            "api": ("turq_host_call_run (calls bound once to their page-locked buffers)" if not args.no_bound and mode == Mode.INT8_ACT and m <= 64
+                    else "turq_qmatmul_multi_host / turq_qmatmul_host") +
+                   " per group of linears sharing x: page-locked host x in, page-locked host y out, one synchronize per "
+                   "call; the activation rows cross the bus once per call (read in place by the quantization launch), "
+                   "every output once (written in place by the GEMV)"},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": sampler.summary(),
         "roofline": roofline,
@@ -854,6 +885,7 @@ def main():
     ap.add_argument("--tp", action="store_true", help="tensor-parallel over all ranks (the sharded cfg5 workload)")
     ap.add_argument("--tp-fuse-limit", type=int, default=None, help="tensor-parallel arm: largest result (bytes) exchanged inside the matmul kernel")
     ap.add_argument("--no-multi", action="store_true", help="one launch per weight (no q|k, gate|up multi-weight launches)")
+    ap.add_argument("--no-bound", action="store_true", help="e2e arm: per-call host entries instead of bound host calls")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of the timed pass's outputs")
     ap.add_argument("--no-extras", action="store_true", help="skip the sweep / prefill / other-config objects of the default run")
     ap.add_argument("--nccl", action="store_true", help="tensor-parallel arm: NCCL collectives and eager launches instead of the "

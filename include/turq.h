@@ -183,6 +183,20 @@ int32_t turq_qmatmul_multi_host(turq_ctx* ctx, int32_t count, const turq_qtensor
                                 const float* host_x, int64_t m, float* const* host_ys, int32_t mode,
                                 const float* const* host_biases);
 
+/* A host-buffer call bound to its buffers, for a decoder that calls the same linears with the
+ * same page-locked x / y buffers token after token (it rewrites x in place between runs):
+ * create resolves the buffers' device aliases, allocates the call's own activation scratch and
+ * records its launches once; run is then one graph launch and one synchronize, with the results
+ * of turq_qmatmul_multi_host(..., TURQ_MODE_INT8_ACT, no biases). 1 <= m <= 64. The buffers
+ * and the weights must stay alive until destroy; runs of calls of one context are serialised by
+ * the caller (they share the context's stream and hand-over workspace). Fails with
+ * TURQ_E_INVALID_ARG when a buffer is not page-locked: use turq_qmatmul_multi_host then. */
+typedef struct turq_host_call turq_host_call;
+int32_t turq_host_call_create(turq_ctx* ctx, int32_t count, const turq_qtensor* const* qts, const float* host_x,
+                              int64_t m, float* const* host_ys, turq_host_call** out);
+int32_t turq_host_call_run(turq_host_call* call);
+int32_t turq_host_call_destroy(turq_host_call* call);
+
 /* Integer-scheme QMatMul for hosts that must not allocate device memory during a call
  * (a process whose memory pool already owns the GPU, a plugin inside a foreign runtime).
  * No counterpart in the reference. Same arguments and results as turq_qmatmul with

@@ -573,3 +573,31 @@ def test_tensor_core_multi_call_converts_x_once_and_matches_separate_calls(tq):
     for g, s_, w, (t, n) in zip(got, sep, ws, shapes):
         assert torch.equal(g, s_)
     assert oracle.rel_fro(got[2].cpu().numpy(), oracle.matmul_f64(oracle.Q6_K, ws[2], 256, k, x.cpu().numpy())) < TOL
+
+
+@pytest.mark.parametrize("dt", TYPES, ids=ids)
+def test_bound_host_call_reruns_on_rewritten_buffers(tq, dt):
+    """turq_host_call_*: a decoder binds q|k|v (or one linear) to its page-locked buffers once and
+    reruns the call after rewriting x in place; every run gives the bits of the device call."""
+    k, shapes = 1024, [272, 64, 1000]
+    rng = np.random.default_rng(SEED + 909)
+    ws = [make_weight(dt, n, k, SEED + 900 + n) for n in shapes]
+    mms = [tq.QMatMul.from_arc(tq.QTensor.new(w, tq.GgmlDType(dt), (n, k))) for w, n in zip(ws, shapes)]
+    for m in (1, 5, 16):
+        x = torch.empty((m, k), dtype=torch.float32).pin_memory()
+        call = tq.HostCall(mms, x)
+        single = tq.HostCall(mms[2:], x)
+        for step in range(3):
+            x.copy_(torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)))     # the next token's activations
+            outs = call.run()
+            want = tq.QMatMul.forward_multi(mms, x.cuda(), mode=tq.Mode.INT8_ACT)
+            for o, w_ in zip(outs, want):
+                assert torch.equal(o, w_.cpu())
+            assert torch.equal(single.run()[0], want[2].cpu())
+        assert oracle.rel_fro(outs[0].numpy(), oracle.qmatmul(dt, ws[0], shapes[0], k, x.numpy())) < 1e-5
+        call.close()
+        single.close()
+    with pytest.raises(tq.TurqError) as e:
+        tq.HostCall(mms, torch.zeros((2, k)))                  # pageable memory: not bindable
+    assert e.value.status == 1
+    tq.context().poll_status()

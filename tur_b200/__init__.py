@@ -2,5 +2,5 @@
 
 `tur_b200.quantized` mirrors the candle names tur uses on this path (GgmlDType, QTensor,
 QMatMul) and `tur_b200.linear` mirrors tur's own LinearX (src/models/layers/linear.rs)."""
-from .quantized import GgmlDType, QMatMul, QTensor, TurqError, Mode, context, new_context, topk  # noqa: F401
+from .quantized import GgmlDType, QMatMul, QTensor, TurqError, Mode, context, new_context, topk, HostCall  # noqa: F401
 from .linear import LinearX, linear  # noqa: F401

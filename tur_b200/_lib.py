@@ -44,6 +44,9 @@ SIGNATURES = {
     "turq_qmatmul_multi": (c_i32, [c_vp, c_i32, c_vp, c_vp, c_i32, c_i64, c_vp, c_i32, c_vp, c_vp]),
     "turq_qmatmul_host": (c_i32, [c_vp, c_vp, c_vp, c_i64, c_vp, c_i32, c_vp]),
     "turq_qmatmul_multi_host": (c_i32, [c_vp, c_i32, c_vp, c_vp, c_i64, c_vp, c_i32, c_vp]),
+    "turq_host_call_create": (c_i32, [c_vp, c_i32, c_vp, c_vp, c_i64, c_vp, PP]),
+    "turq_host_call_run": (c_i32, [c_vp]),
+    "turq_host_call_destroy": (c_i32, [c_vp]),
     "turq_qmatmul_static": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i64, c_vp, c_vp, c_vp]),
     "turq_qmatmul_swiglu": (c_i32, [c_vp, c_vp, c_vp, c_vp, c_i32, c_i64, c_vp, c_i32, c_vp]),
     "turq_rmsnorm_qmatmul_multi": (c_i32, [c_vp, c_i32, c_vp, c_vp, c_i32, c_i64, c_vp, ctypes.c_float, c_vp, c_vp, c_i32, c_vp, c_vp]),

@@ -471,7 +471,8 @@ int32_t turq_qmatmul(turq_ctx* ctx, const turq_qtensor* qt, const void* dev_x, i
 
 static int32_t qmatmul_multi_impl(turq_ctx* ctx, int32_t count, const turq_qtensor* const* qts, const void* dev_x,
                                   int32_t x_dtype, int64_t m, float* const* dev_ys, int32_t mode,
-                                  const float* const* dev_biases, void* stream, bool x_remote) {
+                                  const float* const* dev_biases, void* stream, bool x_remote,
+                                  uint8_t* own_scratch = nullptr /* planes buffer of a bound call instead of the context's */) {
   if (!ctx || !qts || !dev_x || !dev_ys) return fail(ctx, TURQ_E_INVALID_ARG, "null argument");
   if (count < 1 || count > 4) return fail(ctx, TURQ_E_INVALID_ARG, "count %d outside 1..4", count);
   for (int i = 0; i < count; i++) {
@@ -527,13 +528,15 @@ static int32_t qmatmul_multi_impl(turq_ctx* ctx, int32_t count, const turq_qtens
   const int64_t k = qts[0]->n_cols;
   const int fmt = qts[0]->dtype == TURQ_Q8_0 ? TQ_Q8_0 : TQ_Q8_K;
   turq::ActPackPlan plan = turq::plan_act_pack(fmt, m, k);
-  int32_t st = ensure(ctx, &ctx->scratch, &ctx->scratch_bytes, plan.total);
-  if (st != TURQ_OK) return st;
+  if (!own_scratch) {
+    int32_t st = ensure(ctx, &ctx->scratch, &ctx->scratch_bytes, plan.total);
+    if (st != TURQ_OK) return st;
+  }
   turq::GemvPart parts[4];
   for (int i = 0; i < count; i++)
     parts[i] = turq::GemvPart{qts[i]->tiles, qts[i]->n_rows, dev_ys[i], dev_biases ? dev_biases[i] : nullptr, qts[i]->dtype, nullptr};
   int launches = 0;
-  cudaError_t e = turq::launch_gemv_int8_multi(qts[0]->dtype, parts, count, k, dev_x, x_dtype, ctx->scratch, m, ctx->gemv_ws,
+  cudaError_t e = turq::launch_gemv_int8_multi(qts[0]->dtype, parts, count, k, dev_x, x_dtype, own_scratch ? own_scratch : ctx->scratch, m, ctx->gemv_ws,
                                                ctx->dev_status, ctx->sm_count, static_cast<cudaStream_t>(stream), &launches,
                                                x_remote);
   ctx->launches += launches;
@@ -626,6 +629,81 @@ int32_t turq_qmatmul_multi_host(turq_ctx* ctx, int32_t count, const turq_qtensor
   for (int i = 0; i < count; i++)
     TQ_CUDA(ctx, cudaMemcpyAsync(host_ys[i], dys[i], (size_t)m * qts[i]->n_rows * 4, cudaMemcpyDeviceToHost, s));
   return turq_ctx_poll_status(ctx, s);
+}
+
+int32_t turq_host_call_create(turq_ctx* ctx, int32_t count, const turq_qtensor* const* qts, const float* host_x, int64_t m,
+                              float* const* host_ys, turq_host_call** out) {
+  if (!ctx || !qts || !host_x || !host_ys || !out) return fail(ctx, TURQ_E_INVALID_ARG, "null argument");
+  *out = nullptr;
+  if (count < 1 || count > 4) return fail(ctx, TURQ_E_INVALID_ARG, "count %d outside 1..4", count);
+  if (m <= 0 || m > 64) return fail(ctx, TURQ_E_LIMIT, "a bound host call takes 1..64 rows (decode batches); use turq_qmatmul_multi_host beyond");
+  bool k_quant = false, q8_0 = false;
+  for (int i = 0; i < count; i++) {
+    if (!qts[i] || !host_ys[i]) return fail(ctx, TURQ_E_INVALID_ARG, "null argument");
+    if (qts[i]->n_cols != qts[0]->n_cols || qts[i]->device != ctx->device)
+      return fail(ctx, TURQ_E_SHAPE, "weights of one call must share the in-feature count and live on the context's device");
+    (qts[i]->dtype == TURQ_Q8_0 ? q8_0 : k_quant) = true;
+  }
+  if (k_quant && q8_0) return fail(ctx, TURQ_E_DTYPE, "Q8_0 and K-quant weights do not share an activation format");
+  TQ_CUDA(ctx, cudaSetDevice(ctx->device));
+  turq_host_call* hc = new (std::nothrow) turq_host_call();
+  if (!hc) return fail(ctx, TURQ_E_INVALID_ARG, "out of host memory");
+  hc->ctx = ctx;
+  void* mx = mapped_alias(host_x);
+  float* mys[4] = {nullptr, nullptr, nullptr, nullptr};
+  bool ok = mx != nullptr && (uintptr_t)mx % 16 == 0;
+  for (int i = 0; ok && i < count; i++) {
+    mys[i] = static_cast<float*>(mapped_alias(host_ys[i]));
+    ok = mys[i] != nullptr;
+  }
+  if (!ok) {
+    delete hc;
+    return fail(ctx, TURQ_E_INVALID_ARG, "a bound host call needs page-locked x (16-byte aligned) and y buffers (cudaHostAlloc / cudaHostRegister)");
+  }
+  const int64_t k = qts[0]->n_cols;
+  const int fmt = q8_0 ? TQ_Q8_0 : TQ_Q8_K;
+  cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&hc->scratch), turq::plan_act_pack(fmt, m, k).total);
+  if (e != cudaSuccess) {
+    delete hc;
+    return cuda_fail(ctx, e, "cudaMalloc(bound call planes)");
+  }
+  // The launches of the call, recorded once: afterwards a run is one graph launch and one synchronize.
+  cudaStream_t s = ctx->own_stream;
+  cudaGraph_t graph = nullptr;
+  e = cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal);
+  int32_t st = TURQ_OK;
+  if (e == cudaSuccess) {
+    st = qmatmul_multi_impl(ctx, count, qts, mx, TURQ_F32, m, mys, TURQ_MODE_INT8_ACT, nullptr, s, true, hc->scratch);
+    e = cudaStreamEndCapture(s, &graph);
+  }
+  if (e == cudaSuccess && st == TURQ_OK) e = cudaGraphInstantiate(&hc->exec, graph, 0);
+  if (graph) cudaGraphDestroy(graph);
+  if (e != cudaSuccess || st != TURQ_OK) {
+    cudaGetLastError();
+    turq_host_call_destroy(hc);
+    return st != TURQ_OK ? st : cuda_fail(ctx, e, "recording the bound call");
+  }
+  *out = hc;
+  return TURQ_OK;
+}
+
+int32_t turq_host_call_run(turq_host_call* hc) {
+  if (!hc || !hc->ctx || !hc->exec) return TURQ_E_INVALID_ARG;
+  turq_ctx* ctx = hc->ctx;
+  TQ_CUDA(ctx, cudaGraphLaunch(hc->exec, ctx->own_stream));
+  return turq_ctx_poll_status(ctx, ctx->own_stream);
+}
+
+int32_t turq_host_call_destroy(turq_host_call* hc) {
+  if (!hc) return TURQ_E_INVALID_ARG;
+  if (hc->ctx) {
+    cudaSetDevice(hc->ctx->device);
+    cudaStreamSynchronize(hc->ctx->own_stream);
+  }
+  if (hc->exec) cudaGraphExecDestroy(hc->exec);
+  if (hc->scratch) cudaFree(hc->scratch);
+  delete hc;
+  return TURQ_OK;
 }
 
 int32_t turq_qmatmul_host(turq_ctx* ctx, const turq_qtensor* qt, const float* host_x, int64_t m, float* host_y,

@@ -33,3 +33,11 @@ struct turq_qtensor {
   size_t tile_bytes = 0;
 };
 
+// A host-buffer matmul call with everything resolved up front (turq_host_call_*): the device
+// aliases of the caller's page-locked buffers, a planes buffer of its own, and the launches
+// recorded as an executable graph.
+struct turq_host_call {
+  turq_ctx* ctx = nullptr;
+  uint8_t* scratch = nullptr;
+  cudaGraphExec_t exec = nullptr;
+};

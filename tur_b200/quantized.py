@@ -420,6 +420,48 @@ class QMatMul:
         return vals, ids
 
 
+class HostCall:
+    """Linears bound to their page-locked host buffers (include/turq.h, turq_host_call_*): the
+    caller rewrites `x` in place and calls `run()` token after token; results appear in `outs`.
+    One graph launch and one synchronize per run. Integer scheme, 1..64 rows, no bias."""
+
+    def __init__(self, mms: Sequence["QMatMul"], x: torch.Tensor, outs: Optional[Sequence[torch.Tensor]] = None):
+        lib = _lib.load()
+        self._ctx = mms[0].qtensor._ctx
+        k = mms[0].qtensor.shape()[1]
+        if x.is_cuda or x.dtype != torch.float32 or not x.is_contiguous() or x.dim() != 2 or x.shape[1] != k or not x.is_pinned():
+            raise TurqError(1, "a bound host call needs a page-locked, contiguous f32 host matrix [m, in-features]")
+        m = x.shape[0]
+        if outs is None:
+            outs = [torch.empty((m, mm.qtensor.shape()[0]), dtype=torch.float32).pin_memory() for mm in mms]
+        for o, mm in zip(outs, mms):
+            if o.is_cuda or o.dtype != torch.float32 or not o.is_contiguous() or o.numel() != m * mm.qtensor.shape()[0] or not o.is_pinned():
+                raise TurqError(1, "outs must be page-locked, contiguous f32 host tensors of m x n elements")
+        self.x, self.outs, self._mms = x, list(outs), list(mms)    # keep buffers and weights alive
+        n = len(mms)
+        arr = ctypes.c_void_p * n
+        h = ctypes.c_void_p()
+        self._ctx.check(lib.turq_host_call_create(self._ctx.handle, n, arr(*[mm.qtensor._h for mm in mms]), x.data_ptr(), m,
+                                                  arr(*[o.data_ptr() for o in self.outs]), ctypes.byref(h)))
+        self._h = h
+        self._run = lib.turq_host_call_run
+
+    def run(self) -> list[torch.Tensor]:
+        st = self._run(self._h)
+        if st != 0:
+            self._ctx.check(st)
+        return self.outs
+
+    __call__ = run
+
+    def close(self) -> None:
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            _lib.load().turq_host_call_destroy(h)
+
+    __del__ = close
+
+
 def topk(vals: torch.Tensor, k: int, ids: Optional[torch.Tensor] = None, id_offset: int = 0) -> tuple[torch.Tensor, torch.Tensor]:
     """k largest per row of vals [m, n] (f32, CUDA) with their ids (positions + id_offset, or the
     given int32 ids [m, n]): best first, ties to the lower id."""
