@@ -12,6 +12,11 @@
 //   LinearX::Quantized { qmatmul, bias } / linear()          turq::LinearX
 //     (src/models/layers/linear.rs:9-32, 50-70)
 //
+//   Qwen3MLP::forward (src/models/qwen3.rs:160-166)          turq::swiglu
+//   ln -> projections (src/models/qwen3.rs:633-638)          turq::rmsnorm_forward_multi
+//   lm_head -> LogitsProcessor::sample                       turq::QMatMul::lm_head_topk
+//     (src/backend/engine.rs:528-529, 810-824)
+//
 // Header-only; link with libturq.so. Device pointers are the caller's (any allocator).
 #pragma once
 #include <cstdint>
@@ -55,6 +60,10 @@ class Context {
   }
   // Synchronizes `stream` and throws if a kernel gave up a bounded device-side wait.
   void poll_status(void* stream = nullptr) const { check(turq_ctx_poll_status(h_, stream)); }
+  // Sizes the scratch for the largest call so that no later call allocates.
+  void reserve(int64_t max_m, int64_t max_k, int64_t max_n) const { check(turq_ctx_reserve(h_, max_m, max_k, max_n)); }
+  // Pins what Mode::Auto means to one scheme for every row count (batch-independent results).
+  void set_auto_policy(int32_t mode) const { check(turq_ctx_set_auto_policy(h_, mode)); }
 
  private:
   turq_ctx* h_ = nullptr;
@@ -133,12 +142,49 @@ class QMatMul {
     c->check(turq_qmatmul_host(c->handle(), w_->handle(), x, m, y.data(), static_cast<int32_t>(mode), bias));
     return y;
   }
+  // Several linears that read the same x (attn_q|k|v, ffn_gate|up) in one call; ys[i] is [m, rows of mms[i]].
+  static void forward_multi(const std::vector<const QMatMul*>& mms, const void* dev_x, GgmlDType x_dtype, int64_t m,
+                            const std::vector<float*>& dev_ys, Mode mode = Mode::Auto, void* stream = nullptr) {
+    if (mms.empty() || mms.size() != dev_ys.size()) throw Error(TURQ_E_INVALID_ARG, "forward_multi: weights and outputs must pair up");
+    std::vector<const turq_qtensor*> qts;
+    for (const QMatMul* mm : mms) qts.push_back(mm->w_->handle());
+    const auto& c = mms[0]->w_->context();
+    c->check(turq_qmatmul_multi(c->handle(), static_cast<int32_t>(qts.size()), qts.data(), dev_x, static_cast<int32_t>(x_dtype), m,
+                                dev_ys.data(), static_cast<int32_t>(mode), nullptr, stream));
+  }
+  // The k best (logit, token id) pairs per row of x . W^T, best first, ties to the lower id.
+  void lm_head_topk(const void* dev_x, GgmlDType x_dtype, int64_t m, int32_t k, float* dev_vals, int32_t* dev_ids,
+                    int32_t id_offset = 0, float* dev_logits = nullptr, Mode mode = Mode::Auto, void* stream = nullptr) const {
+    const auto& c = w_->context();
+    c->check(turq_lm_head_topk(c->handle(), w_->handle(), dev_x, static_cast<int32_t>(x_dtype), m, k, id_offset, dev_vals, dev_ids,
+                               dev_logits, static_cast<int32_t>(mode), stream));
+  }
   const std::shared_ptr<QTensor>& weight() const { return w_; }
 
  private:
   explicit QMatMul(std::shared_ptr<QTensor> w) : w_(std::move(w)) {}
   std::shared_ptr<QTensor> w_;
 };
+
+// silu(x . Wg^T) * (x . Wu^T): one launch in the integer scheme.
+inline void swiglu(const QMatMul& gate, const QMatMul& up, const void* dev_x, GgmlDType x_dtype, int64_t m, float* dev_out,
+                   Mode mode = Mode::Auto, void* stream = nullptr) {
+  const auto& c = gate.weight()->context();
+  c->check(turq_qmatmul_swiglu(c->handle(), gate.weight()->handle(), up.weight()->handle(), dev_x, static_cast<int32_t>(x_dtype), m,
+                               dev_out, static_cast<int32_t>(mode), stream));
+}
+
+// y_i = rmsnorm(x; weight, eps) . W_i^T; dev_h_out (nullable) receives the normalised rows.
+inline void rmsnorm_forward_multi(const std::vector<const QMatMul*>& mms, const void* dev_x, GgmlDType x_dtype, int64_t m,
+                                  const float* dev_norm_weight, float eps, float* dev_h_out, const std::vector<float*>& dev_ys,
+                                  Mode mode = Mode::Auto, void* stream = nullptr) {
+  if (mms.empty() || mms.size() != dev_ys.size()) throw Error(TURQ_E_INVALID_ARG, "rmsnorm_forward_multi: weights and outputs must pair up");
+  std::vector<const turq_qtensor*> qts;
+  for (const QMatMul* mm : mms) qts.push_back(mm->weight()->handle());
+  const auto& c = mms[0]->weight()->context();
+  c->check(turq_rmsnorm_qmatmul_multi(c->handle(), static_cast<int32_t>(qts.size()), qts.data(), dev_x, static_cast<int32_t>(x_dtype), m,
+                                      dev_norm_weight, eps, dev_h_out, dev_ys.data(), static_cast<int32_t>(mode), nullptr, stream));
+}
 
 // The `Quantized` arm of tur's LinearX: QMatMul plus an optional f32 bias in device memory
 // (the add is fused into the matmul epilogue).

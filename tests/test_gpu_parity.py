@@ -601,3 +601,41 @@ def test_bound_host_call_reruns_on_rewritten_buffers(tq, dt):
         tq.HostCall(mms, torch.zeros((2, k)))                  # pageable memory: not bindable
     assert e.value.status == 1
     tq.context().poll_status()
+
+
+def test_contexts_are_reentrant_across_threads_and_streams(tq):
+    """tur runs one worker thread per model (src/server/worker.rs:63-72). Calls through different
+    contexts - each with its own scratch and hand-over workspace - may run concurrently from
+    different threads on different streams and must not disturb each other."""
+    import threading
+    n, k = 9600, 1024                                  # 600 row-tiles: split with hand-over between CTAs
+    ws = {dt: make_weight(dt, n, k, SEED + 1200 + dt) for dt in (oracle.Q4_K, oracle.Q6_K)}
+    xs = {m: torch.from_numpy(np.random.default_rng(SEED + m).standard_normal((m, k)).astype(np.float32)).cuda() for m in (1, 5, 12)}
+    ref_mm = {dt: tq.QMatMul.from_arc(tq.QTensor.new(w, tq.GgmlDType(dt), (n, k))) for dt, w in ws.items()}
+    want = {(dt, m): ref_mm[dt].forward(x, mode=tq.Mode.INT8_ACT).clone() for dt in ws for m, x in xs.items()}
+    torch.cuda.synchronize()
+    errors = []
+
+    def worker(dt):
+        try:
+            ctx = tq.new_context()
+            mm = tq.QMatMul.from_arc(tq.QTensor.new(ws[dt], tq.GgmlDType(dt), (n, k), ctx=ctx))
+            stream = torch.cuda.Stream()
+            with torch.cuda.stream(stream):
+                for it in range(30):
+                    for m, x in xs.items():
+                        y = mm.forward(x, mode=tq.Mode.INT8_ACT)
+                        if it % 10 == 9:
+                            stream.synchronize()
+                            if not torch.equal(y, want[(dt, m)]):
+                                errors.append((dt, m, it))
+                ctx.poll_status()
+        except Exception as e:  # reported to the main thread
+            errors.append(repr(e))
+
+    threads = [threading.Thread(target=worker, args=(dt,)) for dt in ws for _ in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
