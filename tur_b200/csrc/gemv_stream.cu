@@ -202,7 +202,7 @@ constexpr int ACT_STAGED = 2;  // bulk-copied from global scratch into shared me
 // mixes store them); parts flagged in part_alt hold DT2 tiles. Both types have one tile per
 // 256 elements, so the walk over tiles is the same; ring slots are sized for the larger tile.
 template <int DT, int MG, int ACT, int DT2 = DT>
-__global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(const __grid_constant__ StreamArgs a) {
+__global__ void __launch_bounds__(THREADS, 2) gemv_stream_kernel(const __grid_constant__ StreamArgs a) {
   constexpr bool MIXED = DT2 != DT;
   constexpr int TB = TileGeom<DT>::BYTES;
   constexpr int TB2 = TileGeom<DT2>::BYTES;
@@ -448,10 +448,24 @@ __global__ void __launch_bounds__(THREADS, MG == 1 ? 3 : 2) gemv_stream_kernel(c
           while (part + 1 < a.nparts && w.rt >= a.rt_begin[part + 1]) part++;
           alt = a.part_alt[part] != 0;
         }
-        if (MIXED && alt) {
-          tile_mma<DT2, MG>(tile, lane, act, a.k, kt, a.rows, left, acc);
-        } else {
-          tile_mma<DT, MG>(tile, lane, act, a.k, kt, a.rows, left, acc);
+        // one activation row: the single-row tile function (same bits, about half the instructions)
+        bool done_row1 = false;
+        if constexpr (MG == 1 && DT != TQ_Q8_0 && DT2 != TQ_Q8_0) {
+          if (a.rows == 1) {
+            if (MIXED && alt) {
+              tile_mma_row1<DT2>(tile, lane, act, a.k, kt, acc);
+            } else {
+              tile_mma_row1<DT>(tile, lane, act, a.k, kt, acc);
+            }
+            done_row1 = true;
+          }
+        }
+        if (!done_row1) {
+          if (MIXED && alt) {
+            tile_mma<DT2, MG>(tile, lane, act, a.k, kt, a.rows, left, acc);
+          } else {
+            tile_mma<DT, MG>(tile, lane, act, a.k, kt, a.rows, left, acc);
+          }
         }
       }
       __syncwarp();

@@ -230,4 +230,132 @@ __device__ __forceinline__ void tile_mma(const uint8_t* __restrict__ t, int lane
   }
 }
 
+// The same tile against ONE activation row (decode, M = 1), K-quant types. With a single row the
+// 8-wide activation operand of the MMA would carry seven rows of zeros and every lane would
+// still apply the sub-block scales to all four of its C elements. Here the eight B columns carry
+// the eight 32-element sub-blocks instead (16-element ones for Q6_K, in two accumulator sets):
+// the MMA of sub-block s gets the activation bytes in column s only, so after the tile's MMAs
+// C[row][j] is the integer dot of `row` with sub-block j. A lane then scales just its own two
+// (four) sub-blocks, the four lanes of a row add their integers with two shuffles, and the
+// float step is the one of the general function - same integers, same float operations, so
+// the result has the bits of tile_mma<DT, 1> with rows = 1. Each lane loads one 8-byte (two
+// 4-byte) activation fragment per tile instead of eight (sixteen).
+template <int DT>
+__device__ __forceinline__ void tile_mma_row1(const uint8_t* __restrict__ t, int lane, const ActPack& act, int k, int kt,
+                                              float (&acc)[1][4]) {
+  static_assert(DT == TQ_Q4_K || DT == TQ_Q5_K || DT == TQ_Q6_K, "single-row variant exists for the K-quants");
+  const int g = lane >> 2, c = lane & 3;
+  const float dx0 = act.dsc[kt];
+  if constexpr (DT == TQ_Q4_K || DT == TQ_Q5_K) {
+    constexpr int QS = DT == TQ_Q4_K ? TQ_Q4K_QS : TQ_Q5K_QS;
+    constexpr int SH = DT == TQ_Q4_K ? 4 : 0;
+    const uint4 h0 = lds_v4(t + 16 * g), h1 = lds_v4(t + 16 * (g + 8));
+    const uint4 hh[2] = {h0, h1};
+    const uint4 bs0 = ld_v4(act.bs32 + kt * 8);
+    uint32_t scl[2], sch[2];
+    int aM[2];
+#pragma unroll
+    for (int hr = 0; hr < 2; hr++) {
+      const uint32_t s0 = hh[hr].y, s1 = hh[hr].z, s2 = hh[hr].w;
+      scl[hr] = s0 & 0x3F3F3F3Fu;
+      sch[hr] = (s2 & 0x0F0F0F0Fu) | ((s0 >> 2) & 0x30303030u);
+      const int mnl = (int)(s1 & 0x3F3F3F3Fu);
+      const int mnh = (int)(((s2 >> 4) & 0x0F0F0F0Fu) | ((s1 >> 2) & 0x30303030u));
+      aM[hr] = __dp2a_hi((int)bs0.w, mnh, __dp2a_lo((int)bs0.z, mnh, __dp2a_hi((int)bs0.y, mnl, __dp2a_lo((int)bs0.x, mnl, 0))));
+    }
+    // this lane's activation fragment: elements 8c .. 8c+7 of sub-block g
+    const uint2 frag = ld_v2(act.qs + kt * 256 + 32 * g + 8 * c);
+    int cc[4] = {0, 0, 0, 0};
+    uint4 qh = make_uint4(0, 0, 0, 0);
+    if constexpr (DT == TQ_Q5_K) qh = lds_v4(t + TQ_Q5K_QH + 16 * lane);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const uint4 q = lds_v4(t + QS + 512 * i + 16 * lane);
+      uint32_t alo[4] = {q.x & 0x0F0F0F0Fu, q.z & 0x0F0F0F0Fu, q.y & 0x0F0F0F0Fu, q.w & 0x0F0F0F0Fu};
+      uint32_t ahi[4] = {q.x & 0xF0F0F0F0u, q.z & 0xF0F0F0F0u, q.y & 0xF0F0F0F0u, q.w & 0xF0F0F0F0u};
+      if constexpr (DT == TQ_Q5_K) {
+        const uint32_t hw[4] = {qh.x, qh.z, qh.y, qh.w};
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          alo[e] |= ((hw[e] >> (2 * i)) << 4) & 0x10101010u;
+          ahi[e] = (ahi[e] >> 4) | (((hw[e] >> (2 * i + 1)) << 4) & 0x10101010u);
+        }
+      }
+      const bool lo_mine = g == 2 * i, hi_mine = g == 2 * i + 1;
+      mma_16832<true>(cc, alo, lo_mine ? frag.x : 0u, lo_mine ? frag.y : 0u);
+      mma_16832<true>(cc, ahi, hi_mine ? frag.x : 0u, hi_mine ? frag.y : 0u);
+    }
+    // cc[0] = (row g, sub-block 2c), cc[1] = (row g, 2c+1), cc[2] = (row g+8, 2c), cc[3] = (row g+8, 2c+1)
+    const int sh_even = 8 * ((2 * c) & 3), sh_odd = sh_even + 8;
+    int p[2];
+#pragma unroll
+    for (int hr = 0; hr < 2; hr++) {
+      const uint32_t sw = c < 2 ? scl[hr] : sch[hr];
+      const int s_even = (int)((sw >> sh_even) & 0xFFu), s_odd = (int)((sw >> sh_odd) & 0xFFu);
+      p[hr] = s_even * cc[2 * hr] + ((s_odd * cc[2 * hr + 1]) >> SH);
+      p[hr] += __shfl_xor_sync(0xFFFFFFFFu, p[hr], 1);
+      p[hr] += __shfl_xor_sync(0xFFFFFFFFu, p[hr], 2);
+    }
+    const float d[2] = {f16_bits_to_f32(h0.x), f16_bits_to_f32(h1.x)};
+    const float dmin[2] = {f16_bits_to_f32(h0.x >> 16), f16_bits_to_f32(h1.x >> 16)};
+    acc[0][0] += (dx0 * d[0]) * (float)p[0] - (dx0 * dmin[0]) * (float)aM[0];
+    acc[0][2] += (dx0 * d[1]) * (float)p[1] - (dx0 * dmin[1]) * (float)aM[1];
+  } else {  // Q6_K: 16 sub-blocks of 16 elements -> two accumulator sets of 8 columns
+    const uint4 s0v = lds_v4(t + 16 * g), s1v = lds_v4(t + 16 * (g + 8));
+    const uint32_t scw[2][4] = {{s0v.x, s0v.y, s0v.z, s0v.w}, {s1v.x, s1v.y, s1v.z, s1v.w}};
+    const int16_t* b0p = act.bs16 + kt * 16;
+    const uint4 p0 = ld_v4(b0p), p1 = ld_v4(b0p + 8);
+    const uint32_t bw0[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+    int off32[2];
+#pragma unroll
+    for (int hr = 0; hr < 2; hr++) {
+      int o0 = 0;
+#pragma unroll
+      for (int w = 0; w < 4; w++) o0 = __dp2a_hi((int)bw0[2 * w + 1], (int)scw[hr][w], __dp2a_lo((int)bw0[2 * w], (int)scw[hr][w], o0));
+      off32[hr] = -32 * o0;
+    }
+    // this lane's activation fragments: elements 4c .. 4c+3 of sub-blocks g and g + 8
+    const uint32_t fa = ld_u32(act.qs + kt * 256 + 16 * g + 4 * c);
+    const uint32_t fb = ld_u32(act.qs + kt * 256 + 16 * (g + 8) + 4 * c);
+    int ca[4] = {0, 0, 0, 0}, cb[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const uint4 ql = lds_v4(t + TQ_Q6K_QL + 512 * i + 16 * lane);
+      const uint4 qh = lds_v4(t + TQ_Q6K_QH + 512 * (i >> 1) + 16 * lane);
+      const uint32_t qh0 = (i & 1) ? qh.y : qh.x, qh1 = (i & 1) ? qh.w : qh.z;
+#pragma unroll
+      for (int jj = 0; jj < 4; jj++) {
+        const int j = 4 * i + jj;
+        const int tw = jj >> 1, nib = jj & 1;
+        const uint32_t w0 = tw ? ql.y : ql.x, w1 = tw ? ql.w : ql.z;
+        uint32_t a0 = (nib ? (w0 >> 4) : w0) & 0x0F0F0F0Fu, a1 = (nib ? (w1 >> 4) : w1) & 0x0F0F0F0Fu;
+        const int sh = 2 * jj;
+        a0 |= (sh <= 4 ? (qh0 << (4 - sh)) : (qh0 >> (sh - 4))) & 0x30303030u;
+        a1 |= (sh <= 4 ? (qh1 << (4 - sh)) : (qh1 >> (sh - 4))) & 0x30303030u;
+        if (j < 8) {
+          mma_16816_u8s8(ca, a0, a1, g == j ? fa : 0u);
+        } else {
+          mma_16816_u8s8(cb, a0, a1, g == j - 8 ? fb : 0u);
+        }
+      }
+    }
+    // ca: sub-blocks 2c, 2c+1 (rows g | g+8); cb: sub-blocks 8+2c, 9+2c
+    const int b_even = (2 * c) & 3, b_odd = b_even + 1;
+    int p[2];
+#pragma unroll
+    for (int hr = 0; hr < 2; hr++) {
+      const uint32_t wa = (c >> 1) ? scw[hr][1] : scw[hr][0];
+      const uint32_t wb = (c >> 1) ? scw[hr][3] : scw[hr][2];
+      p[hr] = sext_byte(wa, b_even) * ca[2 * hr] + sext_byte(wa, b_odd) * ca[2 * hr + 1] + sext_byte(wb, b_even) * cb[2 * hr] +
+              sext_byte(wb, b_odd) * cb[2 * hr + 1];
+      p[hr] += __shfl_xor_sync(0xFFFFFFFFu, p[hr], 1);
+      p[hr] += __shfl_xor_sync(0xFFFFFFFFu, p[hr], 2);
+      p[hr] += off32[hr];
+    }
+    const float d0 = f16_bits_to_f32(lds_u16(t + TQ_Q6K_D + 2 * g)), d1 = f16_bits_to_f32(lds_u16(t + TQ_Q6K_D + 2 * (g + 8)));
+    acc[0][0] += (dx0 * d0) * (float)p[0];
+    acc[0][2] += (dx0 * d1) * (float)p[1];
+  }
+}
+
 }  // namespace turq
