@@ -391,6 +391,42 @@ def test_joint_launch_with_row_tiles_cut_between_ctas(tq, second, m):
         assert oracle.rel_fro(y.cpu().numpy(), oracle.qmatmul(t, w, n, k, x)) < 1e-5
 
 
+@pytest.mark.parametrize("dt", [oracle.Q4_K, oracle.Q5_K, oracle.Q6_K], ids=["Q4_K", "Q5_K", "Q6_K"])
+@pytest.mark.parametrize("n,k", [(272, 2560), (5000, 4096), (1040, 12288)], ids=["partly_filled_stages", "cut_row_tiles", "staged_planes"])
+def test_single_row_tile_function_gives_the_bits_of_a_batch_row(tq, dt, n, k):
+    """One activation row takes a tile function of its own in the K-quant GEMV (sub-blocks in the
+    MMA's columns instead of activation rows). Its sums must be the general function's: row 0 of
+    a 2-, 5- and 11-row batch, through whole and cut row-tiles and both activation routes."""
+    w = make_weight(dt, n, k, SEED + 77 + n)
+    rng = np.random.default_rng(SEED + 78 + k)
+    x = rng.standard_normal((11, k)).astype(np.float32)
+    x[0, ::7] *= 40.0   # wide range inside the blocks of the row under test
+    xd = torch.from_numpy(x).cuda()
+    mm = tq.QMatMul.from_arc(tq.QTensor.new(w, tq.GgmlDType(dt), (n, k)))
+    y1 = mm.forward(xd[:1], mode=tq.Mode.INT8_ACT)
+    for rows in (2, 5, 11):
+        assert torch.equal(mm.forward(xd[:rows], mode=tq.Mode.INT8_ACT)[:1], y1)
+    assert oracle.rel_fro(y1.cpu().numpy(), oracle.qmatmul(dt, w, n, k, x[:1])) < 1e-5
+    tq.context().poll_status()
+
+
+def test_single_row_tile_function_in_a_mixed_type_launch(tq):
+    """attn_q|k|v of the K-quant mixes as one launch at one row (both single-row tile functions in
+    one kernel) against the same launch at three rows."""
+    k = 4096
+    shapes = [(oracle.Q4_K, 4096), (oracle.Q4_K, 1024), (oracle.Q6_K, 1024)]
+    ws = [make_weight(t, n, k, SEED + 1200 + i) for i, (t, n) in enumerate(shapes)]
+    mms = [tq.QMatMul.from_arc(tq.QTensor.new(w, tq.GgmlDType(t), (n, k))) for w, (t, n) in zip(ws, shapes)]
+    x = np.random.default_rng(SEED + 1210).standard_normal((3, k)).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    one = [y.clone() for y in tq.QMatMul.forward_multi(mms, xd[:1], mode=tq.Mode.INT8_ACT)]
+    three = tq.QMatMul.forward_multi(mms, xd, mode=tq.Mode.INT8_ACT)
+    for a, b, w, (t, n) in zip(one, three, ws, shapes):
+        assert torch.equal(a, b[:1])
+        assert oracle.rel_fro(a.cpu().numpy(), oracle.qmatmul(t, w, n, k, x[:1])) < 1e-5
+    tq.context().poll_status()
+
+
 def test_no_kernel_gave_up_a_wait(tq):
     tq.context().poll_status()
 
