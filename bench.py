@@ -209,13 +209,13 @@ GROUPS = [["attn_q", "attn_k", "attn_v"], ["attn_output"], ["ffn_gate", "ffn_up"
 class Stack:
     """The quantized linears of a workload resident on one GPU: every layer in buffers of its own,
     so a pass streams from HBM. gen = "oracle": seeded N(0, 0.02) weights through the CPU
-    quantizer (host copies kept for the parity check); "random": valid random blocks made on the
-    GPU (timing input for the secondary configurations)."""
+    quantizer (host copies kept for the parity check); "device": seeded N(0, 0.02) weights
+    quantized on the GPU by the library's weight quantizer (the secondary configurations)."""
 
     def __init__(self, wl, dev, gen="oracle", head=True, ctx=None):
         import torch
         from tur_b200 import GgmlDType, QMatMul, QTensor
-        from tur_b200.workloads import random_blocks
+        from tur_b200.workloads import quantized_blocks
         self.wl, self.dev, self.host_blocks = wl, dev, {}
         protos = []
         for i, w in enumerate(wl.per_layer):
@@ -224,7 +224,7 @@ class Stack:
                 self.host_blocks[w.name] = hb
                 protos.append((w, torch.from_numpy(hb).to(dev)))
             else:
-                protos.append((w, random_blocks(w.dtype, w.n, w.k, SEED + i, dev)))
+                protos.append((w, quantized_blocks(w.dtype, w.n, w.k, SEED + i, dev)))
         self.layers = [[(w, QMatMul.from_arc(QTensor.new(b, GgmlDType(w.dtype), (w.n, w.k), ctx=ctx))) for w, b in protos]
                        for _ in range(wl.layers)]
         self.head = None
@@ -234,7 +234,7 @@ class Stack:
                 self.host_blocks[wl.head.name] = hb
                 b = torch.from_numpy(hb).to(dev)
             else:
-                b = random_blocks(wl.head.dtype, wl.head.n, wl.head.k, SEED + 999, dev)
+                b = quantized_blocks(wl.head.dtype, wl.head.n, wl.head.k, SEED + 999, dev)
             self.head = (wl.head, QMatMul.from_arc(QTensor.new(b, GgmlDType(wl.head.dtype), (wl.head.n, wl.head.k), ctx=ctx)))
         del protos
         torch.cuda.synchronize()
@@ -612,12 +612,12 @@ def run_extras(stack, dev, ctx, peak, tpeak, local):
     torch.cuda.empty_cache()
     cfgs = []
     for name in ("cfg1", "cfg4-q5", "cfg4-q8"):
-        st = Stack(WORKLOADS[name], dev, gen="random", head=False)
+        st = Stack(WORKLOADS[name], dev, gen="device", head=False)
         x, y = st.buffers(1)
         g, launches = graph_of(st.make_pass(x, y, Mode.INT8_ACT), dev, ctx)
         t = time_replays(g, 10)
         gbs = st.pass_bytes() / (t * 1e-3) / 1e9
-        cfgs.append({"workload": workload_text(st.wl, 1, False), "weights": "valid random blocks generated on the GPU",
+        cfgs.append({"workload": workload_text(st.wl, 1, False), "weights": "seeded N(0, 0.02) quantized on the GPU (turq_quantize_weights)",
                      "ms_per_step": t, "weight_gbs": gbs, "frac_of_hbm_peak": gbs / peak, "launches": launches})
         del g, x, y, st
         torch.cuda.empty_cache()
@@ -635,13 +635,13 @@ class TPStack:
         import torch
         from tur_b200 import GgmlDType, QMatMul, QTensor
         from tur_b200.tensor_parallel import row_unit_for, shard_blocks, shard_of, split_units
-        from tur_b200.workloads import random_blocks
+        from tur_b200.workloads import quantized_blocks
         self.wl, self.dev, self.rank, self.world = wl, dev, rank, world
         self.n_layers = layers or wl.layers
 
         def make(w, seed):
             sh = shard_of(w, world, rank, row_unit_for(w, head_dim))
-            return sh, shard_blocks(random_blocks(w.dtype, w.n, w.k, seed, dev), w, sh).reshape(-1)
+            return sh, shard_blocks(quantized_blocks(w.dtype, w.n, w.k, seed, dev), w, sh).reshape(-1)
 
         protos = [(w,) + make(w, SEED + i) for i, w in enumerate(wl.per_layer)]
         self.layers = [[(w, sh, QMatMul.from_arc(QTensor.new(b, GgmlDType(w.dtype), sh.shape))) for w, sh, b in protos]
@@ -740,12 +740,12 @@ def tp_parity(stack, group, dev, ctx, m=4):
     import torch
     from tur_b200 import GgmlDType, Mode, QMatMul, QTensor
     from tur_b200.tensor_parallel import split_units
-    from tur_b200.workloads import random_blocks
+    from tur_b200.workloads import quantized_blocks
     out = {}
     for i, (w, sh, mm) in enumerate(stack.layers[0]):
         if w.name not in ("ffn_gate", "ffn_down"):
             continue
-        full = QMatMul.from_arc(QTensor.new(random_blocks(w.dtype, w.n, w.k, SEED + i, dev), GgmlDType(w.dtype), (w.n, w.k)))
+        full = QMatMul.from_arc(QTensor.new(quantized_blocks(w.dtype, w.n, w.k, SEED + i, dev), GgmlDType(w.dtype), (w.n, w.k)))
         x = torch.from_numpy(gen_activations(m, w.k, SEED + 31 + i)).to(dev)
         ref = full.forward(x, mode=Mode.INT8_ACT)
         if sh.parallel == "column":
@@ -819,7 +819,7 @@ def tp_measure(wl, dev, ctx, rank, world, rows_modes, steps, head=True, own=True
     for pt in points:
         pt["weight_gbs_aggregate"] = total_bytes / (pt["ms_per_step"] * 1e-3) / 1e9
     return {"workload": f"{wl.name}: {wl.description}, tensor-parallel x{world}" + (" + lm_head" if head else ""),
-            "weights": "valid random blocks generated on the GPU, sharded as bytes",
+            "weights": "seeded N(0, 0.02) quantized on the GPU (turq_quantize_weights), sharded as bytes",
             "exchange": ("own kernels over peer memory (turq_tp_*): all-reduce fused behind attn_output and ffn_down, "
                          "all-gather behind the head; no NCCL call inside the pass") if own else
                         "NCCL all-reduce after attn_output and ffn_down, all-gather after the head (eager launches)",

@@ -145,6 +145,15 @@ int32_t turq_dequantize(turq_ctx* ctx, const turq_qtensor* qt, int32_t out_dtype
 int32_t turq_embedding(turq_ctx* ctx, const turq_qtensor* qt, const int32_t* dev_ids, int64_t n_ids,
                        int32_t out_dtype, void* dev_out, void* stream);
 
+/* QTensor::quantize (candle-core; tur only loads quantized files, src/weights/gguf_varbuilder.rs:73,
+ * but the benchmark configurations quantize synthetic weights with it): f32 rows
+ * [n_rows, n_cols] -> wire-format blocks of dtype (Q8_0, Q4_K, Q5_K or Q6_K), n_rows rows of
+ * turq_row_bytes(dtype, n_cols) bytes, ready for turq_qtensor_from_device. Q8_0 is the GGML
+ * reference quantizer; the K-quant search is this library's own (valid blocks, not candle's
+ * bytes): min/max start plus least-squares refits per sub-block. dev_x 16-byte aligned. */
+int32_t turq_quantize_weights(turq_ctx* ctx, int32_t dtype, const float* dev_x, int64_t n_rows,
+                              int64_t n_cols, void* dev_blocks, void* stream);
+
 /* Activation quantization used inside QMatMul::forward (entered at
  * src/models/layers/linear.rs:24): x [m, k] (F32 or BF16) -> wire-format Q8_0 or Q8_K blocks,
  * m rows of turq_row_bytes(fmt, k) bytes. */

@@ -5,7 +5,7 @@
 //
 //   candle / tur item                                        here
 //   GgmlDType (block_size, type_size)                        turq::GgmlDType, block_size(), type_size()
-//   QTensor::new / shape / dtype / dequantize                turq::QTensor
+//   QTensor::new / quantize / shape / dtype / dequantize     turq::QTensor
 //     (src/weights/gguf_varbuilder.rs:62-79, src/weights/mod.rs:150)
 //   QMatMul::from_arc / forward                              turq::QMatMul
 //     (src/models/layers/linear.rs:24,69)
@@ -77,6 +77,16 @@ class QTensor {
                                             const void* blocks, size_t nbytes) {
     turq_qtensor* h = nullptr;
     ctx->check(turq_qtensor_from_host(ctx->handle(), static_cast<int32_t>(dtype), rows, cols, blocks, nbytes, &h));
+    return std::shared_ptr<QTensor>(new QTensor(std::move(ctx), h));
+  }
+  // candle: QTensor::quantize. dev_x is [rows, cols] f32 on the device; dev_blocks is the caller's
+  // scratch of turq_row_bytes(dtype, cols) * rows bytes that receives the wire blocks on the way.
+  static std::shared_ptr<QTensor> quantize(std::shared_ptr<Context> ctx, GgmlDType dtype, int64_t rows, int64_t cols,
+                                           const float* dev_x, void* dev_blocks, void* stream = nullptr) {
+    const int32_t dt = static_cast<int32_t>(dtype);
+    ctx->check(turq_quantize_weights(ctx->handle(), dt, dev_x, rows, cols, dev_blocks, stream));
+    turq_qtensor* h = nullptr;
+    ctx->check(turq_qtensor_from_device(ctx->handle(), dt, rows, cols, dev_blocks, turq_row_bytes(dt, cols) * (size_t)rows, stream, &h));
     return std::shared_ptr<QTensor>(new QTensor(std::move(ctx), h));
   }
   ~QTensor() {

@@ -383,6 +383,16 @@ static void quant_row_q8k(const float* x, uint8_t* b, int64_t k) {
   }
 }
 
+/* Round to nearest, ties to even, with a defined result for every input (lrintf leaves NaN and
+ * out-of-range values to the platform): NaN -> 0, otherwise saturating at the int range. Only
+ * blocks of non-finite or denormal-range data get there; the device quantizer rounds alike. */
+static inline int rint_sat(float v) {
+  if (v != v) return 0;
+  if (v >= 2147483648.f) return 2147483647;
+  if (v <= -2147483648.f) return -2147483647 - 1;
+  return (int)lrintf(v);
+}
+
 /* Fit x ~ scale*q + mn (mn <= 0) with q in [0,nmax] for one sub-block: min/max start,
  * then alternate rounding and a 2-parameter least-squares refit while the error drops. */
 static void fit_scale_min(const float* x, int n, int nmax, float* scale_out, float* negmin_out) {
@@ -404,7 +414,7 @@ static void fit_scale_min(const float* x, int n, int nmax, float* scale_out, flo
     float inv = 1.f / scale;
     double sq = 0, sqq = 0, sx = 0, sxq = 0, err = 0;
     for (int i = 0; i < n; i++) {
-      int q = (int)lrintf((x[i] - mn) * inv);
+      int q = rint_sat((x[i] - mn) * inv);
       q = q < 0 ? 0 : (q > nmax ? nmax : q);
       float r = scale * (float)q + mn - x[i];
       err += (double)r * r;
@@ -452,8 +462,8 @@ static void quant_row_q45k(const float* x, uint8_t* b, int64_t k, int bits) {
     float inv_min = max_min > 0.f ? 63.f / max_min : 0.f;
     int ls[8], lm[8];
     for (int j = 0; j < 8; j++) {
-      int a = (int)lrintf(inv_scale * scales[j]);
-      int c = (int)lrintf(inv_min * mins[j]);
+      int a = rint_sat(inv_scale * scales[j]);
+      int c = rint_sat(inv_min * mins[j]);
       ls[j] = a < 0 ? 0 : (a > 63 ? 63 : a);
       lm[j] = c < 0 ? 0 : (c > 63 ? 63 : c);
     }
@@ -468,7 +478,7 @@ static void quant_row_q45k(const float* x, uint8_t* b, int64_t k, int bits) {
       for (int i = 0; i < 32; i++) {
         int q = 0;
         if (dl != 0.f) {
-          q = (int)lrintf((x[32 * j + i] + ml) / dl);
+          q = rint_sat((x[32 * j + i] + ml) / dl);
           q = q < 0 ? 0 : (q > nmax ? nmax : q);
         }
         L[32 * j + i] = (uint8_t)q;
@@ -504,7 +514,7 @@ static void quant_row_q6k(const float* x, uint8_t* b, int64_t k) {
       if (s != 0.f) { /* one least-squares refit of the scale on the rounded integers */
         double sxq = 0, sqq = 0;
         for (int i = 0; i < 16; i++) {
-          int q = (int)lrintf(xs[i] / s);
+          int q = rint_sat(xs[i] / s);
           q = q < -32 ? -32 : (q > 31 ? 31 : q);
           sxq += (double)xs[i] * q;
           sqq += (double)q * q;
@@ -526,14 +536,14 @@ static void quant_row_q6k(const float* x, uint8_t* b, int64_t k) {
     wr16(b + 208, dh);
     uint8_t L[QK_K];
     for (int j = 0; j < 16; j++) {
-      int s = d != 0.f ? (int)lrintf(scales[j] / d) : 0;
+      int s = d != 0.f ? rint_sat(scales[j] / d) : 0;
       s = s < -128 ? -128 : (s > 127 ? 127 : s);
       sc[j] = (int8_t)s;
       float dl = d * (float)s;
       for (int i = 0; i < 16; i++) {
         int q = 0;
         if (dl != 0.f) {
-          q = (int)lrintf(x[16 * j + i] / dl);
+          q = rint_sat(x[16 * j + i] / dl);
           q = q < -32 ? -32 : (q > 31 ? 31 : q);
         }
         L[16 * j + i] = (uint8_t)(q + 32);

@@ -199,6 +199,48 @@ impl QTensor {
         Self::wrap(ctx, h)
     }
 
+    /// candle: `QTensor::quantize(&Tensor, GgmlDType)`. `src` holds `shape.0` rows of `shape.1` f32
+    /// values; the blocks are computed on the device (`turq_quantize_weights`) and converted to
+    /// the device layout without returning to the host.
+    pub fn quantize(ctx: &Arc<Context>, src: &[f32], dtype: GgmlDType, shape: (usize, usize)) -> Result<Self> {
+        let n = shape.0.checked_mul(shape.1).ok_or(Error { status: sys::TURQ_E_SHAPE, message: "shape overflows".into() })?;
+        if src.len() != n || n == 0 {
+            return Err(Error { status: sys::TURQ_E_SHAPE, message: format!("{} values for shape {:?}", src.len(), shape) });
+        }
+        // SAFETY: pure size query.
+        let nbytes = unsafe { sys::turq_row_bytes(dtype as i32, shape.1 as i64) } * shape.0;
+        if nbytes == 0 {
+            return Err(Error { status: sys::TURQ_E_SHAPE, message: format!("{} columns are not whole blocks", shape.1) });
+        }
+        let (mut dev_x, mut dev_b): (*mut c_void, *mut c_void) = (ptr::null_mut(), ptr::null_mut());
+        let mut h: *mut sys::turq_qtensor = ptr::null_mut();
+        // SAFETY: plain allocation / copy calls of the CUDA runtime and library calls on live
+        // handles; both device buffers are released on every path. The null stream orders the
+        // copy, the two library launches and the synchronous free.
+        let st = unsafe {
+            if cuda::cudaMalloc(&mut dev_x, n * 4) != 0 {
+                return Err(Error { status: sys::TURQ_E_CUDA, message: "cudaMalloc failed".into() });
+            }
+            if cuda::cudaMalloc(&mut dev_b, nbytes) != 0 {
+                cuda::cudaFree(dev_x);
+                return Err(Error { status: sys::TURQ_E_CUDA, message: "cudaMalloc failed".into() });
+            }
+            let mut st = if cuda::cudaMemcpy(dev_x, src.as_ptr().cast::<c_void>(), n * 4, cuda::MEMCPY_HOST_TO_DEVICE) == 0 {
+                sys::turq_quantize_weights(ctx.h, dtype as i32, dev_x.cast::<f32>(), shape.0 as i64, shape.1 as i64, dev_b, ptr::null_mut())
+            } else {
+                sys::TURQ_E_CUDA
+            };
+            if st == sys::TURQ_OK {
+                st = sys::turq_qtensor_from_device(ctx.h, dtype as i32, shape.0 as i64, shape.1 as i64, dev_b, nbytes, ptr::null_mut(), &mut h);
+            }
+            cuda::cudaFree(dev_x);
+            cuda::cudaFree(dev_b);
+            st
+        };
+        ctx.check(st)?;
+        Self::wrap(ctx, h)
+    }
+
     fn wrap(ctx: &Arc<Context>, h: *mut sys::turq_qtensor) -> Result<Self> {
         let (mut dt, mut r, mut c, mut nb) = (0i32, 0i64, 0i64, 0usize);
         // SAFETY: `h` is a live tensor handle, the out pointers are valid.
@@ -281,9 +323,10 @@ impl Drop for QTensor {
     }
 }
 
-/// The three CUDA runtime calls `QTensor::dequantize` needs to hand back host values.
+/// The three CUDA runtime calls `QTensor::quantize` / `dequantize` need to move host values.
 mod cuda {
     use core::ffi::c_void;
+    pub const MEMCPY_HOST_TO_DEVICE: i32 = 1;
     pub const MEMCPY_DEVICE_TO_HOST: i32 = 2;
     #[link(name = "cudart")]
     unsafe extern "C" {

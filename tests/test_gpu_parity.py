@@ -427,6 +427,54 @@ def test_single_row_tile_function_in_a_mixed_type_launch(tq):
     tq.context().poll_status()
 
 
+@pytest.mark.parametrize("dt", TYPES, ids=ids)
+def test_weight_quantizer_writes_the_oracle_quantizer_bytes(tq, dt):
+    """QTensor::quantize (candle-core; the benchmark configurations quantize their synthetic
+    weights with it). The device quantizer must write the bytes of the CPU restatement: seeded
+    N(0, 0.02) rows as the configurations prescribe, plus blocks that take the search's side
+    exits (all zero, constant, all positive, all negative, one outlier, tiny and huge ranges)."""
+    from tur_b200.quantized import quantize_weights
+    n, k = 37, 2048
+    rng = np.random.default_rng(SEED + 4242 + dt)
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    w[0, :256] = 0.0
+    w[1, :256] = 0.75
+    w[2, :256] = np.abs(w[2, :256]) + 0.01
+    w[3, :256] = -np.abs(w[3, :256]) - 0.01
+    w[4, 17] = 9.0
+    w[5, :256] *= 1e-20
+    w[6, :256] *= 1e20
+    w[7, 32:64] = 0.0          # one empty sub-block inside a live block
+    w[8, :256] = np.round(w[8, :256] * 400) / 400   # many rounding ties
+    want = oracle.quantize(dt, w)
+    got = quantize_weights(torch.from_numpy(w).cuda(), tq.GgmlDType(dt))
+    tq.context().poll_status()
+    got = got.cpu().numpy().reshape(-1)
+    want = np.asarray(want).view(np.uint8).reshape(-1)
+    assert got.size == want.size
+    bad = np.flatnonzero(got != want)
+    assert bad.size == 0, f"{bad.size} bytes differ, first at {bad[:8]} (block bytes {oracle.block_bytes(dt)})"
+    # and the tensor made from them is the oracle's tensor
+    qt = tq.QTensor.quantize(torch.from_numpy(w).cuda(), tq.GgmlDType(dt))
+    assert qt.shape() == (n, k) and qt.dtype() == tq.GgmlDType(dt)
+    # (the huge-range row overflows the f16 block scale: inf and inf * 0 on both sides)
+    assert np.array_equal(qt.dequantize().cpu().numpy(), oracle.dequantize(dt, want, k), equal_nan=True)
+
+
+def test_weight_quantizer_rejects_what_it_cannot_do(tq):
+    from tur_b200.quantized import quantize_weights
+    x = torch.zeros(4, 256, device="cuda")
+    with pytest.raises(tq.TurqError) as e:
+        quantize_weights(x, tq.GgmlDType.Q8K)           # an activation format, not a weight type
+    assert e.value.status == 3
+    with pytest.raises(tq.TurqError) as e:
+        quantize_weights(x[:, :100].contiguous(), tq.GgmlDType.Q4K)   # not whole blocks
+    assert e.value.status == 2
+    with pytest.raises(tq.TurqError):
+        quantize_weights(x.cpu(), tq.GgmlDType.Q4K)     # no CPU fallback
+    tq.context().poll_status()
+
+
 def test_no_kernel_gave_up_a_wait(tq):
     tq.context().poll_status()
 

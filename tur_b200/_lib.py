@@ -40,6 +40,7 @@ SIGNATURES = {
     "turq_dequantize": (c_i32, [c_vp, c_vp, c_i32, c_vp, c_vp]),
     "turq_embedding": (c_i32, [c_vp, c_vp, c_vp, c_i64, c_i32, c_vp, c_vp]),
     "turq_quantize_act": (c_i32, [c_vp, c_i32, c_vp, c_i32, c_i64, c_i64, c_vp, c_vp]),
+    "turq_quantize_weights": (c_i32, [c_vp, c_i32, c_vp, c_i64, c_i64, c_vp, c_vp]),
     "turq_qmatmul": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i64, c_vp, c_i32, c_vp, c_vp]),
     "turq_qmatmul_multi": (c_i32, [c_vp, c_i32, c_vp, c_vp, c_i32, c_i64, c_vp, c_i32, c_vp, c_vp]),
     "turq_qmatmul_host": (c_i32, [c_vp, c_vp, c_vp, c_i64, c_vp, c_i32, c_vp]),

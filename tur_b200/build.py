@@ -9,7 +9,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libturq.so")
-SOURCES = ["api.cu", "repack.cu", "dequant.cu", "actquant.cu", "gemv.cu", "gemv_stream.cu", "gemm_tc.cu", "noalloc.cu", "tp.cu", "fused.cu"]
+SOURCES = ["api.cu", "repack.cu", "dequant.cu", "actquant.cu", "wquant.cu", "gemv.cu", "gemv_stream.cu", "gemm_tc.cu", "noalloc.cu", "tp.cu", "fused.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 

@@ -417,6 +417,23 @@ int32_t turq_quantize_act(turq_ctx* ctx, int32_t fmt, const void* dev_x, int32_t
   return TURQ_OK;
 }
 
+int32_t turq_quantize_weights(turq_ctx* ctx, int32_t dtype, const float* dev_x, int64_t n_rows, int64_t n_cols,
+                              void* dev_blocks, void* stream) {
+  if (!ctx || !dev_x || !dev_blocks) return fail(ctx, TURQ_E_INVALID_ARG, "null argument");
+  if (dtype != TURQ_Q8_0 && dtype != TURQ_Q4_K && dtype != TURQ_Q5_K && dtype != TURQ_Q6_K)
+    return fail(ctx, TURQ_E_DTYPE, "weight type must be Q8_0, Q4_K, Q5_K or Q6_K (got %d)", dtype);
+  if (n_rows <= 0 || n_cols <= 0 || n_cols % tq_block_elems(dtype) != 0)
+    return fail(ctx, TURQ_E_SHAPE, "n_rows=%lld n_cols=%lld: n_cols must be a positive multiple of %d", (long long)n_rows,
+                (long long)n_cols, tq_block_elems(dtype));
+  if ((uintptr_t)dev_x % 16 != 0) return fail(ctx, TURQ_E_ALIGN, "dev_x must be 16-byte aligned");
+  TQ_CUDA(ctx, cudaSetDevice(ctx->device));
+  cudaError_t e = turq::launch_quantize_weights(dtype, dev_x, n_rows, n_cols, static_cast<uint8_t*>(dev_blocks),
+                                                static_cast<cudaStream_t>(stream));
+  ctx->launches++;
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "quantize_weights launch");
+  return TURQ_OK;
+}
+
 // TURQ_MODE_AUTO: the integer GEMV up to 16 rows, the tcgen05 GEMM above (64-row activation
 // tiles with split-K for decode batches, 128/256-row tiles for prefill). Measured on B200 at 32
 // and 64 rows the GEMM is ahead for every weight shape of the benchmark configurations.

@@ -57,6 +57,8 @@ cudaError_t launch_slice_cols(int dtype, const uint8_t* src_tiles, uint8_t* dst_
                               cudaStream_t s);
 
 // activations -> wire-format Q8_0 / Q8_K blocks
+// f32 rows -> GGUF wire blocks of a weight type (Q8_0, Q4_K, Q5_K, Q6_K); x 16-byte aligned.
+cudaError_t launch_quantize_weights(int dtype, const float* x, int64_t n_rows, int64_t k, uint8_t* wire, cudaStream_t s);
 cudaError_t launch_quantize_act_wire(int fmt, const void* x, int x_dtype, int64_t m, int64_t k,
                                      void* blocks, cudaStream_t s);
 // activations -> ActPack planes at `scratch` (laid out by plan_act_pack)

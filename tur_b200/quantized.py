@@ -172,6 +172,13 @@ class QTensor:
                                              buf.size, ctypes.byref(out)))
         return cls(out, ctx)
 
+    @classmethod
+    def quantize(cls, src: torch.Tensor, dtype: GgmlDType, ctx: Optional[_Context] = None) -> "QTensor":
+        """candle: QTensor::quantize(&Tensor, GgmlDType). src is a 2-D f32 CUDA tensor whose
+        columns are whole blocks of `dtype` (Q8_0, Q4_K, Q5_K, Q6_K)."""
+        blocks = quantize_weights(src, dtype, ctx=ctx)
+        return cls.new(blocks, dtype, tuple(src.shape), ctx=ctx)
+
     def dtype(self) -> GgmlDType:
         return self._dtype
 
@@ -226,6 +233,23 @@ def quantize_act(x: torch.Tensor, fmt: GgmlDType) -> torch.Tensor:
     out = torch.empty((m, max(rb, 1)), dtype=torch.uint8, device=x.device)
     ctx.check(lib.turq_quantize_act(ctx.handle, int(fmt), ctypes.c_void_p(x2.data_ptr()), int(_TORCH_TO_GGML[x2.dtype]),
                                     m, k, ctypes.c_void_p(out.data_ptr()), _stream_ptr(ctx.device)))
+    return out
+
+
+def quantize_weights(src: torch.Tensor, dtype: GgmlDType, ctx: Optional[_Context] = None) -> torch.Tensor:
+    """f32 [n, k] (CUDA) -> uint8 [n, row_bytes] of wire-format blocks of a weight type."""
+    if not src.is_cuda:
+        raise TurqError(8, "quantize_weights needs a CUDA tensor (no CPU fallback)")
+    if src.dim() != 2 or src.dtype != torch.float32:
+        raise TurqError(2, f"quantize_weights needs a 2-D f32 tensor, got {tuple(src.shape)} {src.dtype}")
+    ctx = ctx or context(src.device)
+    x2 = src.contiguous()
+    n, k = x2.shape
+    lib = _lib.load()
+    rb = lib.turq_row_bytes(int(dtype), k)
+    out = torch.empty((n, max(rb, 1)), dtype=torch.uint8, device=src.device)
+    ctx.check(lib.turq_quantize_weights(ctx.handle, int(dtype), ctypes.c_void_p(x2.data_ptr()), n, k,
+                                        ctypes.c_void_p(out.data_ptr()), _stream_ptr(ctx.device)))
     return out
 
 

@@ -93,3 +93,21 @@ def random_blocks(dtype: int, n: int, k: int, seed: int, device):
         if dtype in (Q4_K, Q5_K):
             raw[:, 2:4] = scale
     return raw.reshape(-1)
+
+
+def quantized_blocks(dtype: int, n: int, k: int, seed: int, device):
+    """Seeded N(0, 0.02) weights [n, k] quantized on the GPU to wire blocks of `dtype` (flat uint8
+    tensor): the value distribution the benchmark configurations prescribe, made by the library's
+    own weight quantizer (turq_quantize_weights), in slabs of rows so that the f32 source of a
+    large vocabulary matrix never has to exist as a whole."""
+    import torch
+    from .quantized import GgmlDType, quantize_weights
+    g = torch.Generator(device=device).manual_seed(seed)
+    rows_per_slab = max(16, (1 << 26) // k)
+    parts = []
+    for r0 in range(0, n, rows_per_slab):
+        r = min(rows_per_slab, n - r0)
+        w = torch.randn((r, k), device=device, generator=g, dtype=torch.float32) * 0.02
+        parts.append(quantize_weights(w, GgmlDType(dtype)).reshape(-1))
+    return torch.cat(parts) if len(parts) > 1 else parts[0]
+
