@@ -286,6 +286,13 @@ int32_t turq_tp_set_wait_limit(turq_tp* tp, int64_t cycles);
 /* Largest result (m * n * 4 bytes) turq_qmatmul_rowparallel exchanges inside the matmul kernel
  * itself (default 64 KB); 0 = always use the separate exchange launch. Same value on every rank. */
 int32_t turq_tp_set_fuse_limit(turq_tp* tp, int64_t bytes);
+/* Smallest result (bytes) that takes the two-shot exchange on three or more ranks: every rank
+ * reduces one slice, then copies the others (default 256 KB). Same value on every rank. */
+int32_t turq_tp_set_twoshot_limit(turq_tp* tp, int64_t bytes);
+/* Rows per chunk of a prefill-sized turq_qmatmul_rowparallel in the dequantizing modes, whose
+ * exchange overlaps the next chunk's product (0 = default, about 16 MB of result per chunk;
+ * products of fewer than two chunks are not cut). Same value on every rank. */
+int32_t turq_tp_set_chunk_rows(turq_tp* tp, int64_t rows);
 /* Clears this rank's flags and call counter. Collective in effect: call it on every rank, with
  * no group call in flight (the host synchronizes the ranks around it). */
 int32_t turq_tp_reset(turq_tp* tp);
@@ -312,7 +319,7 @@ int32_t turq_qmatmul_gather(turq_tp* tp, const turq_qtensor* qt, const void* dev
 /* Test support on a single GPU: connects the group to local stand-ins for the other ranks, which
  * never signal by themselves (a call then runs into its wait limit), and lets the host play a
  * peer's part for the next call: its data (count floats, may be NULL / 0) and, with signal != 0,
- * its "ready" flags. */
+ * its "ready" flags (signal = k: the stand-in has arrived at the next k calls). */
 int32_t turq_tp_connect_loopback(turq_tp* tp);
 int32_t turq_tp_loopback_fill(turq_tp* tp, int32_t peer, const float* dev_src, int64_t count, int32_t signal,
                               void* stream);

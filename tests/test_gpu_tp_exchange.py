@@ -113,6 +113,67 @@ def test_reduction_adds_the_ranks_in_rank_order(tq, world, rank):
     tq.context().poll_status()
 
 
+@pytest.mark.parametrize("world,rank", [(4, 1), (8, 7), (3, 0)])
+def test_two_shot_exchange_reduces_one_slice_and_copies_the_others(tq, world, rank):
+    """Large results on three or more ranks: this rank adds its slice of the float4 groups in rank
+    order and takes the other slices, already reduced, from their owners. The stand-ins hold what
+    a real peer's slot holds at the second meeting point: its partial, with its own slice replaced
+    by the reduced values."""
+    from tur_b200.tensor_parallel import TPGroup
+    rng = np.random.default_rng(SEED + 17 * world)
+    count = 4 * 5000 + 4 * world - 4          # slices of unequal length at the end
+    g = TPGroup(rank, world, count * 4, loopback=True)
+    g.set_twoshot_limit(1)
+    nvec = count // 4
+    per = (nvec + world - 1) // world
+    for call in range(3):
+        parts = [torch.from_numpy(rng.standard_normal(count).astype(np.float32)).cuda() for _ in range(world)]
+        want = parts[0].clone()
+        for p in range(1, world):
+            want += parts[p]
+        for p in range(world):
+            if p == rank:
+                continue
+            slot = parts[p].clone()
+            lo, hi = 4 * p * per, min(4 * (p + 1) * per, count)
+            slot[lo:hi] = want[lo:hi]
+            g.loopback_fill(p, slot, signal=True)
+        assert torch.equal(g.allreduce(parts[rank]), want), call
+    tq.context().poll_status()
+
+
+def test_prefill_sized_row_parallel_product_is_cut_into_chunks(tq):
+    """Chunks of rows whose exchange runs on the group's second stream while the next chunk is
+    computed. One GPU: the stand-in peer contributes zeros and has arrived at every chunk's
+    meeting point ahead of time, so the result is this rank's own product - the same bits as the
+    plain matmul - eager and in a replayed graph."""
+    from tur_b200.tensor_parallel import TPGroup
+    n, k, m = 512, 1024, 1024 + 128
+    rng = np.random.default_rng(SEED + 4321)
+    w = oracle.quantize(oracle.Q4_K, (rng.standard_normal((n, k)) * 0.02).astype(np.float32))
+    mm = tq.QMatMul.from_arc(tq.QTensor.new(w, tq.GgmlDType.Q4K, (n, k)))
+    x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).cuda().to(torch.bfloat16)
+    bias = torch.from_numpy(rng.standard_normal(n).astype(np.float32)).cuda()
+    want = mm.forward(x, bias=bias, mode=tq.Mode.TENSOR_CORE)
+    g = TPGroup(0, 2, 256 * n * 4, loopback=True)      # a slot holds one chunk, not the product
+    g.set_chunk_rows(256)                              # 5 chunks (the last one 128 rows)
+    g.loopback_fill(1, None, signal=40)
+    y = g.qmatmul_rowparallel(mm, x, bias=bias, mode=tq.Mode.TENSOR_CORE)
+    assert torch.equal(y, want)
+    out = torch.empty_like(y)
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side), torch.cuda.graph(graph, stream=side):
+        g.qmatmul_rowparallel(mm, x, bias=bias, mode=tq.Mode.TENSOR_CORE, out=out)
+    for _ in range(3):
+        out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, want)
+    tq.context().poll_status()
+
+
 def test_a_peer_that_never_arrives_ends_the_wait_with_a_status(tq):
     from tur_b200.tensor_parallel import TPGroup
     ctx = tq.new_context()

@@ -81,8 +81,55 @@ def main() -> None:
             y = g.allgather(yl, widths)
             assert torch.equal(y, ref), "column-parallel gather"
             assert torch.equal(g.qmatmul_gather(mine, x, widths, mode=Mode.INT8_ACT), ref), "gather fused behind the matmul"
+    # ---- large results: the two-shot exchange on three or more ranks (one-shot on two), bit-exact
+    # against the ordered sum, identical on every rank; then a prefill-sized row-parallel product
+    # cut into chunks whose exchanges overlap the next chunk's GEMM, eager and as a graph
+    big = TPGroup(rank, world, ((1 << 20) + 256) * 4, ctx=ctx)
+    for count in (1 << 18, (1 << 20) + 4 * 37):
+        x = torch.randn(count, device=dev, generator=gen)
+        everyone = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(everyone, x)
+        want = everyone[0].clone()
+        for p in range(1, world):
+            want += everyone[p]
+        got = big.allreduce(x)
+        assert torch.equal(got, want), f"large allreduce count={count}"
+    w = down
+    full_blocks = random_blocks(w.dtype, w.n, w.k, 77 + w.n, dev)
+    sh = shard_of(w, world, rank, 256)
+    full = QMatMul.from_arc(QTensor.new(full_blocks, GgmlDType(w.dtype), (w.n, w.k)))
+    mine = QMatMul.from_arc(QTensor.new(shard_blocks(full_blocks, w, sh).reshape(-1), GgmlDType(w.dtype), sh.shape))
+    mp = 1536
+    xp = torch.from_numpy(np.random.default_rng(6).standard_normal((mp, w.k)).astype(np.float32)).to(dev).to(torch.bfloat16)
+    xl = xp[:, sh.cols[0]: sh.cols[0] + sh.cols[1]].contiguous()
+    ref = full.forward(xp, mode=Mode.TENSOR_CORE)
+    big.set_chunk_rows(0)
+    whole = TPGroup(rank, world, mp * down.n * 4, ctx=ctx)
+    whole.set_chunk_rows(1 << 20)                      # never cut: the unchunked exchange of the same product
+    y_whole = whole.qmatmul_rowparallel(mine, xl, mode=Mode.TENSOR_CORE)
+    big.set_chunk_rows(256)                            # 6 chunks
+    y = big.qmatmul_rowparallel(mine, xl, mode=Mode.TENSOR_CORE)
+    err = float((y - ref).norm() / ref.norm())
+    assert err < 2e-3, f"chunked row-parallel rel error {err}"
+    assert torch.equal(y, y_whole), "chunked and unchunked exchange disagree"
+    everyone = [torch.empty_like(y) for _ in range(world)]
+    dist.all_gather(everyone, y)
+    assert all(torch.equal(everyone[0], e) for e in everyone)
+    out = torch.empty_like(y)
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side), torch.cuda.graph(graph, stream=side):
+        big.qmatmul_rowparallel(mine, xl, mode=Mode.TENSOR_CORE, out=out)
+    dist.barrier()
+    for _ in range(5):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, y), "graph replay of the chunked product"
     ctx.poll_status()
     dist.barrier()
+    whole.close()
+    big.close()
     g.close()
     dist.destroy_process_group()
     print(f"TP_WORKER_OK {rank}", flush=True)

@@ -59,6 +59,8 @@ SIGNATURES = {
     "turq_tp_destroy": (c_i32, [c_vp]),
     "turq_tp_set_wait_limit": (c_i32, [c_vp, c_i64]),
     "turq_tp_set_fuse_limit": (c_i32, [c_vp, c_i64]),
+    "turq_tp_set_twoshot_limit": (c_i32, [c_vp, c_i64]),
+    "turq_tp_set_chunk_rows": (c_i32, [c_vp, c_i64]),
     "turq_tp_reset": (c_i32, [c_vp]),
     "turq_tp_allreduce": (c_i32, [c_vp, c_vp, c_vp, c_i64, c_vp]),
     "turq_tp_allgather": (c_i32, [c_vp, c_vp, c_i64, c_vp, c_vp, c_vp]),

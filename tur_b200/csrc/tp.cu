@@ -52,6 +52,18 @@ __global__ void __launch_bounds__(TP_THREADS) tp_allreduce_kernel(const TpArgs a
   tp_finish(a, seq, ok);
 }
 
+// Large results on three or more ranks: reduce-scatter, then gather (tp_twoshot).
+__global__ void __launch_bounds__(TP_THREADS) tp_allreduce2_kernel(const TpArgs a) {
+  __shared__ int s_ok;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const unsigned seq = *reinterpret_cast<volatile unsigned*>(a.counter) + 1u;
+  const size_t slot_off = (seq & 1u) ? a.slot_elems : 0;
+  bool ok = tp_rendezvous(a, seq, &s_ok, blockIdx.x);
+  if (ok) ok = tp_twoshot(a, seq, slot_off, &s_ok, blockIdx.x, gridDim.x);
+  tp_finish(a, seq, ok);
+}
+
 __global__ void __launch_bounds__(TP_THREADS) tp_allgather_kernel(const TpArgs a) {
   __shared__ int s_ok;
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -123,6 +135,11 @@ struct turq_tp {
   bool connected = false;
   long long wait_cycles = 2000000000ll;  // about one second of SM clock
   size_t fuse_max_bytes = 64 << 10;      // results up to this size are exchanged by the GEMV's own last CTA
+  size_t twoshot_min_bytes = 256 << 10;  // results from this size on take the two-shot exchange (3+ ranks)
+  int64_t chunk_rows = 0;                // rows per chunk of a chunked row-parallel GEMM (0: about 16 MB of result)
+  // chunked row-parallel GEMM: the exchange of chunk j runs on `comm` while chunk j + 1 is computed
+  cudaStream_t comm = nullptr;
+  cudaEvent_t ev_mm[2] = {}, ev_x[2] = {};
 };
 
 namespace {
@@ -181,10 +198,64 @@ int32_t launch_reduce(turq_tp* tp, int64_t count, int64_t n, const float* bias, 
   a.bias = bias;
   a.out = out;
   // the same grid on every rank (CTA b pairs with CTA b of the peers): it depends on count only
-  const int grid = grid_for((count + 3) / 4, turq::TP_MAX_BLOCKS);
-  cudaError_t e = tp_launch_pdl(turq::tp_allreduce_kernel, (unsigned)grid, (unsigned)turq::TP_THREADS, s, a);
+  // (so does the choice of the two-shot form: size and world only)
+  const bool twoshot = tp->world >= 3 && (count & 3) == 0 && (size_t)count * 4 >= tp->twoshot_min_bytes;
+  const int grid = twoshot ? grid_for(((count >> 2) + tp->world - 1) / tp->world, turq::TP_MAX_BLOCKS)
+                           : grid_for((count + 3) / 4, turq::TP_MAX_BLOCKS);
+  cudaError_t e = twoshot ? tp_launch_pdl(turq::tp_allreduce2_kernel, (unsigned)grid, (unsigned)turq::TP_THREADS, s, a)
+                          : tp_launch_pdl(turq::tp_allreduce_kernel, (unsigned)grid, (unsigned)turq::TP_THREADS, s, a);
   tp->ctx->launches++;
   if (e != cudaSuccess) return tp_cuda_fail(tp, e, "all-reduce launch");
+  return TURQ_OK;
+}
+
+// Row-parallel product in chunks of rows: chunk j is computed on the caller's stream into one of
+// two result buffers, copied into the slot and exchanged on the group's second stream, while the
+// caller's stream goes on with chunk j + 1. The caller's stream rejoins at the end. A result
+// buffer is reused after the exchange two chunks earlier has read it; the slot protocol is the
+// one of separate calls (stage and exchange of a chunk follow the previous chunk's exchange on
+// the same stream).
+int32_t rowparallel_chunked(turq_tp* tp, const turq_qtensor* qt, const void* dev_x, int32_t x_dtype, int64_t m, float* dev_y,
+                            int32_t mode, const float* dev_bias, cudaStream_t s, int64_t chunk_m) {
+  turq_ctx* ctx = tp->ctx;
+  const int64_t n = qt->n_rows, k = qt->n_cols;
+  const int64_t nchunks = (m + chunk_m - 1) / chunk_m;
+  // even chunks in multiples of 64 rows, so that no chunk is a sliver
+  int64_t rows = (((m + nchunks - 1) / nchunks + 63) / 64) * 64;
+  if (rows > chunk_m) rows = chunk_m;
+  const size_t buf_elems = (size_t)rows * (size_t)n;
+  int32_t st = turq::api_ensure_tmp(ctx, 2 * buf_elems * 4);
+  if (st != TURQ_OK) return st;
+  float* bufs[2] = {reinterpret_cast<float*>(ctx->tmp), reinterpret_cast<float*>(ctx->tmp) + buf_elems};
+  const size_t x_es = x_dtype == TURQ_BF16 ? 2 : 4;
+  cudaError_t e = cudaSuccess;
+  int64_t j = 0;
+  for (int64_t r0 = 0; r0 < m && e == cudaSuccess; r0 += rows, j++) {
+    const int64_t mj = m - r0 < rows ? m - r0 : rows;
+    const int slot = (int)(j & 1);
+    if (j >= 2) e = cudaStreamWaitEvent(s, tp->ev_x[slot], 0);  // the exchange that read this buffer
+    if (e != cudaSuccess) break;
+    st = turq_qmatmul(ctx, qt, static_cast<const uint8_t*>(dev_x) + (size_t)r0 * (size_t)k * x_es, x_dtype, mj, bufs[slot], mode, nullptr, s);
+    if (st != TURQ_OK) return st;
+    e = cudaEventRecord(tp->ev_mm[slot], s);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(tp->comm, tp->ev_mm[slot], 0);
+    if (e != cudaSuccess) break;
+    const int64_t cnt = mj * n;
+    int64_t blocks = (cnt / 4 + 255) / 256;
+    if (blocks > 2 * (int64_t)ctx->sm_count) blocks = 2 * (int64_t)ctx->sm_count;
+    if (blocks < 1) blocks = 1;
+    turq::tp_stage_kernel<<<(unsigned)blocks, 256, 0, tp->comm>>>(bufs[slot], slot0(tp, tp->rank), tp->slot_bytes / 4, counter_of(tp), cnt);
+    ctx->launches++;
+    e = cudaGetLastError();
+    if (e != cudaSuccess) break;
+    st = launch_reduce(tp, cnt, n, dev_bias, dev_y + (size_t)r0 * (size_t)n, tp->comm);
+    if (st != TURQ_OK) return st;
+    e = cudaEventRecord(tp->ev_x[slot], tp->comm);
+  }
+  // rejoin: the caller's stream continues after the last two exchanges
+  if (e == cudaSuccess && j >= 2) e = cudaStreamWaitEvent(s, tp->ev_x[(int)((j - 2) & 1)], 0);
+  if (e == cudaSuccess && j >= 1) e = cudaStreamWaitEvent(s, tp->ev_x[(int)((j - 1) & 1)], 0);
+  if (e != cudaSuccess) return tp_cuda_fail(tp, e, "chunked row-parallel product");
   return TURQ_OK;
 }
 
@@ -215,6 +286,16 @@ int32_t turq_tp_create(turq_ctx* ctx, int32_t rank, int32_t world, size_t max_by
   if (e != cudaSuccess) {
     if (tp->region) cudaFree(tp->region);
     delete tp;
+    cudaGetLastError();
+    return bad(TURQ_E_CUDA, cudaGetErrorString(e));
+  }
+  e = cudaStreamCreateWithFlags(&tp->comm, cudaStreamNonBlocking);
+  for (int i = 0; i < 2 && e == cudaSuccess; i++) {
+    e = cudaEventCreateWithFlags(&tp->ev_mm[i], cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&tp->ev_x[i], cudaEventDisableTiming);
+  }
+  if (e != cudaSuccess) {
+    turq_tp_destroy(tp);
     cudaGetLastError();
     return bad(TURQ_E_CUDA, cudaGetErrorString(e));
   }
@@ -291,7 +372,10 @@ int32_t turq_tp_loopback_fill(turq_tp* tp, int32_t peer, const float* dev_src, i
   if (e == cudaSuccess && signal) {
     unsigned host_flags[turq::TP_MAX_BLOCKS * turq::TP_MAX_RANKS];
     e = cudaMemcpy(host_flags, flags_of(tp, tp->rank), sizeof(host_flags), cudaMemcpyDeviceToHost);
-    for (int b = 0; b < turq::TP_MAX_BLOCKS; b++) host_flags[b * turq::TP_MAX_RANKS + peer] = seq;
+    // both meeting points of that call (a stand-in that plays a two-shot peer has its reduced
+    // slice in the data already)
+    // `signal` = how many upcoming calls the stand-in has "arrived" at (1: the next one)
+    for (int b = 0; b < turq::TP_MAX_BLOCKS; b++) host_flags[b * turq::TP_MAX_RANKS + peer] = 2u * (done + (unsigned)signal) + 1u;
     if (e == cudaSuccess) e = cudaMemcpy(flags_of(tp, tp->rank), host_flags, sizeof(host_flags), cudaMemcpyHostToDevice);
   }
   if (e == cudaSuccess) e = cudaStreamSynchronize(s);
@@ -308,6 +392,18 @@ int32_t turq_tp_set_wait_limit(turq_tp* tp, int64_t cycles) {
 int32_t turq_tp_set_fuse_limit(turq_tp* tp, int64_t bytes) {
   if (!tp || bytes < 0) return TURQ_E_INVALID_ARG;
   tp->fuse_max_bytes = (size_t)bytes;
+  return TURQ_OK;
+}
+
+int32_t turq_tp_set_twoshot_limit(turq_tp* tp, int64_t bytes) {
+  if (!tp || bytes < 0) return TURQ_E_INVALID_ARG;
+  tp->twoshot_min_bytes = (size_t)bytes;
+  return TURQ_OK;
+}
+
+int32_t turq_tp_set_chunk_rows(turq_tp* tp, int64_t rows) {
+  if (!tp || rows < 0) return TURQ_E_INVALID_ARG;
+  tp->chunk_rows = rows;
   return TURQ_OK;
 }
 
@@ -332,6 +428,11 @@ int32_t turq_tp_destroy(turq_tp* tp) {
     if (tp->loopback[p]) cudaFree(tp->peers[p]);
   }
   if (tp->region) cudaFree(tp->region);
+  for (int i = 0; i < 2; i++) {
+    if (tp->ev_mm[i]) cudaEventDestroy(tp->ev_mm[i]);
+    if (tp->ev_x[i]) cudaEventDestroy(tp->ev_x[i]);
+  }
+  if (tp->comm) cudaStreamDestroy(tp->comm);
   cudaGetLastError();
   delete tp;
   return TURQ_OK;
@@ -401,12 +502,22 @@ int32_t turq_qmatmul_rowparallel(turq_tp* tp, const turq_qtensor* qt, const void
   if (!qt || !dev_x || !dev_y) return tp_fail(tp, TURQ_E_INVALID_ARG, "null argument");
   if (m <= 0 || m > INT32_MAX / 2) return tp_fail(tp, TURQ_E_SHAPE, "m out of range");
   const int64_t count = m * qt->n_rows;
-  if ((size_t)count * 4 > tp->slot_bytes) return tp_fail(tp, TURQ_E_LIMIT, "m x out-features exceeds an exchange slot (turq_tp_create max_bytes)");
+  // Prefill-sized products in the dequantizing modes are cut into chunks of rows: the exchange of
+  // a chunk runs on a second stream while the next chunk is computed, and a slot only has to
+  // hold one chunk.
+  const int32_t mode_resolved = mode == TURQ_MODE_AUTO ? turq::api_auto_mode(ctx, qt->n_rows, qt->n_cols, m) : mode;
+  int64_t chunk_m = tp->chunk_rows > 0 ? tp->chunk_rows : ((((int64_t)16 << 20) / (qt->n_rows * 4) + 255) / 256) * 256;
+  if (chunk_m < 256) chunk_m = 256;
+  while (chunk_m > 64 && (size_t)chunk_m * (size_t)qt->n_rows * 4 > tp->slot_bytes) chunk_m -= 64;
+  const bool chunked = tp->world > 1 && mode_resolved != TURQ_MODE_INT8_ACT && m >= 2 * chunk_m &&
+                       (size_t)chunk_m * (size_t)qt->n_rows * 4 <= tp->slot_bytes;
+  if (!chunked && (size_t)count * 4 > tp->slot_bytes) return tp_fail(tp, TURQ_E_LIMIT, "m x out-features exceeds an exchange slot (turq_tp_create max_bytes)");
   if ((uintptr_t)dev_y % 16 != 0) return tp_fail(tp, TURQ_E_ALIGN, "dev_y must be 16-byte aligned");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   float* s0 = slot0(tp, tp->rank);
   float* s1 = s0 + tp->slot_bytes / 4;
   float* staged = nullptr;
+  if (chunked) return rowparallel_chunked(tp, qt, dev_x, x_dtype, m, dev_y, mode_resolved, dev_bias, s, chunk_m);
   // Small results (decode): the GEMV's last CTA does the exchange - one kernel computes and
   // reduces. Larger ones get the multi-CTA exchange launch.
   turq::TpArgs fuse{};

@@ -173,6 +173,14 @@ class TPGroup:
         """Largest result the row-parallel matmul exchanges inside its own kernel (0: never)."""
         self.ctx.check(self._lib.turq_tp_set_fuse_limit(self._h, nbytes))
 
+    def set_twoshot_limit(self, nbytes: int) -> None:
+        """Smallest result exchanged as reduce-scatter + gather (three or more ranks)."""
+        self.ctx.check(self._lib.turq_tp_set_twoshot_limit(self._h, nbytes))
+
+    def set_chunk_rows(self, rows: int) -> None:
+        """Rows per chunk of a prefill-sized row-parallel product (0: default)."""
+        self.ctx.check(self._lib.turq_tp_set_chunk_rows(self._h, rows))
+
     def reset(self) -> None:
         self.ctx.check(self._lib.turq_tp_reset(self._h))
 
@@ -226,11 +234,12 @@ class TPGroup:
             bias.data_ptr() if bias is not None else None, self._stream()))
         return out
 
-    def loopback_fill(self, peer: int, data=None, signal: bool = True) -> None:
-        """Tests: play rank `peer`'s part for the next call (its data and, with `signal`, its flags)."""
+    def loopback_fill(self, peer: int, data=None, signal=True) -> None:
+        """Tests: play rank `peer`'s part for the next call: its data and, with `signal`, its flags
+        (an integer k > 1: it has arrived at the next k calls already)."""
         ptr = self._ct.c_void_p(data.data_ptr()) if data is not None else None
         self.ctx.check(self._lib.turq_tp_loopback_fill(self._h, peer, ptr, data.numel() if data is not None else 0,
-                                                       1 if signal else 0, self._stream()))
+                                                       int(signal), self._stream()))
 
 
 def row_unit_for(w: Weight, head_dim: Optional[int] = None) -> int:
