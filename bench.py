@@ -765,7 +765,8 @@ def tp_parity(stack, group, dev, ctx, m=4):
     return out
 
 
-def tp_measure(wl, dev, ctx, rank, world, rows_modes, steps, head=True, own=True, one_gpu=True, fuse_limit=None):
+def tp_measure(wl, dev, ctx, rank, world, rows_modes, steps, head=True, own=True, one_gpu=True, fuse_limit=None,
+               twoshot_limit=None, chunk_rows=None):
     """Strong scaling of one sharded pass: ms per pass at `world` ranks (CUDA-graph replay with the
     library's own exchange kernels when own=True, eager launches with NCCL collectives otherwise)
     and, measured by rank 0 alone in the same run, the unsharded pass on one GPU."""
@@ -780,6 +781,10 @@ def tp_measure(wl, dev, ctx, rank, world, rows_modes, steps, head=True, own=True
         group = TPGroup(rank, world, max(stack.exchange_bytes(max(r for r, _, _ in rows_modes)), 4 * 25600 * 4), ctx=ctx)
         if fuse_limit is not None:
             group.set_fuse_limit(fuse_limit)
+        if twoshot_limit is not None:
+            group.set_twoshot_limit(twoshot_limit)
+        if chunk_rows is not None:
+            group.set_chunk_rows(chunk_rows)
         parity = tp_parity(stack, group, dev, ctx)
     for rows, mode_name, xdtype in rows_modes:
         mode = Mode[mode_name]
@@ -847,7 +852,8 @@ def run_gpu_tp(args):
     sampler = ClockSampler(local)
     with sampler:
         obj = tp_measure(wl, dev, ctx, rank, world, [(m, args.mode, args.xdtype)], args.steps, head=not args.no_head,
-                         own=not args.nccl, one_gpu=not args.no_extras, fuse_limit=args.tp_fuse_limit)
+                         own=not args.nccl, one_gpu=not args.no_extras, fuse_limit=args.tp_fuse_limit,
+                         twoshot_limit=args.tp_twoshot_limit, chunk_rows=args.tp_chunk_rows)
     if rank == 0:
         pt = obj["points"][0]
         ms = pt["ms_per_step"]
@@ -891,6 +897,10 @@ def main():
     ap.add_argument("--no-multi", action="store_true", help="one launch per weight (no q|k, gate|up multi-weight launches)")
     ap.add_argument("--no-bound", action="store_true", help="e2e arm: per-call host entries instead of bound host calls")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of the timed pass's outputs")
+    ap.add_argument("--tp-twoshot-limit", type=int, default=None, help="tensor-parallel arm: smallest result (bytes) exchanged as "
+                    "reduce-scatter + gather")
+    ap.add_argument("--tp-chunk-rows", type=int, default=None, help="tensor-parallel arm: rows per chunk of a prefill-sized row-parallel "
+                    "product (its exchange overlaps the next chunk)")
     ap.add_argument("--no-extras", action="store_true", help="skip the sweep / prefill / other-config objects of the default run")
     ap.add_argument("--nccl", action="store_true", help="tensor-parallel arm: NCCL collectives and eager launches instead of the "
                                                       "library's own exchange kernels in a CUDA graph (prefill-sized exchanges)")

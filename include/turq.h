@@ -287,11 +287,12 @@ int32_t turq_tp_set_wait_limit(turq_tp* tp, int64_t cycles);
  * itself (default 64 KB); 0 = always use the separate exchange launch. Same value on every rank. */
 int32_t turq_tp_set_fuse_limit(turq_tp* tp, int64_t bytes);
 /* Smallest result (bytes) that takes the two-shot exchange on three or more ranks: every rank
- * reduces one slice, then copies the others (default 256 KB). Same value on every rank. */
+ * reduces one slice, then copies the others (default 4 MB). Same value on every rank. */
 int32_t turq_tp_set_twoshot_limit(turq_tp* tp, int64_t bytes);
-/* Rows per chunk of a prefill-sized turq_qmatmul_rowparallel in the dequantizing modes, whose
- * exchange overlaps the next chunk's product (0 = default, about 16 MB of result per chunk;
- * products of fewer than two chunks are not cut). Same value on every rank. */
+/* Rows per chunk of a prefill-sized turq_qmatmul_rowparallel in the dequantizing modes: the
+ * exchange of a chunk then runs on a second stream while the next chunk is computed, and an
+ * exchange slot only has to hold one chunk (0 = default: the product is not cut; products of
+ * fewer than two chunks never are). Same value on every rank. */
 int32_t turq_tp_set_chunk_rows(turq_tp* tp, int64_t rows);
 /* Clears this rank's flags and call counter. Collective in effect: call it on every rank, with
  * no group call in flight (the host synchronizes the ranks around it). */

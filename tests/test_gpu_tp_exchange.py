@@ -174,6 +174,27 @@ def test_prefill_sized_row_parallel_product_is_cut_into_chunks(tq):
     tq.context().poll_status()
 
 
+@pytest.mark.parametrize("m", [40, 300], ids=["split_k_reduction_picks_the_slot", "gemm_epilogue_picks_the_slot"])
+def test_tensor_core_product_lands_in_the_exchange_slot_without_a_copy(tq, m):
+    """In the tensor-core mode the GEMM's epilogue (or, for decode batches, its split-K
+    reduction) reads the call counter on the device and writes the slot of the upcoming call
+    itself. Four calls in a row alternate the slots; the stand-in peer contributes fresh data to
+    each, so a product written to the wrong slot would show."""
+    from tur_b200.tensor_parallel import TPGroup
+    n, k = 384, 1024
+    rng = np.random.default_rng(SEED + 99 + m)
+    w = oracle.quantize(oracle.Q6_K, (rng.standard_normal((n, k)) * 0.02).astype(np.float32))
+    mm = tq.QMatMul.from_arc(tq.QTensor.new(w, tq.GgmlDType.Q6K, (n, k)))
+    g = TPGroup(0, 2, m * n * 4, loopback=True)
+    for call in range(4):
+        x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).cuda()
+        peer = torch.from_numpy(rng.standard_normal((m, n)).astype(np.float32)).cuda()
+        g.loopback_fill(1, peer, signal=True)
+        y = g.qmatmul_rowparallel(mm, x, mode=tq.Mode.TENSOR_CORE)
+        assert torch.equal(y, mm.forward(x, mode=tq.Mode.TENSOR_CORE) + peer), call
+    tq.context().poll_status()
+
+
 def test_a_peer_that_never_arrives_ends_the_wait_with_a_status(tq):
     from tur_b200.tensor_parallel import TPGroup
     ctx = tq.new_context()

@@ -85,6 +85,7 @@ def main() -> None:
     # against the ordered sum, identical on every rank; then a prefill-sized row-parallel product
     # cut into chunks whose exchanges overlap the next chunk's GEMM, eager and as a graph
     big = TPGroup(rank, world, ((1 << 20) + 256) * 4, ctx=ctx)
+    big.set_twoshot_limit(1 << 20)                     # both sizes below take the two-shot form on 3+ ranks
     for count in (1 << 18, (1 << 20) + 4 * 37):
         x = torch.randn(count, device=dev, generator=gen)
         everyone = [torch.empty_like(x) for _ in range(world)]
@@ -103,7 +104,6 @@ def main() -> None:
     xp = torch.from_numpy(np.random.default_rng(6).standard_normal((mp, w.k)).astype(np.float32)).to(dev).to(torch.bfloat16)
     xl = xp[:, sh.cols[0]: sh.cols[0] + sh.cols[1]].contiguous()
     ref = full.forward(xp, mode=Mode.TENSOR_CORE)
-    big.set_chunk_rows(0)
     whole = TPGroup(rank, world, mp * down.n * 4, ctx=ctx)
     whole.set_chunk_rows(1 << 20)                      # never cut: the unchunked exchange of the same product
     y_whole = whole.qmatmul_rowparallel(mine, xl, mode=Mode.TENSOR_CORE)

@@ -758,6 +758,17 @@ int32_t qmatmul_for_exchange(turq_ctx* ctx, const turq_qtensor* qt, const void* 
     if (e != cudaSuccess) return cuda_fail(ctx, e, "row-parallel GEMV launch");
     return TURQ_OK;
   }
+  if (mode == TURQ_MODE_TENSOR_CORE && qt->n_cols % 64 == 0 && m <= INT32_MAX / 2) {
+    // the GEMM's epilogue (or its split-K reduction) picks the slot itself: no staging copy
+    int32_t st = ensure(ctx, &ctx->scratch, &ctx->scratch_bytes, gemm_tc_scratch_bytes(m, qt->n_cols, qt->n_rows, ctx->sm_count));
+    if (st != TURQ_OK) return st;
+    int launches = 0;
+    cudaError_t e = launch_gemm_tc(qt->dtype, qt->tiles, qt->n_rows, qt->n_cols, dev_x, x_dtype, m, s0, local_bias, ctx->scratch,
+                                   ctx->sm_count, s, &launches, ctx->dev_status, false, toggle, s1);
+    ctx->launches += launches;
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "row-parallel GEMM launch");
+    return TURQ_OK;
+  }
   int32_t st = ensure(ctx, &ctx->tmp, &ctx->tmp_bytes, (size_t)m * qt->n_rows * 4);
   if (st != TURQ_OK) return st;
   st = turq_qmatmul(ctx, qt, dev_x, x_dtype, m, reinterpret_cast<float*>(ctx->tmp), mode, local_bias, s);

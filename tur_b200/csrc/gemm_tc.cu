@@ -254,6 +254,10 @@ struct GemmArgs {
   const float* bias;
   int* status;
   int splits;       // CTAs along K per output tile (gridDim.z); > 1: a reduction launch follows
+  // exchange slots (tp.cu): with y_toggle set, the result goes to y_alt instead of y when the
+  // word it points to, plus one, is odd - read after the preceding kernels have completed
+  const unsigned* y_toggle;
+  float* y_alt;
 };
 
 // BN = activation rows per CTA (MMA N): 256 for prefill (128 when that is needed to give every
@@ -428,7 +432,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
       const int col_part = dqw >> 2;                  // 0..3
       const int64_t n = (int64_t)n0 + 32 * quarter + lane;
       const float bv = (a.bias && a.splits == 1 && n < a.n_rows) ? a.bias[n] : 0.f;
-      float* const yout = a.y + (size_t)blockIdx.z * (size_t)a.m * (size_t)a.n_rows;
+      float* ybase = a.y;
+      if (a.y_toggle && ((*reinterpret_cast<const volatile unsigned*>(a.y_toggle) + 1u) & 1u)) ybase = a.y_alt;
+      float* const yout = ybase + (size_t)blockIdx.z * (size_t)a.m * (size_t)a.n_rows;
 #pragma unroll 1
       for (int cb = 0; cb < BN / (32 * PARTS) && col_part < PARTS; cb++) {
         const int col0 = (BN / PARTS) * col_part + 32 * cb;
@@ -503,9 +509,10 @@ __global__ void __launch_bounds__(256) prep_act_kernel(const void* __restrict__ 
 // y[i] = sum of the split-K partial sums (in split order) + bias
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part, int splits, int64_t total,
                                                              int64_t n_rows, const float* __restrict__ bias,
-                                                             float* __restrict__ y) {
+                                                             float* __restrict__ y, const unsigned* y_toggle, float* y_alt) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (y_toggle && ((*reinterpret_cast<const volatile unsigned*>(y_toggle) + 1u) & 1u)) y = y_alt;
   const int64_t i4 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (i4 >= total) return;
   if (i4 + 4 <= total && (n_rows & 3) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0) {
@@ -603,7 +610,7 @@ size_t gemm_tc_scratch_bytes(int64_t m, int64_t k, int64_t n_rows, int sm_count)
 
 cudaError_t launch_gemm_tc(int dtype, const uint8_t* tiles, int64_t n_rows, int64_t k, const void* x, int x_dtype,
                            int64_t m, float* y, const float* bias, uint8_t* scratch, int sm_count, cudaStream_t s,
-                           int* launches, int* dev_status_word, bool x_prepared) {
+                           int* launches, int* dev_status_word, bool x_prepared, const unsigned* y_toggle, float* y_alt) {
   if (k % BK != 0 || m <= 0 || m > INT32_MAX || k > INT32_MAX) return cudaErrorInvalidValue;
   EncodeTiledFn enc = encode_fn();
   if (!enc) return cudaErrorNotSupported;
@@ -640,6 +647,8 @@ cudaError_t launch_gemm_tc(int dtype, const uint8_t* tiles, int64_t n_rows, int6
   a.bias = bias;
   a.status = dev_status_word;
   a.splits = splits;
+  a.y_toggle = splits > 1 ? nullptr : y_toggle;  // with split-K the reduction launch picks the buffer
+  a.y_alt = y_alt;
   switch (dtype) {
     case TQ_Q8_0: e = launch_tc_dt<TQ_Q8_0>(map, a, bn, s); break;
     case TQ_Q4_K: e = launch_tc_dt<TQ_Q4_K>(map, a, bn, s); break;
@@ -651,7 +660,7 @@ cudaError_t launch_gemm_tc(int dtype, const uint8_t* tiles, int64_t n_rows, int6
   if (e != cudaSuccess || splits == 1) return e;
   const int64_t total = m * n_rows;
   e = launch_pdl(splitk_reduce_kernel, dim3((unsigned)((total + 1023) / 1024)), dim3(256), 0, s, (const float*)partial, splits,
-                 total, n_rows, bias, y);
+                 total, n_rows, bias, y, y_toggle, y_alt);
   if (launches) (*launches)++;
   return e;
 }

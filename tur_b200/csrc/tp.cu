@@ -135,8 +135,11 @@ struct turq_tp {
   bool connected = false;
   long long wait_cycles = 2000000000ll;  // about one second of SM clock
   size_t fuse_max_bytes = 64 << 10;      // results up to this size are exchanged by the GEMV's own last CTA
-  size_t twoshot_min_bytes = 256 << 10;  // results from this size on take the two-shot exchange (3+ ranks)
-  int64_t chunk_rows = 0;                // rows per chunk of a chunked row-parallel GEMM (0: about 16 MB of result)
+  // Results from this size on take the two-shot exchange (3+ ranks). Measured at 4 ranks: a 1.3 MB
+  // result (64 decode rows) is faster one-shot (cfg5 pass 10.4 against 11.7 ms), an 84 MB result
+  // (4096 prefill rows) two-shot (113 against 134 ms).
+  size_t twoshot_min_bytes = 4 << 20;
+  int64_t chunk_rows = 0;                // rows per chunk of a chunked row-parallel GEMM (0: not cut)
   // chunked row-parallel GEMM: the exchange of chunk j runs on `comm` while chunk j + 1 is computed
   cudaStream_t comm = nullptr;
   cudaEvent_t ev_mm[2] = {}, ev_x[2] = {};
@@ -506,10 +509,13 @@ int32_t turq_qmatmul_rowparallel(turq_tp* tp, const turq_qtensor* qt, const void
   // a chunk runs on a second stream while the next chunk is computed, and a slot only has to
   // hold one chunk.
   const int32_t mode_resolved = mode == TURQ_MODE_AUTO ? turq::api_auto_mode(ctx, qt->n_rows, qt->n_cols, m) : mode;
-  int64_t chunk_m = tp->chunk_rows > 0 ? tp->chunk_rows : ((((int64_t)16 << 20) / (qt->n_rows * 4) + 255) / 256) * 256;
-  if (chunk_m < 256) chunk_m = 256;
+  // Off unless turq_tp_set_chunk_rows asks for it: measured at 4 ranks on the cfg5 prefill pass
+  // (M = 4096) the uncut product with the two-shot exchange took 113 ms, chunks of 2048 / 1024 / 768
+  // rows 116 / 126 / 135 ms - the GEMM's last wave of CTAs gets emptier with every cut.
+  int64_t chunk_m = tp->chunk_rows;
+  if (chunk_m > 0 && chunk_m < 64) chunk_m = 64;
   while (chunk_m > 64 && (size_t)chunk_m * (size_t)qt->n_rows * 4 > tp->slot_bytes) chunk_m -= 64;
-  const bool chunked = tp->world > 1 && mode_resolved != TURQ_MODE_INT8_ACT && m >= 2 * chunk_m &&
+  const bool chunked = chunk_m > 0 && tp->world > 1 && mode_resolved != TURQ_MODE_INT8_ACT && m >= 2 * chunk_m &&
                        (size_t)chunk_m * (size_t)qt->n_rows * 4 <= tp->slot_bytes;
   if (!chunked && (size_t)count * 4 > tp->slot_bytes) return tp_fail(tp, TURQ_E_LIMIT, "m x out-features exceeds an exchange slot (turq_tp_create max_bytes)");
   if ((uintptr_t)dev_y % 16 != 0) return tp_fail(tp, TURQ_E_ALIGN, "dev_y must be 16-byte aligned");

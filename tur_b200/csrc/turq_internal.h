@@ -109,11 +109,14 @@ cudaError_t launch_gemv_f32(int dtype, const uint8_t* tiles, int64_t n_rows, int
 // Tensor-core GEMM (tcgen05): x [m, k] -> f16 operand in scratch, then the fused
 // dequantize + MMA kernel. scratch must hold gemm_tc_scratch_bytes(m, k, n_rows, sm_count).
 // x_prepared: the f16 operand of this x (same m, k) is already in scratch from a preceding call.
+// y_toggle / y_alt: the result goes to y_alt instead of y when *y_toggle + 1 is odd (read on the
+// device after the preceding kernels have completed: the exchange slots of tp.cu).
 size_t gemm_tc_scratch_bytes(int64_t m, int64_t k, int64_t n_rows, int sm_count);
 cudaError_t launch_gemm_tc(int dtype, const uint8_t* tiles, int64_t n_rows, int64_t k,
                            const void* x, int x_dtype, int64_t m, float* y, const float* bias,
                            uint8_t* scratch, int sm_count, cudaStream_t s, int* launches,
-                           int* dev_status_word, bool x_prepared = false);
+                           int* dev_status_word, bool x_prepared = false, const unsigned* y_toggle = nullptr,
+                           float* y_alt = nullptr);
 
 // QMatMul (no bias) whose result has to land in one of two buffers picked on the device: s1 when
 // (*toggle + 1) is odd, else s0 (the exchange slots of tp.cu). In the integer scheme the GEMV's
