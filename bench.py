@@ -547,8 +547,8 @@ def run_gpu(args):
             "ms_per_step": e2e_ms / e2e_steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
             "api": ("turq_host_call_run (calls bound once to their page-locked buffers)" if not args.no_bound and mode == Mode.INT8_ACT and m <= 64
                     else "turq_qmatmul_multi_host / turq_qmatmul_host") +
-                   " per group of linears sharing x: page-locked host x in, page-locked host y out, one synchronize per "
-                   "call; the activation rows cross the bus once per call (read in place by the quantization launch), "
+                   " per group of linears sharing x: page-locked host x in, page-locked host y out, one wait per "
+                   "call (bound calls: on the completion word the call's last kernel stores into mapped host memory; others: a stream synchronize); the activation rows cross the bus once per call (read in place by the quantization launch), "
                    "every output once (written in place by the GEMV)"},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": sampler.summary(),

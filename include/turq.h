@@ -195,7 +195,8 @@ int32_t turq_qmatmul_multi_host(turq_ctx* ctx, int32_t count, const turq_qtensor
 /* A host-buffer call bound to its buffers, for a decoder that calls the same linears with the
  * same page-locked x / y buffers token after token (it rewrites x in place between runs):
  * create resolves the buffers' device aliases, allocates the call's own activation scratch and
- * records its launches once; run is then one graph launch and one synchronize, with the results
+ * records its launches once; run is then one graph launch and one wait (on a completion word the
+ * call's last kernel stores into mapped host memory; bounded, then a stream synchronize), with the results
  * of turq_qmatmul_multi_host(..., TURQ_MODE_INT8_ACT, no biases). 1 <= m <= 64. The buffers
  * and the weights must stay alive until destroy; runs of calls of one context are serialised by
  * the caller (they share the context's stream and hand-over workspace). Fails with

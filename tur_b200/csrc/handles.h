@@ -17,6 +17,13 @@ struct turq_ctx {
   size_t tmp_bytes = 0;
   int* host_status = nullptr;  // status word in mapped pinned host memory, written by kernels with bounded waits
   int* dev_status = nullptr;   // the same word's device address
+  // completion word of bound host calls: the last kernel of a call stores the call number into
+  // mapped host memory (word 16 of the status allocation); the host waits on that word instead
+  // of synchronizing the stream
+  volatile unsigned* host_done = nullptr;
+  unsigned* dev_done = nullptr;       // the same word's device address
+  unsigned* done_count = nullptr;     // device memory: calls signalled so far
+  unsigned done_expected = 0;         // host: calls launched so far
   uint8_t* gemv_ws = nullptr;  // split row-tile workspace of the streaming GEMV (zeroed once)
   cudaStream_t own_stream = nullptr;
   int auto_policy = 0;  // what TURQ_MODE_AUTO resolves to: 0 = by row count, else a fixed turq_mode

@@ -447,7 +447,8 @@ class QMatMul:
 class HostCall:
     """Linears bound to their page-locked host buffers (include/turq.h, turq_host_call_*): the
     caller rewrites `x` in place and calls `run()` token after token; results appear in `outs`.
-    One graph launch and one synchronize per run. Integer scheme, 1..64 rows, no bias."""
+    One graph launch and one wait on the call's completion word per run. Integer scheme, 1..64
+    rows, no bias."""
 
     def __init__(self, mms: Sequence["QMatMul"], x: torch.Tensor, outs: Optional[Sequence[torch.Tensor]] = None):
         lib = _lib.load()
