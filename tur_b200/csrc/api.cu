@@ -577,6 +577,63 @@ int32_t turq_qmatmul_multi(turq_ctx* ctx, int32_t count, const turq_qtensor* con
   return qmatmul_multi_impl(ctx, count, qts, dev_x, x_dtype, m, dev_ys, mode, dev_biases, stream, false);
 }
 
+}  // extern "C"
+
+namespace {
+// Last launch of a host-buffer call: once everything before it has completed (and its stores to the
+// caller's mapped buffers with it), the call number goes into the context's completion word in
+// mapped host memory, where the host waits for it (wait_for_signal).
+__global__ void host_signal_kernel(unsigned* count, volatile unsigned* flag) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const unsigned v = *count + 1u;
+  *count = v;
+  __threadfence_system();
+  *flag = v;
+}
+
+cudaError_t launch_host_signal(turq_ctx* ctx, cudaStream_t s) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1);
+  cfg.blockDim = dim3(1);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, host_signal_kernel, ctx->done_count, static_cast<volatile unsigned*>(ctx->dev_done));
+}
+
+// Waits for the work queued on the context's stream up to and including a signal: the signal
+// kernel goes behind it, and the host spins on the completion word - bounded: after two seconds
+// (a kernel that gave up its own bounded wait finishes far sooner) the stream is synchronized the
+// ordinary way. `launched`: the signal is part of a graph that has just been launched.
+int32_t wait_for_signal(turq_ctx* ctx, bool launched) {
+  if (!launched) {
+    cudaError_t e = launch_host_signal(ctx, ctx->own_stream);
+    ctx->launches++;
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return turq_ctx_poll_status(ctx, ctx->own_stream);
+    }
+  }
+  const unsigned expected = ++ctx->done_expected;
+  const auto t0 = std::chrono::steady_clock::now();
+  for (unsigned spins = 0; *ctx->host_done != expected; spins++) {
+    if ((spins & 0xFFFu) == 0xFFFu && std::chrono::steady_clock::now() - t0 > std::chrono::seconds(2)) {
+      cudaError_t e = cudaStreamSynchronize(ctx->own_stream);
+      if (e != cudaSuccess) return cuda_fail(ctx, e, "waiting for a host call");
+      break;
+    }
+  }
+  std::atomic_thread_fence(std::memory_order_acquire);
+  if (*static_cast<volatile int*>(ctx->host_status) != 0) return turq_ctx_poll_status(ctx, ctx->own_stream);
+  return TURQ_OK;
+}
+}  // namespace
+
+extern "C" {
+
 // Device-side alias of a host pointer when the memory is page-locked and reachable from this
 // device (cudaHostAlloc / cudaHostRegister under unified addressing); nullptr otherwise.
 static void* mapped_alias(const void* host_ptr) {
@@ -626,7 +683,7 @@ int32_t turq_qmatmul_multi_host(turq_ctx* ctx, int32_t count, const turq_qtensor
     if (ok) {
       int32_t st = qmatmul_multi_impl(ctx, count, qts, mx, TURQ_F32, m, mys, TURQ_MODE_INT8_ACT, nullptr, s, true);
       if (st != TURQ_OK) return st;
-      return turq_ctx_poll_status(ctx, s);
+      return s == ctx->own_stream ? wait_for_signal(ctx, false) : turq_ctx_poll_status(ctx, s);
     }
   }
 
@@ -657,36 +714,6 @@ int32_t turq_qmatmul_multi_host(turq_ctx* ctx, int32_t count, const turq_qtensor
     TQ_CUDA(ctx, cudaMemcpyAsync(host_ys[i], dys[i], (size_t)m * qts[i]->n_rows * 4, cudaMemcpyDeviceToHost, s));
   return turq_ctx_poll_status(ctx, s);
 }
-
-}  // extern "C"
-
-namespace {
-// Last node of a bound host call: once everything before it has completed (and its stores to the
-// caller's mapped buffers with it), the call number goes into the context's completion word in
-// mapped host memory, where turq_host_call_run waits for it.
-__global__ void host_signal_kernel(unsigned* count, volatile unsigned* flag) {
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  const unsigned v = *count + 1u;
-  *count = v;
-  __threadfence_system();
-  *flag = v;
-}
-
-cudaError_t launch_host_signal(turq_ctx* ctx, cudaStream_t s) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(1);
-  cfg.blockDim = dim3(1);
-  cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, host_signal_kernel, ctx->done_count, static_cast<volatile unsigned*>(ctx->dev_done));
-}
-}  // namespace
-
-extern "C" {
 
 int32_t turq_host_call_create(turq_ctx* ctx, int32_t count, const turq_qtensor* const* qts, const float* host_x, int64_t m,
                               float* const* host_ys, turq_host_call** out) {
@@ -754,17 +781,7 @@ int32_t turq_host_call_run(turq_host_call* hc) {
   // Wait for the call's own completion word instead of synchronizing the stream: the host sees
   // the result a few microseconds earlier. Bounded: after two seconds (a kernel that gave up its
   // own bounded wait finishes far sooner) the stream is synchronized the ordinary way.
-  const unsigned expected = ++ctx->done_expected;
-  const auto t0 = std::chrono::steady_clock::now();
-  for (unsigned spins = 0; *ctx->host_done != expected; spins++) {
-    if ((spins & 0xFFFu) == 0xFFFu && std::chrono::steady_clock::now() - t0 > std::chrono::seconds(2)) {
-      TQ_CUDA(ctx, cudaStreamSynchronize(ctx->own_stream));
-      break;
-    }
-  }
-  std::atomic_thread_fence(std::memory_order_acquire);
-  if (*static_cast<volatile int*>(ctx->host_status) != 0) return turq_ctx_poll_status(ctx, ctx->own_stream);
-  return TURQ_OK;
+  return wait_for_signal(ctx, true);
 }
 
 int32_t turq_host_call_destroy(turq_host_call* hc) {
