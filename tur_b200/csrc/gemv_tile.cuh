@@ -8,7 +8,7 @@
 //   c0 = (row g, act 2c)  c1 = (row g, act 2c+1)  c2 = (row g+8, act 2c)  c3 = (row g+8, act 2c+1).
 // Sub-block scales stay integers; one f32 multiply per (super-)block and output element.
 // Fragment chunks are read from shared memory where they are needed (128-bit loads), which
-// keeps the live register set small enough for three CTAs per SM.
+// keeps the live register set small (96 registers, no spills, two CTAs per SM).
 #pragma once
 #include "device_utils.cuh"
 #include "layout.h"
