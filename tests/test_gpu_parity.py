@@ -475,6 +475,23 @@ def test_weight_quantizer_rejects_what_it_cannot_do(tq):
     tq.context().poll_status()
 
 
+@pytest.mark.parametrize("dt,n,k,m", [(oracle.Q8_0, 256, 1728, 100), (oracle.Q4_K, 256, 1792, 40), (oracle.Q6_K, 384, 1792, 40),
+                                      (oracle.Q5_K, 128, 1792, 17)],
+                         ids=["q8_0_27_blocks_unsplit", "q4k_split_9_9_10", "q6k_split_9_9_10", "q5k_split"])
+def test_tensor_core_k_loop_with_an_odd_number_of_blocks(tq, dt, n, k, m):
+    """The GEMM's MMA thread handles two 64-wide K-blocks per barrier round; a K loop (or a CTA's
+    share of it under split-K) with an odd count ends on a half-filled pair."""
+    w = make_weight(dt, n, k, SEED + 3100 + k)
+    rng = np.random.default_rng(SEED + 3101 + m)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    xb = torch.from_numpy(x).cuda().to(torch.bfloat16)
+    mm = tq.QMatMul.from_arc(tq.QTensor.new(w, tq.GgmlDType(dt), (n, k)))
+    y = mm.forward(xb, mode=tq.Mode.TENSOR_CORE)
+    assert torch.equal(y, mm.forward(xb, mode=tq.Mode.TENSOR_CORE))
+    assert oracle.rel_fro(y.cpu().numpy(), oracle.matmul_f64(dt, w, n, k, xb.float().cpu().numpy())) < 2e-3
+    tq.context().poll_status()
+
+
 def test_no_kernel_gave_up_a_wait(tq):
     tq.context().poll_status()
 
